@@ -1,0 +1,12 @@
+"""B200-native attention path for eLLM: the attention operator of the reference's
+static graph (causal grouped-query prefill, split-KV decode, KV append into a
+static HBM cache) as hand-written sm_100a CUDA behind a C ABI.
+
+The CUDA library is required: importing the operator classes works anywhere,
+calling them without libellm_attn.so and a B200 raises.
+"""
+from ._lib import (  # noqa: F401
+    EllmError, PREFILL_AUTO, PREFILL_TCGEN05, PREFILL_WARP_MMA, header_symbols, load,
+)
+from .attention import Attention, kv_append, merge_partials  # noqa: F401
+from .kv_cache import StaticKVCache  # noqa: F401

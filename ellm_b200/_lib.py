@@ -1,0 +1,80 @@
+"""ctypes loader of libellm_attn.so and the declarations of include/ellm_attn.h.
+
+There is no fallback: if the library is missing and cannot be built, or a call
+fails, an exception is raised.
+"""
+import ctypes as C
+import os
+import re
+
+from . import build as _build
+
+OK, ERR_INVALID_ARG, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_UNSUPPORTED, ERR_NO_MEMORY = range(6)
+DTYPE_BF16 = 0
+PREFILL_AUTO, PREFILL_TCGEN05, PREFILL_WARP_MMA = 0, 1, 2
+KERNEL_KV_APPEND, KERNEL_DECODE_SPLITKV, KERNEL_MERGE, KERNEL_PREFILL_TCGEN05, KERNEL_PREFILL_WARP_MMA = range(5)
+KERNEL_NAMES = ["kv_append", "decode_splitkv", "merge", "prefill_tcgen05", "prefill_warp_mma"]
+
+
+class EllmError(RuntimeError):
+    def __init__(self, status, text):
+        super().__init__(f"ellm_attn status {status}: {text}")
+        self.status = status
+
+
+class AttnDesc(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("out", C.c_void_p),
+        ("lse", C.c_void_p), ("k_new", C.c_void_p), ("v_new", C.c_void_p),
+        ("max_batch", C.c_size_t), ("q_heads", C.c_size_t), ("kv_heads", C.c_size_t),
+        ("head_size", C.c_size_t), ("kv_strides", C.c_size_t * 4), ("max_seq", C.c_size_t),
+        ("max_interval", C.c_size_t), ("scale", C.c_float), ("dtype", C.c_int), ("device", C.c_int),
+        ("stream", C.c_void_p), ("async_", C.c_int), ("prefill_kernel", C.c_int),
+    ]
+
+
+_lib = None
+
+_SZ, _VP, _I = C.c_size_t, C.c_void_p, C.c_int
+_SIGNATURES = {
+    "ellm_attn_create": (_I, [C.POINTER(AttnDesc), C.POINTER(_VP)]),
+    "ellm_attn_destroy": (_I, [_VP]),
+    "ellm_attn_run": (_I, [_VP, _SZ, _SZ, _SZ, _SZ, _SZ]),
+    "ellm_attn_run_ragged": (_I, [_VP, _VP, _SZ, _SZ, _SZ, _SZ]),
+    "ellm_attn_run_host": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _SZ, _SZ, _SZ]),
+    "ellm_device_alloc": (_I, [_I, _SZ, C.POINTER(_VP)]),
+    "ellm_device_free": (_I, [_I, _VP]),
+    "ellm_kv_append": (_I, [_VP, _VP, C.POINTER(_SZ), _SZ, _SZ, _SZ, _SZ, _SZ, _VP, _SZ, _SZ, _I, _VP]),
+    "ellm_attn_merge_partials": (_I, [_VP, _VP, _SZ, _SZ, _SZ, _VP, _VP, _I, _VP]),
+    "ellm_attn_run_window": (_I, [_VP, _SZ, _SZ, _SZ, _SZ, _SZ, _VP, _VP]),
+    "ellm_attn_set_profiling": (_I, [_VP, _I]),
+    "ellm_attn_kernel_stats": (_I, [_VP, _I, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
+    "ellm_last_error": (C.c_char_p, []),
+    "ellm_status_string": (C.c_char_p, [_I]),
+    "ellm_attn_abi_version": (_I, []),
+}
+
+
+def header_symbols():
+    """Names of the functions include/ellm_attn.h declares (parsed from the header)."""
+    with open(os.path.join(_build.INCLUDE, "ellm_attn.h")) as f:
+        text = re.sub(r"/\*.*?\*/", "", f.read(), flags=re.S)
+    return sorted(set(re.findall(r"\b(ellm_[a-z0-9_]+)\s*\(", text)))
+
+
+def load():
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.build()
+    lib = C.CDLL(path)
+    for name, (res, args) in _SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+        fn.restype, fn.argtypes = res, args
+    _lib = lib
+    return lib
+
+
+def check(status):
+    if status != OK:
+        raise EllmError(status, load().ellm_last_error().decode())

@@ -1,0 +1,110 @@
+"""Host-side mirror of the reference's attention operator over the C ABI.
+
+`Attention.new(...)` takes the arguments of the reference's `Attention::new`
+(src/compiler/mul/attention.rs:41-67) in the same order and with the same
+meaning, and `run(position_index, position_interval, batch_size, cpu_num,
+thread_id)` is its `run` (attention.rs:69-76).  What a device needs beyond that
+(cache capacity, the new K/V rows to append, an LSE output, a stream) are keyword
+arguments.  Tensors are torch CUDA tensors used purely as device buffers; raw
+integer device pointers work too.
+"""
+import ctypes as C
+
+from . import _lib as L
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    return x.data_ptr()
+
+
+class Attention:
+    def __init__(self):
+        raise TypeError("use Attention.new(...)")
+
+    @classmethod
+    def new(cls, q_ptr, k_ptr, v_ptr, output_ptr, batch_size, attention_head_num, kv_head_num,
+            head_size, kv_strides, inverse_sqrt_head, *, max_seq, max_interval=1, lse=None,
+            k_new=None, v_new=None, device=0, stream=None, async_=False,
+            prefill_kernel=L.PREFILL_AUTO):
+        self = object.__new__(cls)
+        lib = L.load()
+        d = L.AttnDesc()
+        d.q, d.k_cache, d.v_cache, d.out = _ptr(q_ptr), _ptr(k_ptr), _ptr(v_ptr), _ptr(output_ptr)
+        d.lse, d.k_new, d.v_new = _ptr(lse), _ptr(k_new), _ptr(v_new)
+        d.max_batch, d.q_heads, d.kv_heads, d.head_size = batch_size, attention_head_num, kv_head_num, head_size
+        d.kv_strides = (C.c_size_t * 4)(*[int(s) for s in kv_strides])
+        d.max_seq, d.max_interval = max_seq, max_interval
+        d.scale = float(inverse_sqrt_head)
+        d.dtype, d.device = L.DTYPE_BF16, device
+        d.stream = stream
+        d.async_ = 1 if async_ else 0
+        d.prefill_kernel = prefill_kernel
+        handle = C.c_void_p()
+        L.check(lib.ellm_attn_create(C.byref(d), C.byref(handle)))
+        self._lib, self._h, self.desc = lib, handle, d
+        # keep the buffers alive as long as the operator (the reference leaks them instead)
+        self._keep = (q_ptr, k_ptr, v_ptr, output_ptr, lse, k_new, v_new)
+        return self
+
+    def run(self, position_index, position_interval, batch_size, cpu_num=1, thread_id=0):
+        L.check(self._lib.ellm_attn_run(self._h, position_index, position_interval, batch_size,
+                                        cpu_num, thread_id))
+
+    def run_ragged(self, positions, position_interval, batch_size, cpu_num=1, thread_id=0):
+        L.check(self._lib.ellm_attn_run_ragged(self._h, _ptr(positions), position_interval,
+                                               batch_size, cpu_num, thread_id))
+
+    def run_window(self, position_index, position_interval, batch_size, key_begin, key_end,
+                   o_part, lse_part):
+        L.check(self._lib.ellm_attn_run_window(self._h, position_index, position_interval,
+                                               batch_size, key_begin, key_end, _ptr(o_part),
+                                               _ptr(lse_part)))
+
+    def run_host(self, q_host, out_host, position_index, position_interval, batch_size, *,
+                 k_new_host=None, v_new_host=None, lse_host=None, positions_host=None):
+        L.check(self._lib.ellm_attn_run_host(self._h, _ptr(q_host), _ptr(k_new_host),
+                                             _ptr(v_new_host), _ptr(out_host), _ptr(lse_host),
+                                             _ptr(positions_host), position_index,
+                                             position_interval, batch_size))
+
+    def set_profiling(self, on):
+        L.check(self._lib.ellm_attn_set_profiling(self._h, 1 if on else 0))
+
+    def kernel_stats(self):
+        """{kernel name: (launches, timed launches, total ms of the timed ones)}"""
+        out = {}
+        for i, name in enumerate(L.KERNEL_NAMES):
+            n, t, ms = C.c_uint64(), C.c_uint64(), C.c_double()
+            L.check(self._lib.ellm_attn_kernel_stats(self._h, i, C.byref(n), C.byref(t), C.byref(ms)))
+            out[name] = (n.value, t.value, ms.value)
+        return out
+
+    def close(self):
+        if self._h:
+            self._lib.ellm_attn_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def kv_append(cache, src, kv_strides, max_batch, kv_heads, head_size, max_seq, position_index,
+              position_interval, batch_size, positions=None, device=0, stream=None):
+    lib = L.load()
+    L.check(lib.ellm_kv_append(_ptr(cache), _ptr(src), (C.c_size_t * 4)(*[int(s) for s in kv_strides]),
+                               max_batch, kv_heads, head_size, max_seq, position_index,
+                               _ptr(positions), position_interval, batch_size, device, stream))
+
+
+def merge_partials(o_parts, lse_parts, out, lse_out=None, device=0, stream=None):
+    """o_parts [parts, rows, 128] fp32, lse_parts [parts, rows] fp32 -> out [rows, 128] bf16."""
+    parts, rows, d = o_parts.shape
+    L.check(L.load().ellm_attn_merge_partials(_ptr(o_parts), _ptr(lse_parts), parts, rows, d,
+                                              _ptr(out), _ptr(lse_out), device, stream))

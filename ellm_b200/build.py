@@ -1,0 +1,55 @@
+"""Compiles the CUDA library in-tree: ellm_b200/libellm_attn.so (sm_100a only).
+
+`python -m ellm_b200.build` rebuilds when a source is newer than the library.
+"""
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libellm_attn.so")
+INCLUDE = os.path.join(os.path.dirname(HERE), "include")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-shared", "-Xcompiler", "-fPIC", "--use_fast_math=false",
+]
+
+
+def sources():
+    out = [os.path.join(INCLUDE, "ellm_attn.h")]
+    for name in sorted(os.listdir(CSRC)):
+        if name.endswith((".cu", ".cuh", ".h")):
+            out.append(os.path.join(CSRC, name))
+    return out
+
+
+def stale():
+    if not os.path.exists(LIB):
+        return True
+    t = os.path.getmtime(LIB)
+    return any(os.path.getmtime(s) > t for s in sources())
+
+
+def build(force=False, verbose=False):
+    if not force and not stale():
+        return LIB
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        raise RuntimeError("nvcc not found: cannot build libellm_attn.so")
+    cmd = [nvcc] + [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += ["-I", INCLUDE, "-o", LIB, os.path.join(CSRC, "ellm_attn_api.cu")]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    if verbose:
+        sys.stderr.write(res.stderr)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

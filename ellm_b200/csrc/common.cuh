@@ -1,0 +1,184 @@
+// Shared device helpers for the attention kernels (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ellm {
+
+constexpr int kHeadDim = 128;            // the reference's f16 kernel hard-wires 128 as well
+constexpr int kRowBytes = kHeadDim * 2;  // one K or V row in bf16
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// The reference's work partitioner (src/compiler/assign.rs:11-38): split
+// [0, length) into `num` parts, the first length % num parts one longer.
+// Returns false when part `id` is empty.
+__host__ __device__ inline bool assign_range(long long length, long long num, long long id,
+                                             long long* begin, long long* end) {
+    if (length < id + 1) return false;
+    long long q = length / num, r = length % num;
+    if (id < r) {
+        *begin = (q + 1) * id;
+        *end = *begin + q + 1;
+    } else {
+        *begin = q * id + r;
+        *end = *begin + q;
+    }
+    return true;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// 16-byte async global->shared copy; src_bytes == 0 zero-fills the destination.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
+                 "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                            uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1,
+                                                  uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+
+// D(16x8, fp32) += A(16x16, bf16, row) * B(16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Byte offset of 16-byte chunk `chunk` (0..15) of row `row` in a tile of 256-byte
+// rows, XOR-swizzled so that the 8 rows one ldmatrix phase touches fall in 8
+// different bank groups.
+__device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
+    return static_cast<uint32_t>(row * kRowBytes + ((chunk ^ (row & 7)) << 4));
+}
+
+// Online-softmax state of one warp over a 16-row tile: thread `lane` owns rows
+// lane/4 and lane/4 + 8, and of every 8-wide column block the columns
+// (lane%4)*2, +1 - the accumulator layout of m16n8k16.
+struct RowState {
+    float m[2];  // running max of scaled scores, log2 domain
+    float l[2];  // running sum of exp2(score - m), this thread's columns only until finalised
+};
+
+// One step of the recurrence on a 16 x (8*NKB) score tile held in s[NKB][4]
+// (already multiplied by scale*log2e and masked with -inf), followed by
+// O += P * V for V rows [0, 8*NKB) of the swizzled smem tile at v_base.
+// o[16][4]: 16 blocks of 8 head-dim columns.
+template <int NKB>
+__device__ __forceinline__ void softmax_pv_step(float (&s)[NKB][4], RowState& st, float (&o)[16][4],
+                                                uint32_t v_base, int lane) {
+    float mx[2] = {st.m[0], st.m[1]};
+#pragma unroll
+    for (int j = 0; j < NKB; ++j) {
+        mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
+        mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    }
+    float corr[2], msub[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        // a row that has seen no key yet keeps m = -inf; subtract 0 there so that
+        // exp2(-inf - 0) = 0 instead of exp2(-inf + inf) = NaN
+        msub[r] = (mx[r] == -INFINITY) ? 0.0f : mx[r];
+        corr[r] = fast_exp2(st.m[r] - msub[r]);
+        st.m[r] = mx[r];
+        st.l[r] *= corr[r];
+    }
+#pragma unroll
+    for (int j = 0; j < NKB; ++j) {
+        s[j][0] = fast_exp2(s[j][0] - msub[0]);
+        s[j][1] = fast_exp2(s[j][1] - msub[0]);
+        s[j][2] = fast_exp2(s[j][2] - msub[1]);
+        s[j][3] = fast_exp2(s[j][3] - msub[1]);
+        st.l[0] += s[j][0] + s[j][1];
+        st.l[1] += s[j][2] + s[j][3];
+    }
+#pragma unroll
+    for (int nb = 0; nb < 16; ++nb) {
+        o[nb][0] *= corr[0];
+        o[nb][1] *= corr[0];
+        o[nb][2] *= corr[1];
+        o[nb][3] *= corr[1];
+    }
+    // P (bf16) as the A operand: key blocks 2*kk and 2*kk+1 form one k16 step
+    const int mat = lane >> 3, mrow = lane & 7;
+#pragma unroll
+    for (int kk = 0; kk < NKB / 2; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+        // ldmatrix.x4.trans: matrices (keys 0-7, d0-7), (keys 8-15, d0-7),
+        // (keys 0-7, d8-15), (keys 8-15, d8-15) of this k16 step
+        const int vrow = kk * 16 + (mat & 1) * 8 + mrow;
+#pragma unroll
+        for (int np = 0; np < 8; ++np) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(v_base + swz_off(vrow, np * 2 + (mat >> 1)), b0, b1, b2, b3);
+            mma_bf16_16816(o[2 * np], a, b0, b1);
+            mma_bf16_16816(o[2 * np + 1], a, b2, b3);
+        }
+    }
+}
+
+// S(16 x 8*NKB) = Q(16 x 128) * K^T for K rows [0, 8*NKB) of the swizzled smem tile.
+// qf[8][4]: the A fragments of the 8 k16 steps over head_dim.
+template <int NKB>
+__device__ __forceinline__ void qk_step(const uint32_t (&qf)[8][4], uint32_t k_base, float (&s)[NKB][4],
+                                        int lane) {
+    const int mat = lane >> 3, mrow = lane & 7;
+#pragma unroll
+    for (int j = 0; j < NKB; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+#pragma unroll
+    for (int jp = 0; jp < NKB / 2; ++jp) {
+        // ldmatrix.x4: (keys 0-7, d0-7), (keys 0-7, d8-15), (keys 8-15, d0-7), (keys 8-15, d8-15)
+        const int krow = jp * 16 + (mat >> 1) * 8 + mrow;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(k_base + swz_off(krow, ks * 2 + (mat & 1)), b0, b1, b2, b3);
+            mma_bf16_16816(s[2 * jp], qf[ks], b0, b1);
+            mma_bf16_16816(s[2 * jp + 1], qf[ks], b2, b3);
+        }
+    }
+}
+
+}  // namespace ellm

@@ -1,0 +1,254 @@
+// K2: split-KV decode attention, one new query row per sequence.  HBM-bound: every
+// K and V row of every live sequence is read exactly once per call, whatever the
+// number of query heads sharing it.
+//
+// Replaces, for position_interval == 1, the per-(sequence, query head) key loop of
+// the reference kernel (src/kernel/x86_64/f16_512/flash_attention.rs:58-86, called
+// per item from src/compiler/mul/attention.rs:117-153).
+//
+// Work decomposition.  A *segment* is one (sequence b, KV head, block of <=16 query
+// heads of its group); its keys are cut into tiles of 64.  All tiles of all
+// segments form one flat list which is split evenly over the resident CTAs with
+// the reference's own partitioner rule (compiler::assign).  A CTA walks its
+// contiguous tile range; each maximal run inside one segment is a *piece* and
+// yields one fp32 partial (O, LSE) in the workspace, slot = cta + segment (unique
+// because consecutive pieces advance the CTA index, the segment index or both).
+// merge_partials.cuh then combines the pieces of each segment.
+//
+// Inside a CTA the 4 warps are independent streams: warp w owns keys
+// [16w, 16w+16) of every tile, copies them global->shared itself (cp.async, 16 B
+// per lane, 512 B contiguous per instruction, XOR-swizzled rows), and keeps its
+// own online-softmax state; the warps only meet at the end of a piece.  Q.K^T and
+// P.V run on the warp-level tensor-core MMA with the <=16 query heads of the
+// group as the M dimension, so one K/V read serves the whole group.
+#pragma once
+#include "common.cuh"
+
+namespace ellm {
+
+constexpr int kDecWarps = 4;
+constexpr int kDecThreads = kDecWarps * 32;
+constexpr int kDecTileKeys = 64;                  // keys per tile (16 per warp)
+constexpr int kDecStages = 3;                     // cp.async ring depth per warp
+constexpr int kDecWarpStageBytes = 16 * kRowBytes * 2;  // 16 K rows + 16 V rows = 8 KB
+constexpr int kDecMaxBatch = 1024;                // prefix table held in shared memory
+constexpr int kDecSmemBytes = kDecWarps * kDecStages * kDecWarpStageBytes + (kDecMaxBatch + 1) * 4;
+
+struct DecodeParams {
+    const __nv_bfloat16* q;        // [max_batch, q_heads, 128] (chunk row 0)
+    const __nv_bfloat16* k_cache;
+    const __nv_bfloat16* v_cache;
+    float* part_o;                 // [slots, 16, 128]
+    float* part_lse;               // [slots, 16]
+    int* prefix_out;               // [max_batch + 1]: block 0 publishes the tile prefix table for the merge
+    const int32_t* positions;      // device int32[batch] or nullptr
+    long long uniform_len;         // keys per sequence when positions == nullptr
+    long long len_cap;             // no sequence is read past this many keys (cache rows / window end)
+    long long key_begin;           // attend keys [key_begin, len) only (0 for a plain decode)
+    long long s0, s1, s2;          // kv strides in elements (batch, head, position)
+    int batch;
+    int q_heads, kv_heads, group;  // group = q_heads / kv_heads
+    int gtiles;                    // ceil(group / 16)
+    float scale_log2;              // scale * log2(e)
+    int num_ctas;
+};
+
+// Keys sequence b attends: its new token sits at positions[b], so positions[b] + 1.
+__device__ __forceinline__ long long dec_seq_len(const DecodeParams& p, int b) {
+    long long len = p.positions ? static_cast<long long>(p.positions[b]) + 1 : p.uniform_len;
+    return len < p.len_cap ? len : p.len_cap;
+}
+
+// Tiles of sequence b (all of its segments have the same count).
+__device__ __forceinline__ int dec_seq_tiles(const DecodeParams& p, int b) {
+    long long n = dec_seq_len(p, b) - p.key_begin;
+    if (n <= 0) return 0;
+    return static_cast<int>((n + kDecTileKeys - 1) / kDecTileKeys);
+}
+
+// prefix[b] = sum of tiles of sequences < b, for b in [0, batch]; all threads call.
+__device__ inline void dec_build_prefix(const DecodeParams& p, int* prefix) {
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int b = 0; b < p.batch; ++b) {
+            prefix[b] = acc;
+            acc += dec_seq_tiles(p, b);
+        }
+        prefix[p.batch] = acc;
+    }
+    __syncthreads();
+}
+
+// Largest b with prefix[b] * segs_per_seq <= t  (t < total tiles), skipping empty
+// sequences.
+__device__ __forceinline__ int dec_find_seq(const int* prefix, int batch, long long segs_per_seq,
+                                            long long t) {
+    int lo = 0, hi = batch;  // invariant: prefix[lo]*S <= t < prefix[hi]*S
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (static_cast<long long>(prefix[mid]) * segs_per_seq <= t) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+__global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const DecodeParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    int* prefix = reinterpret_cast<int*>(smem + kDecWarps * kDecStages * kDecWarpStageBytes);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t warp_smem = smem_u32(smem) + warp * kDecStages * kDecWarpStageBytes;
+
+    dec_build_prefix(p, prefix);
+    if (blockIdx.x == 0)
+        for (int i = threadIdx.x; i <= p.batch; i += kDecThreads) p.prefix_out[i] = prefix[i];
+    const long long segs_per_seq = static_cast<long long>(p.kv_heads) * p.gtiles;
+    const long long total = static_cast<long long>(prefix[p.batch]) * segs_per_seq;
+    long long t_begin, t_end;
+    if (!assign_range(total, p.num_ctas, blockIdx.x, &t_begin, &t_end)) return;
+
+    const int r0 = lane >> 2;  // this thread's rows: r0 and r0 + 8
+    long long t = t_begin;
+    while (t < t_end) {
+        // ---- locate the piece: segment of tile t and how far it runs ----
+        const int b = dec_find_seq(prefix, p.batch, segs_per_seq, t);
+        const int tiles_b = prefix[b + 1] - prefix[b];
+        const long long seq_base = static_cast<long long>(prefix[b]) * segs_per_seq;
+        const int seg_in_seq = static_cast<int>((t - seq_base) / tiles_b);
+        const int tile0 = static_cast<int>((t - seq_base) % tiles_b);
+        const long long seg_end = seq_base + static_cast<long long>(seg_in_seq + 1) * tiles_b;
+        const long long piece_end = seg_end < t_end ? seg_end : t_end;
+        const int ntiles = static_cast<int>(piece_end - t);
+        const int kvh = seg_in_seq / p.gtiles, gt = seg_in_seq % p.gtiles;
+        const long long segment = static_cast<long long>(b) * segs_per_seq + seg_in_seq;
+        const long long len = dec_seq_len(p, b);
+        const int rows_valid = min(16, p.group - gt * 16);
+        const long long key0 = p.key_begin + static_cast<long long>(tile0) * kDecTileKeys + warp * 16;
+        const __nv_bfloat16* kbase = p.k_cache + b * p.s0 + kvh * p.s1;
+        const __nv_bfloat16* vbase = p.v_cache + b * p.s0 + kvh * p.s1;
+
+        // ---- cp.async ring: lane copies chunk (lane&15) of rows (lane>>4) + 2*i ----
+        auto issue = [&](int it) {
+            const long long kfirst = key0 + static_cast<long long>(it) * kDecTileKeys;
+            const uint32_t sK = warp_smem + (it % kDecStages) * kDecWarpStageBytes;
+            const uint32_t sV = sK + 16 * kRowBytes;
+            const int chunk = lane & 15;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int row = (lane >> 4) + 2 * i;
+                const long long key = kfirst + row;
+                const bool ok = key < len;
+                const long long off = (ok ? key : 0) * p.s2 + chunk * 8;
+                cp_async_16(sK + swz_off(row, chunk), kbase + off, ok ? 16 : 0);
+                cp_async_16(sV + swz_off(row, chunk), vbase + off, ok ? 16 : 0);
+            }
+        };
+#pragma unroll
+        for (int s = 0; s < kDecStages - 1; ++s) {
+            if (s < ntiles) issue(s);
+            cp_async_commit();
+        }
+
+        // ---- Q fragments: rows = query heads kvh*group + gt*16 + r ----
+        uint32_t qf[8][4];
+        {
+            const int c0 = (lane & 3) * 2;
+            const __nv_bfloat16* qrow0 =
+                p.q + (static_cast<long long>(b) * p.q_heads + kvh * p.group + gt * 16 + r0) * kHeadDim;
+            const __nv_bfloat16* qrow1 = qrow0 + 8 * kHeadDim;
+            const bool v0 = r0 < rows_valid, v1 = r0 + 8 < rows_valid;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                qf[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(qrow0 + ks * 16 + c0) : 0u;
+                qf[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(qrow1 + ks * 16 + c0) : 0u;
+                qf[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(qrow0 + ks * 16 + c0 + 8) : 0u;
+                qf[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(qrow1 + ks * 16 + c0 + 8) : 0u;
+            }
+        }
+
+        RowState st;
+        st.m[0] = st.m[1] = -INFINITY;
+        st.l[0] = st.l[1] = 0.0f;
+        float o[16][4];
+#pragma unroll
+        for (int nb = 0; nb < 16; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.0f;
+
+        for (int it = 0; it < ntiles; ++it) {
+            if (it + kDecStages - 1 < ntiles) issue(it + kDecStages - 1);
+            cp_async_commit();
+            cp_async_wait<kDecStages - 1>();
+            __syncwarp();
+            const long long kfirst = key0 + static_cast<long long>(it) * kDecTileKeys;
+            if (kfirst < len) {  // warp-uniform: this warp's 16 keys are not all past the end
+                const uint32_t sK = warp_smem + (it % kDecStages) * kDecWarpStageBytes;
+                float s[2][4];
+                qk_step<2>(qf, sK, s, lane);
+                const long long kc = kfirst + (lane & 3) * 2;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const bool in0 = kc + 8 * j < len, in1 = kc + 8 * j + 1 < len;
+                    s[j][0] = in0 ? s[j][0] * p.scale_log2 : -INFINITY;
+                    s[j][1] = in1 ? s[j][1] * p.scale_log2 : -INFINITY;
+                    s[j][2] = in0 ? s[j][2] * p.scale_log2 : -INFINITY;
+                    s[j][3] = in1 ? s[j][3] * p.scale_log2 : -INFINITY;
+                }
+                softmax_pv_step<2>(s, st, o, sK + 16 * kRowBytes, lane);
+            }
+            __syncwarp();  // all lanes done with this stage before it is refilled
+        }
+        cp_async_wait<0>();
+
+        // ---- end of piece: combine the 4 warps through shared memory ----
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+            st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+        }
+        __syncthreads();  // every warp has drained its ring; smem is free
+        float* so = reinterpret_cast<float*>(smem);             // [warps][16][128]
+        float* sm = so + kDecWarps * 16 * kHeadDim;             // [warps][16]
+        float* sl = sm + kDecWarps * 16;                        // [warps][16]
+        {
+            float* wo = so + warp * 16 * kHeadDim;
+            const int c0 = (lane & 3) * 2;
+#pragma unroll
+            for (int nb = 0; nb < 16; ++nb) {
+                *reinterpret_cast<float2*>(wo + r0 * kHeadDim + nb * 8 + c0) = make_float2(o[nb][0], o[nb][1]);
+                *reinterpret_cast<float2*>(wo + (r0 + 8) * kHeadDim + nb * 8 + c0) = make_float2(o[nb][2], o[nb][3]);
+            }
+            if ((lane & 3) == 0) {
+                sm[warp * 16 + r0] = st.m[0];
+                sm[warp * 16 + r0 + 8] = st.m[1];
+                sl[warp * 16 + r0] = st.l[0];
+                sl[warp * 16 + r0 + 8] = st.l[1];
+            }
+        }
+        __syncthreads();
+        {
+            const long long slot = static_cast<long long>(blockIdx.x) + segment;
+            float* po = p.part_o + slot * 16 * kHeadDim;
+            for (int idx = threadIdx.x; idx < rows_valid * (kHeadDim / 4); idx += kDecThreads) {
+                const int r = idx / (kHeadDim / 4), c4 = (idx % (kHeadDim / 4)) * 4;
+                float mmax = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < kDecWarps; ++w) mmax = fmaxf(mmax, sm[w * 16 + r]);
+                float lsum = 0.0f;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int w = 0; w < kDecWarps; ++w) {
+                    const float mw = sm[w * 16 + r];
+                    const float a = (mw == -INFINITY) ? 0.0f : fast_exp2(mw - mmax);
+                    lsum += a * sl[w * 16 + r];
+                    const float4 x = *reinterpret_cast<const float4*>(so + (w * 16 + r) * kHeadDim + c4);
+                    acc.x += a * x.x; acc.y += a * x.y; acc.z += a * x.z; acc.w += a * x.w;
+                }
+                const float inv = 1.0f / lsum;
+                acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+                *reinterpret_cast<float4*>(po + r * kHeadDim + c4) = acc;
+                if (c4 == 0) p.part_lse[slot * 16 + r] = (mmax + log2f(lsum)) * kLn2;
+            }
+        }
+        __syncthreads();  // smem is reused by the next piece's ring
+        t = piece_end;
+    }
+}
+
+}  // namespace ellm

@@ -1,0 +1,560 @@
+// C ABI of the attention path (see include/ellm_attn.h): argument checks, the
+// handle, kernel selection and launches.  No torch types, no CPU fallback: every
+// call either launches the CUDA kernels or returns an error status.
+#include "../../include/ellm_attn.h"
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <utility>
+#include <vector>
+
+#include "decode_splitkv.cuh"
+#include "kv_append.cuh"
+#include "merge_partials.cuh"
+#include "prefill_warp_mma.cuh"
+#include "prefill_tcgen05.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int status, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+#define ELLM_CUDA(call)                                                                      \
+    do {                                                                                     \
+        cudaError_t e_ = (call);                                                             \
+        if (e_ != cudaSuccess)                                                               \
+            return fail(ELLM_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), \
+                        __FILE__, __LINE__);                                                 \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+        if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+struct ellm_attn {
+    ellm_attn_desc d;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    int group = 1, gtiles = 1;
+    int dec_ctas = 0;
+    size_t slots = 0;
+    float* part_o = nullptr;
+    float* part_lse = nullptr;
+    int* prefix = nullptr;
+    int32_t* positions_dev = nullptr;  // staging for ellm_attn_run_host
+    int* status_dev = nullptr;         // bounded-wait status word written by the tcgen05 kernel
+    int* status_host = nullptr;        // pinned mirror
+    ellm::Tcgen05Plan tc;              // tensor maps etc. of the tcgen05 prefill kernel
+    std::mutex mu;
+    uint64_t launches[ELLM_KERNEL_COUNT] = {};
+    uint64_t timed[ELLM_KERNEL_COUNT] = {};
+    double total_ms[ELLM_KERNEL_COUNT] = {};
+    bool profiling = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending[ELLM_KERNEL_COUNT];
+};
+
+namespace {
+
+struct LaunchScope {  // counts a launch and, when profiling, brackets it with events
+    ellm_attn* h;
+    int id;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    LaunchScope(ellm_attn* h_, int id_) : h(h_), id(id_) {
+        if (h && h->profiling) {
+            cudaEventCreate(&e0);
+            cudaEventCreate(&e1);
+            cudaEventRecord(e0, h->stream);
+        }
+    }
+    ~LaunchScope() {
+        if (!h) return;
+        h->launches[id]++;
+        if (e0) {
+            cudaEventRecord(e1, h->stream);
+            h->pending[id].emplace_back(e0, e1);
+        }
+    }
+};
+
+int check_desc(const ellm_attn_desc* d) {
+    if (!d) return fail(ELLM_ERR_INVALID_ARG, "desc is NULL");
+    if (!d->q || !d->k_cache || !d->v_cache || !d->out)
+        return fail(ELLM_ERR_INVALID_ARG, "q, k_cache, v_cache and out must be non-NULL");
+    if ((d->k_new == nullptr) != (d->v_new == nullptr))
+        return fail(ELLM_ERR_INVALID_ARG, "k_new and v_new must be both set or both NULL");
+    if (d->dtype != ELLM_DTYPE_BF16) return fail(ELLM_ERR_UNSUPPORTED, "dtype %d: only bf16", d->dtype);
+    if (d->head_size != static_cast<size_t>(ellm::kHeadDim))
+        return fail(ELLM_ERR_UNSUPPORTED, "head_size %zu: only 128 (as the reference's f16 kernel)", d->head_size);
+    if (d->max_batch == 0 || d->q_heads == 0 || d->kv_heads == 0 || d->max_seq == 0 || d->max_interval == 0)
+        return fail(ELLM_ERR_INVALID_ARG, "max_batch, q_heads, kv_heads, max_seq, max_interval must be > 0");
+    if (d->q_heads % d->kv_heads != 0)
+        return fail(ELLM_ERR_INVALID_ARG, "q_heads %zu is not a multiple of kv_heads %zu", d->q_heads, d->kv_heads);
+    if (d->kv_strides[3] != 1) return fail(ELLM_ERR_UNSUPPORTED, "kv_strides[3] must be 1 (head_dim contiguous)");
+    for (int i = 0; i < 3; ++i)
+        if (d->kv_strides[i] % 8 != 0 || d->kv_strides[i] == 0)
+            return fail(ELLM_ERR_INVALID_ARG, "kv_strides[%d] = %zu must be a non-zero multiple of 8 elements", i, d->kv_strides[i]);
+    if (!aligned16(d->q) || !aligned16(d->k_cache) || !aligned16(d->v_cache) || !aligned16(d->out) ||
+        !aligned16(d->k_new) || !aligned16(d->v_new))
+        return fail(ELLM_ERR_INVALID_ARG, "device buffers must be 16-byte aligned");
+    if (d->lse && (reinterpret_cast<uintptr_t>(d->lse) & 3u)) return fail(ELLM_ERR_INVALID_ARG, "lse misaligned");
+    if (!(d->scale > 0.0f) || !std::isfinite(d->scale)) return fail(ELLM_ERR_INVALID_ARG, "scale must be finite and > 0");
+    if (d->prefill_kernel < ELLM_PREFILL_AUTO || d->prefill_kernel > ELLM_PREFILL_WARP_MMA)
+        return fail(ELLM_ERR_INVALID_ARG, "prefill_kernel %d unknown", d->prefill_kernel);
+    return ELLM_OK;
+}
+
+int launch_append(ellm_attn* h, cudaStream_t stream, void* k_cache, void* v_cache, const void* k_new,
+                  const void* v_new, const size_t* strides, size_t max_batch, size_t kv_heads,
+                  size_t max_seq, size_t position_index, const int32_t* positions, size_t interval,
+                  size_t batch) {
+    ellm::AppendParams ap;
+    ap.k_new = static_cast<const uint4*>(k_new);
+    ap.v_new = static_cast<const uint4*>(v_new);
+    ap.k_cache = static_cast<__nv_bfloat16*>(k_cache);
+    ap.v_cache = static_cast<__nv_bfloat16*>(v_cache);
+    ap.positions = positions;
+    ap.position_index = static_cast<long long>(position_index);
+    ap.s0 = strides[0]; ap.s1 = strides[1]; ap.s2 = strides[2];
+    ap.max_seq = static_cast<long long>(max_seq);
+    ap.interval = static_cast<int>(interval);
+    ap.batch = static_cast<int>(batch);
+    ap.max_batch = static_cast<int>(max_batch);
+    ap.kv_heads = static_cast<int>(kv_heads);
+    const long long threads = static_cast<long long>(interval) * batch * kv_heads * 16;
+    const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
+    {
+        LaunchScope ls(h, ELLM_KERNEL_KV_APPEND);
+        ellm::kv_append_kernel<<<blocks, 256, 0, stream>>>(ap);
+    }
+    ELLM_CUDA(cudaGetLastError());
+    return ELLM_OK;
+}
+
+// Decode (interval == 1): K2 then K3.  out_f32 != nullptr selects the fp32
+// partial output of the windowed form.
+int launch_decode(ellm_attn* h, const int32_t* positions, size_t position_index, size_t batch,
+                  long long key_begin, long long key_end, float* out_f32, float* lse_out) {
+    if (batch > static_cast<size_t>(ellm::kDecMaxBatch))
+        return fail(ELLM_ERR_UNSUPPORTED, "decode batch %zu exceeds %d", batch, ellm::kDecMaxBatch);
+    ellm::DecodeParams p;
+    p.q = static_cast<const __nv_bfloat16*>(h->d.q);
+    p.k_cache = static_cast<const __nv_bfloat16*>(h->d.k_cache);
+    p.v_cache = static_cast<const __nv_bfloat16*>(h->d.v_cache);
+    p.part_o = h->part_o;
+    p.part_lse = h->part_lse;
+    p.prefix_out = h->prefix;
+    p.positions = positions;
+    long long len = static_cast<long long>(position_index) + 1;
+    if (len > key_end) len = key_end;
+    p.uniform_len = len;
+    p.len_cap = key_end < static_cast<long long>(h->d.max_seq) ? key_end : static_cast<long long>(h->d.max_seq);
+    p.key_begin = key_begin;
+    p.s0 = h->d.kv_strides[0]; p.s1 = h->d.kv_strides[1]; p.s2 = h->d.kv_strides[2];
+    p.batch = static_cast<int>(batch);
+    p.q_heads = static_cast<int>(h->d.q_heads);
+    p.kv_heads = static_cast<int>(h->d.kv_heads);
+    p.group = h->group;
+    p.gtiles = h->gtiles;
+    p.scale_log2 = h->d.scale * ellm::kLog2e;
+    p.num_ctas = h->dec_ctas;
+    {
+        LaunchScope ls(h, ELLM_KERNEL_DECODE_SPLITKV);
+        ellm::decode_splitkv_kernel<<<h->dec_ctas, ellm::kDecThreads, ellm::kDecSmemBytes, h->stream>>>(p);
+    }
+    ELLM_CUDA(cudaGetLastError());
+    const unsigned blocks = static_cast<unsigned>((batch * h->d.q_heads + 3) / 4);
+    {
+        LaunchScope ls(h, ELLM_KERNEL_MERGE);
+        if (out_f32)
+            ellm::decode_merge_kernel<float><<<blocks, 128, 0, h->stream>>>(p, out_f32, lse_out);
+        else
+            ellm::decode_merge_kernel<__nv_bfloat16><<<blocks, 128, 0, h->stream>>>(
+                p, static_cast<__nv_bfloat16*>(h->d.out), lse_out);
+    }
+    ELLM_CUDA(cudaGetLastError());
+    return ELLM_OK;
+}
+
+int launch_prefill_warp_mma(ellm_attn* h, const int32_t* positions, size_t position_index,
+                            size_t interval, size_t batch, long long key_begin, long long key_end,
+                            float* out_f32, float* lse_out) {
+    ellm::PrefillParams p;
+    p.q = static_cast<const __nv_bfloat16*>(h->d.q);
+    p.k_cache = static_cast<const __nv_bfloat16*>(h->d.k_cache);
+    p.v_cache = static_cast<const __nv_bfloat16*>(h->d.v_cache);
+    p.out = out_f32 ? static_cast<void*>(out_f32) : h->d.out;
+    p.lse = lse_out;
+    p.positions = positions;
+    p.position_index = static_cast<long long>(position_index);
+    p.key_begin = key_begin;
+    p.key_end = key_end < static_cast<long long>(h->d.max_seq) ? key_end : static_cast<long long>(h->d.max_seq);
+    p.s0 = h->d.kv_strides[0]; p.s1 = h->d.kv_strides[1]; p.s2 = h->d.kv_strides[2];
+    p.interval = static_cast<int>(interval);
+    p.batch = static_cast<int>(batch);
+    p.max_batch = static_cast<int>(h->d.max_batch);
+    p.q_heads = static_cast<int>(h->d.q_heads);
+    p.kv_heads = static_cast<int>(h->d.kv_heads);
+    p.group = h->group;
+    p.row_tiles = static_cast<int>((interval * h->group + ellm::kPfRows - 1) / ellm::kPfRows);
+    p.scale_log2 = h->d.scale * ellm::kLog2e;
+    if (batch > 65535 || h->d.kv_heads > 65535)
+        return fail(ELLM_ERR_UNSUPPORTED, "batch / kv_heads exceed the grid limit 65535");
+    dim3 grid(p.row_tiles, p.kv_heads, p.batch);
+    {
+        LaunchScope ls(h, ELLM_KERNEL_PREFILL_WARP_MMA);
+        if (out_f32)
+            ellm::prefill_warp_mma_kernel<float><<<grid, ellm::kPfThreads, ellm::kPfSmemBytes, h->stream>>>(p);
+        else
+            ellm::prefill_warp_mma_kernel<__nv_bfloat16><<<grid, ellm::kPfThreads, ellm::kPfSmemBytes, h->stream>>>(p);
+    }
+    ELLM_CUDA(cudaGetLastError());
+    return ELLM_OK;
+}
+
+int finish(ellm_attn* h) {
+    if (h->d.async) return ELLM_OK;
+    ELLM_CUDA(cudaStreamSynchronize(h->stream));
+    if (h->status_host && *h->status_host != 0) {
+        const int code = *h->status_host;
+        *h->status_host = 0;
+        cudaMemsetAsync(h->status_dev, 0, sizeof(int), h->stream);
+        return fail(ELLM_ERR_DEVICE_TIMEOUT, "a bounded device-side wait ran out (code %d)", code);
+    }
+    return ELLM_OK;
+}
+
+// Common body of run / run_ragged / run_window.
+int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size_t interval,
+             size_t batch, long long key_begin, long long key_end, float* out_f32, float* lse_out,
+             bool append) {
+    if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL");
+    if (interval == 0 || batch == 0) return ELLM_OK;  // nothing to do, as an empty assign() range
+    if (batch > h->d.max_batch) return fail(ELLM_ERR_INVALID_ARG, "batch_size %zu > max_batch %zu", batch, h->d.max_batch);
+    if (interval > h->d.max_interval)
+        return fail(ELLM_ERR_INVALID_ARG, "position_interval %zu > max_interval %zu", interval, h->d.max_interval);
+    if (!positions && position_index + interval > h->d.max_seq)
+        return fail(ELLM_ERR_INVALID_ARG, "position_index %zu + interval %zu exceeds max_seq %zu", position_index, interval, h->d.max_seq);
+    if (key_begin < 0 || key_end < key_begin) return fail(ELLM_ERR_INVALID_ARG, "bad key window");
+    DeviceGuard guard(h->d.device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", h->d.device);
+    std::lock_guard<std::mutex> lock(h->mu);
+    int rc;
+    if (append && h->d.k_new) {
+        rc = launch_append(h, h->stream, h->d.k_cache, h->d.v_cache, h->d.k_new, h->d.v_new, h->d.kv_strides,
+                           h->d.max_batch, h->d.kv_heads, h->d.max_seq, position_index, positions, interval, batch);
+        if (rc) return rc;
+    }
+    if (interval == 1) {
+        rc = launch_decode(h, positions, position_index, batch, key_begin, key_end, out_f32, lse_out);
+    } else {
+        bool use_tc = false;
+        if (!out_f32 && key_begin == 0 && key_end >= static_cast<long long>(h->d.max_seq)) {
+            if (h->d.prefill_kernel == ELLM_PREFILL_TCGEN05) use_tc = true;
+            else if (h->d.prefill_kernel == ELLM_PREFILL_AUTO) use_tc = ellm::tcgen05_prefers(h->tc, interval, h->group);
+        }
+        if (use_tc) {
+            if (!h->tc.ready)
+                return fail(ELLM_ERR_UNSUPPORTED, "tcgen05 prefill unavailable for this handle: %s", h->tc.why);
+            {
+                LaunchScope ls(h, ELLM_KERNEL_PREFILL_TCGEN05);
+                rc = ellm::launch_prefill_tcgen05(h->tc, h->d, positions, position_index, interval, batch, lse_out,
+                                                  h->status_dev, h->stream);
+            }
+            if (rc == ELLM_ERR_UNSUPPORTED) return fail(rc, "tcgen05 prefill: %s", h->tc.why);
+            if (rc) return fail(rc, "tcgen05 prefill launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        } else {
+            rc = launch_prefill_warp_mma(h, positions, position_index, interval, batch, key_begin, key_end, out_f32, lse_out);
+        }
+    }
+    if (rc) return rc;
+    if (h->status_dev && !h->d.async)
+        cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream);
+    return finish(h);
+}
+
+}  // namespace
+
+extern "C" {
+
+int ellm_attn_abi_version(void) { return 1; }
+
+const char* ellm_last_error(void) { return g_err; }
+
+const char* ellm_status_string(int status) {
+    switch (status) {
+        case ELLM_OK: return "ok";
+        case ELLM_ERR_INVALID_ARG: return "invalid argument";
+        case ELLM_ERR_CUDA: return "CUDA error";
+        case ELLM_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+        case ELLM_ERR_UNSUPPORTED: return "unsupported shape";
+        case ELLM_ERR_NO_MEMORY: return "out of memory";
+        default: return "unknown status";
+    }
+}
+
+int ellm_attn_create(const ellm_attn_desc* desc, ellm_attn** out) {
+    if (!out) return fail(ELLM_ERR_INVALID_ARG, "out is NULL");
+    *out = nullptr;
+    int rc = check_desc(desc);
+    if (rc) return rc;
+    int ndev = 0;
+    ELLM_CUDA(cudaGetDeviceCount(&ndev));
+    if (desc->device < 0 || desc->device >= ndev)
+        return fail(ELLM_ERR_INVALID_ARG, "device %d out of range (%d devices)", desc->device, ndev);
+    DeviceGuard guard(desc->device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", desc->device);
+    cudaDeviceProp prop;
+    ELLM_CUDA(cudaGetDeviceProperties(&prop, desc->device));
+    if (prop.major != 10)
+        return fail(ELLM_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", desc->device, prop.major, prop.minor);
+    ellm_attn* h = new (std::nothrow) ellm_attn();
+    if (!h) return fail(ELLM_ERR_NO_MEMORY, "host allocation failed");
+    h->d = *desc;
+    h->stream = static_cast<cudaStream_t>(desc->stream);
+    h->sm_count = prop.multiProcessorCount;
+    h->group = static_cast<int>(desc->q_heads / desc->kv_heads);
+    h->gtiles = (h->group + 15) / 16;
+    h->dec_ctas = 2 * h->sm_count;
+    h->slots = static_cast<size_t>(h->dec_ctas) + desc->max_batch * desc->kv_heads * h->gtiles;
+    auto cleanup = [&](int status) {
+        ellm_attn_destroy(h);
+        return status;
+    };
+    if (cudaMalloc(&h->part_o, h->slots * 16 * ellm::kHeadDim * sizeof(float)) != cudaSuccess ||
+        cudaMalloc(&h->part_lse, h->slots * 16 * sizeof(float)) != cudaSuccess ||
+        cudaMalloc(&h->prefix, (desc->max_batch + 1) * sizeof(int)) != cudaSuccess ||
+        cudaMalloc(&h->positions_dev, desc->max_batch * sizeof(int32_t)) != cudaSuccess ||
+        cudaMalloc(&h->status_dev, sizeof(int)) != cudaSuccess ||
+        cudaMallocHost(&h->status_host, sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        return cleanup(fail(ELLM_ERR_NO_MEMORY, "workspace allocation failed (%zu slots)", h->slots));
+    }
+    *h->status_host = 0;
+    if (cudaMemset(h->status_dev, 0, sizeof(int)) != cudaSuccess) return cleanup(fail(ELLM_ERR_CUDA, "memset failed"));
+    if (cudaFuncSetAttribute(ellm::decode_splitkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kDecSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(ellm::prefill_warp_mma_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kPfSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(ellm::prefill_warp_mma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kPfSmemBytes) != cudaSuccess)
+        return cleanup(fail(ELLM_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(cudaGetLastError())));
+    ellm::tcgen05_plan_init(h->tc, h->d, h->sm_count);  // leaves tc.ready false (with a reason) when it cannot serve this handle
+    if (desc->prefill_kernel == ELLM_PREFILL_TCGEN05 && !h->tc.ready) {
+        fail(ELLM_ERR_UNSUPPORTED, "tcgen05 prefill requested but unavailable: %s", h->tc.why);
+        return cleanup(ELLM_ERR_UNSUPPORTED);
+    }
+    *out = h;
+    return ELLM_OK;
+}
+
+int ellm_attn_destroy(ellm_attn* h) {
+    if (!h) return ELLM_OK;
+    DeviceGuard guard(h->d.device);
+    for (auto& v : h->pending)
+        for (auto& pr : v) {
+            cudaEventDestroy(pr.first);
+            cudaEventDestroy(pr.second);
+        }
+    cudaFree(h->part_o);
+    cudaFree(h->part_lse);
+    cudaFree(h->prefix);
+    cudaFree(h->positions_dev);
+    cudaFree(h->status_dev);
+    if (h->status_host) cudaFreeHost(h->status_host);
+    delete h;
+    return ELLM_OK;
+}
+
+int ellm_attn_run(ellm_attn* h, size_t position_index, size_t position_interval, size_t batch_size,
+                  size_t cpu_num, size_t thread_id) {
+    if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL");
+    if (cpu_num == 0 || thread_id >= cpu_num) return fail(ELLM_ERR_INVALID_ARG, "thread_id %zu outside cpu_num %zu", thread_id, cpu_num);
+    if (thread_id != 0) return ELLM_OK;  // one launch per operator step; the others go straight to the barrier
+    return run_impl(h, nullptr, position_index, position_interval, batch_size, 0, INT64_MAX, nullptr, h->d.lse, true);
+}
+
+int ellm_attn_run_ragged(ellm_attn* h, const int32_t* positions, size_t position_interval,
+                         size_t batch_size, size_t cpu_num, size_t thread_id) {
+    if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL");
+    if (!positions) return fail(ELLM_ERR_INVALID_ARG, "positions is NULL");
+    if (cpu_num == 0 || thread_id >= cpu_num) return fail(ELLM_ERR_INVALID_ARG, "thread_id %zu outside cpu_num %zu", thread_id, cpu_num);
+    if (thread_id != 0) return ELLM_OK;
+    return run_impl(h, positions, 0, position_interval, batch_size, 0, INT64_MAX, nullptr, h->d.lse, true);
+}
+
+int ellm_attn_run_window(ellm_attn* h, size_t position_index, size_t position_interval,
+                         size_t batch_size, size_t key_begin, size_t key_end, float* o_part,
+                         float* lse_part) {
+    if (!o_part || !lse_part) return fail(ELLM_ERR_INVALID_ARG, "o_part and lse_part must be non-NULL");
+    return run_impl(h, nullptr, position_index, position_interval, batch_size, static_cast<long long>(key_begin),
+                    static_cast<long long>(key_end > static_cast<size_t>(INT64_MAX) ? INT64_MAX : key_end), o_part, lse_part, false);
+}
+
+int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host, const void* v_new_host,
+                       void* out_host, float* lse_host, const int32_t* positions_host,
+                       size_t position_index, size_t position_interval, size_t batch_size) {
+    if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL");
+    if (!q_host || !out_host) return fail(ELLM_ERR_INVALID_ARG, "q_host and out_host must be non-NULL");
+    if ((k_new_host || v_new_host) && !h->d.k_new) return fail(ELLM_ERR_INVALID_ARG, "handle has no k_new/v_new device buffers bound");
+    if ((k_new_host == nullptr) != (v_new_host == nullptr)) return fail(ELLM_ERR_INVALID_ARG, "k_new_host and v_new_host must come together");
+    if (lse_host && !h->d.lse) return fail(ELLM_ERR_INVALID_ARG, "handle has no lse device buffer bound");
+    if (batch_size == 0 || position_interval == 0) return ELLM_OK;
+    if (batch_size > h->d.max_batch || position_interval > h->d.max_interval)
+        return fail(ELLM_ERR_INVALID_ARG, "batch_size / position_interval exceed the handle's maxima");
+    DeviceGuard guard(h->d.device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", h->d.device);
+    const size_t D = h->d.head_size;
+    // [interval][max_batch][heads][D]: copy the live batch of every chunk row
+    const size_t q_pitch = h->d.max_batch * h->d.q_heads * D * 2, q_width = batch_size * h->d.q_heads * D * 2;
+    const size_t kv_pitch = h->d.max_batch * h->d.kv_heads * D * 2, kv_width = batch_size * h->d.kv_heads * D * 2;
+    const size_t l_pitch = h->d.max_batch * h->d.q_heads * 4, l_width = batch_size * h->d.q_heads * 4;
+    ELLM_CUDA(cudaMemcpy2DAsync(const_cast<void*>(h->d.q), q_pitch, q_host, q_pitch, q_width, position_interval, cudaMemcpyHostToDevice, h->stream));
+    if (k_new_host) {
+        ELLM_CUDA(cudaMemcpy2DAsync(const_cast<void*>(h->d.k_new), kv_pitch, k_new_host, kv_pitch, kv_width, position_interval, cudaMemcpyHostToDevice, h->stream));
+        ELLM_CUDA(cudaMemcpy2DAsync(const_cast<void*>(h->d.v_new), kv_pitch, v_new_host, kv_pitch, kv_width, position_interval, cudaMemcpyHostToDevice, h->stream));
+    }
+    const int32_t* positions = nullptr;
+    if (positions_host) {
+        ELLM_CUDA(cudaMemcpyAsync(h->positions_dev, positions_host, batch_size * sizeof(int32_t), cudaMemcpyHostToDevice, h->stream));
+        positions = h->positions_dev;
+    }
+    const int was_async = h->d.async;
+    h->d.async = 1;
+    int rc = run_impl(h, positions, position_index, position_interval, batch_size, 0, INT64_MAX, nullptr, h->d.lse, k_new_host != nullptr);
+    h->d.async = was_async;
+    if (rc) return rc;
+    ELLM_CUDA(cudaMemcpy2DAsync(out_host, q_pitch, h->d.out, q_pitch, q_width, position_interval, cudaMemcpyDeviceToHost, h->stream));
+    if (lse_host)
+        ELLM_CUDA(cudaMemcpy2DAsync(lse_host, l_pitch, h->d.lse, l_pitch, l_width, position_interval, cudaMemcpyDeviceToHost, h->stream));
+    ELLM_CUDA(cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
+    ELLM_CUDA(cudaStreamSynchronize(h->stream));
+    if (*h->status_host != 0) {
+        const int code = *h->status_host;
+        *h->status_host = 0;
+        cudaMemsetAsync(h->status_dev, 0, sizeof(int), h->stream);
+        return fail(ELLM_ERR_DEVICE_TIMEOUT, "a bounded device-side wait ran out (code %d)", code);
+    }
+    return ELLM_OK;
+}
+
+int ellm_device_alloc(int device, size_t bytes, void** out) {
+    if (!out) return fail(ELLM_ERR_INVALID_ARG, "out is NULL");
+    *out = nullptr;
+    if (bytes == 0) return fail(ELLM_ERR_INVALID_ARG, "bytes is 0");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) {  // cudaMalloc returns at least 256-byte alignment
+        cudaGetLastError();
+        return fail(ELLM_ERR_NO_MEMORY, "cudaMalloc of %zu bytes failed", bytes);
+    }
+    if (cudaMemset(p, 0, bytes) != cudaSuccess) {
+        cudaFree(p);
+        return fail(ELLM_ERR_CUDA, "cudaMemset failed");
+    }
+    *out = p;
+    return ELLM_OK;
+}
+
+int ellm_device_free(int device, void* ptr) {
+    if (!ptr) return ELLM_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    ELLM_CUDA(cudaFree(ptr));
+    return ELLM_OK;
+}
+
+int ellm_kv_append(void* cache, const void* src, const size_t kv_strides[4], size_t max_batch,
+                   size_t kv_heads, size_t head_size, size_t max_seq, size_t position_index,
+                   const int32_t* positions, size_t position_interval, size_t batch_size, int device,
+                   void* stream) {
+    if (!cache || !src || !kv_strides) return fail(ELLM_ERR_INVALID_ARG, "cache, src and kv_strides must be non-NULL");
+    if (head_size != static_cast<size_t>(ellm::kHeadDim)) return fail(ELLM_ERR_UNSUPPORTED, "head_size %zu: only 128", head_size);
+    if (kv_strides[3] != 1) return fail(ELLM_ERR_UNSUPPORTED, "kv_strides[3] must be 1");
+    for (int i = 0; i < 3; ++i)
+        if (kv_strides[i] % 8 != 0) return fail(ELLM_ERR_INVALID_ARG, "kv_strides[%d] must be a multiple of 8 elements", i);
+    if (!aligned16(cache) || !aligned16(src)) return fail(ELLM_ERR_INVALID_ARG, "cache and src must be 16-byte aligned");
+    if (batch_size > max_batch) return fail(ELLM_ERR_INVALID_ARG, "batch_size %zu > max_batch %zu", batch_size, max_batch);
+    if (!positions && position_index + position_interval > max_seq)
+        return fail(ELLM_ERR_INVALID_ARG, "position_index %zu + interval %zu exceeds max_seq %zu", position_index, position_interval, max_seq);
+    if (position_interval == 0 || batch_size == 0 || kv_heads == 0) return ELLM_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    return launch_append(nullptr, static_cast<cudaStream_t>(stream), cache, nullptr, src, nullptr, kv_strides, max_batch,
+                         kv_heads, max_seq, position_index, positions, position_interval, batch_size);
+}
+
+int ellm_attn_merge_partials(const float* o_parts, const float* lse_parts, size_t parts, size_t rows,
+                             size_t head_size, void* out, float* lse_out, int device, void* stream) {
+    if (!o_parts || !lse_parts || !out) return fail(ELLM_ERR_INVALID_ARG, "o_parts, lse_parts and out must be non-NULL");
+    if (head_size != static_cast<size_t>(ellm::kHeadDim)) return fail(ELLM_ERR_UNSUPPORTED, "head_size %zu: only 128", head_size);
+    if (parts == 0 || parts > 65535) return fail(ELLM_ERR_INVALID_ARG, "parts %zu out of range", parts);
+    if (rows == 0) return ELLM_OK;
+    if (!aligned16(o_parts) || !aligned16(out)) return fail(ELLM_ERR_INVALID_ARG, "o_parts and out must be 16-byte aligned");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    const unsigned blocks = static_cast<unsigned>((rows + 3) / 4);
+    ellm::merge_partials_kernel<__nv_bfloat16><<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        o_parts, lse_parts, static_cast<int>(parts), static_cast<long long>(rows), static_cast<__nv_bfloat16*>(out), lse_out);
+    ELLM_CUDA(cudaGetLastError());
+    return ELLM_OK;
+}
+
+int ellm_attn_set_profiling(ellm_attn* h, int on) {
+    if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL");
+    std::lock_guard<std::mutex> lock(h->mu);
+    h->profiling = on != 0;
+    return ELLM_OK;
+}
+
+int ellm_attn_kernel_stats(ellm_attn* h, int kernel_id, uint64_t* launches, uint64_t* timed_launches,
+                           double* total_ms) {
+    if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL");
+    if (kernel_id < 0 || kernel_id >= ELLM_KERNEL_COUNT) return fail(ELLM_ERR_INVALID_ARG, "kernel_id %d unknown", kernel_id);
+    DeviceGuard guard(h->d.device);
+    std::lock_guard<std::mutex> lock(h->mu);
+    auto& pend = h->pending[kernel_id];
+    if (!pend.empty()) {
+        ELLM_CUDA(cudaStreamSynchronize(h->stream));
+        for (auto& pr : pend) {
+            float ms = 0.0f;
+            if (cudaEventElapsedTime(&ms, pr.first, pr.second) == cudaSuccess) {
+                h->total_ms[kernel_id] += ms;
+                h->timed[kernel_id]++;
+            }
+            cudaEventDestroy(pr.first);
+            cudaEventDestroy(pr.second);
+        }
+        pend.clear();
+    }
+    if (launches) *launches = h->launches[kernel_id];
+    if (timed_launches) *timed_launches = h->timed[kernel_id];
+    if (total_ms) *total_ms = h->total_ms[kernel_id];
+    return ELLM_OK;
+}
+
+}  // extern "C"

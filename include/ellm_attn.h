@@ -1,0 +1,172 @@
+/* C ABI of the B200 attention path for eLLM.
+ *
+ * This library stands in for ONE operator of the reference crate: the attention
+ * node of its static graph.  Every entry point names the reference interface it
+ * replaces (paths relative to the reference project root).  Signatures carry
+ * plain pointers and sizes only.  All data pointers are DEVICE pointers unless a
+ * parameter is named *_host.  Every function returns an ellm_status; nothing
+ * aborts the process (the reference panics instead: Cargo.toml `panic = "abort"`).
+ *
+ * Element type: bf16 in, bf16 out, fp32 accumulation, fp32 log-sum-exp.
+ */
+#ifndef ELLM_ATTN_H
+#define ELLM_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ellm_status {
+    ELLM_OK = 0,
+    ELLM_ERR_INVALID_ARG = 1,   /* null pointer, bad head counts, misaligned base, position past max_seq */
+    ELLM_ERR_CUDA = 2,          /* a CUDA runtime / driver call failed; see ellm_last_error() */
+    ELLM_ERR_DEVICE_TIMEOUT = 3,/* a bounded device-side wait ran out; results of that call are invalid */
+    ELLM_ERR_UNSUPPORTED = 4,   /* shape outside what the kernels implement (e.g. head_size != 128) */
+    ELLM_ERR_NO_MEMORY = 5
+} ellm_status;
+
+typedef enum ellm_dtype { ELLM_DTYPE_BF16 = 0 } ellm_dtype;
+
+/* Which kernel ellm_attn_run picks for a chunk of more than one row. */
+typedef enum ellm_prefill_kernel {
+    ELLM_PREFILL_AUTO = 0,     /* tcgen05 kernel when the chunk is large enough, else the warp-MMA kernel */
+    ELLM_PREFILL_TCGEN05 = 1,
+    ELLM_PREFILL_WARP_MMA = 2
+} ellm_prefill_kernel;
+
+typedef struct ellm_attn ellm_attn;
+
+/* The arguments of Attention::new (src/compiler/mul/attention.rs:41-67) as
+ * Tensor::attention passes them (src/ptensor/tensor.rs:107-139), plus what a
+ * device needs that a CPU does not.
+ *
+ * Layouts (elements, not bytes):
+ *   q, out : [chunk rows, max_batch, q_heads, head_size] row-major - the
+ *            reference addresses both with the MAX batch stride
+ *            (attention.rs:86,118-119).
+ *   k_cache, v_cache : element (b, kvh, pos, c) at
+ *            b*kv_strides[0] + kvh*kv_strides[1] + pos*kv_strides[2] + c*kv_strides[3],
+ *            the stride vector the reference takes from the permuted K tensor
+ *            (src/qwen3_moe/attention.rs:149-166).  kv_strides[3] must be 1;
+ *            the others must be multiples of 8 elements (16 bytes).
+ *   lse    : [chunk rows, max_batch, q_heads] fp32, natural log, softmax scale
+ *            included; may be NULL.  The reference drops it.
+ *   k_new, v_new : [chunk rows, max_batch, kv_heads, head_size]; the chunk's new
+ *            K/V rows which run() first writes into the cache at
+ *            [position_index, position_index+interval) - the reference's
+ *            output_to_kv intent (src/compiler/zip_map/complex_zip.rs:92-98).
+ *            Both NULL = the caller already wrote the cache.
+ * A query head h reads KV head h / (q_heads / kv_heads).
+ */
+typedef struct ellm_attn_desc {
+    const void* q;
+    void* k_cache;
+    void* v_cache;
+    void* out;
+    float* lse;
+    const void* k_new;
+    const void* v_new;
+    size_t max_batch;      /* Attention::new batch_size: the allocated batch */
+    size_t q_heads;        /* attention_head_num */
+    size_t kv_heads;       /* kv_head_num */
+    size_t head_size;      /* 128 */
+    size_t kv_strides[4];
+    size_t max_seq;        /* rows per (sequence, kv head) the cache holds */
+    size_t max_interval;   /* most chunk rows one run() will be given (sizes q/out) */
+    float scale;           /* inverse_sqrt_head */
+    int dtype;             /* ellm_dtype */
+    int device;            /* CUDA device ordinal */
+    void* stream;          /* cudaStream_t the kernels are enqueued on; NULL = legacy default stream */
+    int async;             /* 0: run() returns after the stream has drained (what the
+                              executor's barrier expects, src/serving/start.rs:69-73);
+                              1: run() only enqueues */
+    int prefill_kernel;    /* ellm_prefill_kernel */
+} ellm_attn_desc;
+
+/* Attention::new.  Allocates the handle's split-KV workspace on desc->device. */
+int ellm_attn_create(const ellm_attn_desc* desc, ellm_attn** out);
+int ellm_attn_destroy(ellm_attn* h);
+
+/* Attention::run(position_index, position_interval, batch_size, cpu_num,
+ * thread_id) (src/compiler/mul/attention.rs:69-76; same signature as every
+ * Operator::run, src/compiler/operator.rs:68-75).  Chunk row r of sequence b is
+ * the token at absolute position position_index + r and attends keys
+ * 0..=position_index + r.  The executor calls this from every worker thread;
+ * thread_id 0 launches, every other thread_id returns ELLM_OK at once and the
+ * executor's barrier does the rest. */
+int ellm_attn_run(ellm_attn* h, size_t position_index, size_t position_interval,
+                  size_t batch_size, size_t cpu_num, size_t thread_id);
+
+/* Extension (the reference has one position for the whole batch): sequence b
+ * starts its chunk at positions[b] (device int32[batch_size]). */
+int ellm_attn_run_ragged(ellm_attn* h, const int32_t* positions, size_t position_interval,
+                         size_t batch_size, size_t cpu_num, size_t thread_id);
+
+/* Same step for a caller whose activations live in HOST memory (the reference's
+ * buffers are host allocations, src/memory/allocator.rs:4-27): copies q (and
+ * k_new/v_new, positions when non-NULL) to the handle's bound device buffers,
+ * runs, copies out (and lse) back, and returns when the results are in host
+ * memory.  The KV cache stays resident on the device. */
+int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
+                       const void* v_new_host, void* out_host, float* lse_host,
+                       const int32_t* positions_host, size_t position_index,
+                       size_t position_interval, size_t batch_size);
+
+/* allocate_init (src/memory/allocator.rs:16-27) for device memory: zero-filled,
+ * 256-byte aligned.  Unlike the reference, which never frees, there is a free. */
+int ellm_device_alloc(int device, size_t bytes, void** out);
+int ellm_device_free(int device, void* ptr);
+
+/* The KV-append step alone (complex_zip.rs:92-98 semantics): rows
+ * src[(r*max_batch + b)*kv_heads + kvh][head_size] -> cache row
+ * (b, kvh, position_b + r).  positions NULL = position_index for every b. */
+int ellm_kv_append(void* cache, const void* src, const size_t kv_strides[4], size_t max_batch,
+                   size_t kv_heads, size_t head_size, size_t max_seq, size_t position_index,
+                   const int32_t* positions, size_t position_interval, size_t batch_size,
+                   int device, void* stream);
+
+/* Combine `parts` partial results of the same query rows taken over disjoint key
+ * sets: L = log sum_i exp(L_i), O = sum_i O_i exp(L_i - L).  No counterpart in the
+ * reference (it never splits the key range); it is the exchange step of the
+ * split-KV decode and of sequence-chunk sharding across GPUs.
+ * o_parts [parts, rows, head_size] fp32, lse_parts [parts, rows] fp32,
+ * out [rows, head_size] bf16, lse_out [rows] fp32 (may be NULL). */
+int ellm_attn_merge_partials(const float* o_parts, const float* lse_parts, size_t parts,
+                             size_t rows, size_t head_size, void* out, float* lse_out,
+                             int device, void* stream);
+
+/* Attention over an explicit key window, fp32 partial output: chunk rows attend
+ * keys [key_begin, min(key_end, position+1)) only.  Used by sequence-chunk
+ * sharding, where each GPU holds one contiguous slice of the keys.
+ * o_part [chunk rows, max_batch, q_heads, head_size] fp32, lse_part fp32. */
+int ellm_attn_run_window(ellm_attn* h, size_t position_index, size_t position_interval,
+                         size_t batch_size, size_t key_begin, size_t key_end, float* o_part,
+                         float* lse_part);
+
+/* Counters for the benchmark: kernels launched by this handle since creation, and
+ * per-kernel device time when profiling is on (events around each launch). */
+typedef enum ellm_kernel_id {
+    ELLM_KERNEL_KV_APPEND = 0,
+    ELLM_KERNEL_DECODE_SPLITKV = 1,
+    ELLM_KERNEL_MERGE = 2,
+    ELLM_KERNEL_PREFILL_TCGEN05 = 3,
+    ELLM_KERNEL_PREFILL_WARP_MMA = 4,
+    ELLM_KERNEL_COUNT = 5
+} ellm_kernel_id;
+int ellm_attn_set_profiling(ellm_attn* h, int on);
+/* launches: all launches of that kernel; timed_launches / total_ms: those made while
+ * profiling was on and their summed device time.  Synchronises the stream. */
+int ellm_attn_kernel_stats(ellm_attn* h, int kernel_id, uint64_t* launches,
+                           uint64_t* timed_launches, double* total_ms);
+
+const char* ellm_last_error(void);   /* thread-local text of the last failure */
+const char* ellm_status_string(int status);
+int ellm_attn_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ELLM_ATTN_H */

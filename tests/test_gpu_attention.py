@@ -1,0 +1,193 @@
+"""Parity of the CUDA attention path with the CPU oracle, through the C ABI.
+
+Every test here needs a B200.  Inputs are seeded; cache rows past each
+sequence's end are NaN so that any out-of-range read poisons the output."""
+import numpy as np
+import pytest
+import torch
+
+import ellm_b200
+from ellm_b200 import _lib as L
+from helpers import Case, assert_attention_close, assert_cache_bit_exact, bits
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(case, **gpu_kw):
+    want_k, want_v, want_o, want_l = case.oracle()
+    got_k, got_v, got_o, got_l = case.gpu(**gpu_kw)
+    assert_cache_bit_exact(got_k, got_v, want_k, want_v)
+    return assert_attention_close(case, got_o, got_l, want_o, want_l)
+
+
+def test_reference_kat_all_ones_through_the_abi():
+    # the reference's only attention KAT (generic/flash_attention.rs:119-147) on the GPU:
+    # q = K = V = 1, 8 keys, scale 1 -> O = 1, LSE = 128 + ln 8
+    dev = torch.device("cuda:0")
+    q = torch.ones(1, 1, 1, 128, dtype=torch.bfloat16, device=dev)
+    k = torch.ones(1, 1, 8, 128, dtype=torch.bfloat16, device=dev)
+    v = torch.ones(1, 1, 8, 128, dtype=torch.bfloat16, device=dev)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(1, 1, 1, dtype=torch.float32, device=dev)
+    op = ellm_b200.Attention.new(q, k, v, out, 1, 1, 1, 128, [8 * 128, 8 * 128, 128, 1], 1.0, max_seq=8, lse=lse)
+    op.run(7, 1, 1, 1, 0)
+    assert (out.float() == 1.0).all()
+    assert abs(lse.item() - (128.0 + np.log(8.0))) < 1e-3
+    assert op.kernel_stats()["decode_splitkv"][0] == 1
+
+
+@pytest.mark.parametrize("lens", [[1], [2], [63], [64], [65], [127, 128, 129], [1, 700, 64, 3000]])
+@pytest.mark.parametrize("q_heads,kv_heads", [(8, 1), (4, 4), (32, 4)])
+def test_decode_ragged(lens, q_heads, kv_heads):
+    # sequence b holds lens[b]-1 cached tokens; the new token is appended at lens[b]-1
+    pos = [n - 1 for n in lens]
+    case = Case(seed=100 + len(lens), interval=1, batch=len(lens), q_heads=q_heads, kv_heads=kv_heads,
+                max_seq=max(lens) + 3, positions=pos)
+    _check(case)
+    assert case.last_stats["kv_append"][0] == 1 and case.last_stats["decode_splitkv"][0] == 1
+    assert case.last_stats["merge"][0] == 1
+
+
+def test_decode_uniform_position_and_dead_batch_slots():
+    case = Case(seed=7, interval=1, batch=3, max_batch=5, q_heads=16, kv_heads=2, max_seq=300, position_index=257)
+    _check(case, cpu_num=4)  # all four thread ids call run; exactly one launches
+    assert case.last_stats["decode_splitkv"][0] == 1
+
+
+def test_decode_wide_group_uses_two_head_tiles():
+    case = Case(seed=8, interval=1, batch=2, q_heads=24, kv_heads=1, max_seq=200, positions=[150, 31])
+    _check(case)
+
+
+def test_decode_long_contexts_many_pieces():
+    # enough tiles that every CTA gets a piece and sequences span several CTAs
+    case = Case(seed=9, interval=1, batch=4, q_heads=32, kv_heads=4, max_seq=8192,
+                positions=[8000, 1023, 4097, 6000], poison=True)
+    _check(case)
+
+
+@pytest.mark.parametrize("interval,position_index", [(2, 0), (63, 0), (64, 0), (65, 0), (127, 0), (129, 0), (17, 40), (64, 64)])
+@pytest.mark.parametrize("q_heads,kv_heads", [(4, 4), (8, 1), (6, 2)])
+def test_prefill_warp_mma_shapes(interval, position_index, q_heads, kv_heads):
+    case = Case(seed=200 + interval, interval=interval, batch=2, q_heads=q_heads, kv_heads=kv_heads,
+                max_seq=position_index + interval + 5, position_index=position_index)
+    _check(case, prefill_kernel=L.PREFILL_WARP_MMA)
+    assert case.last_stats["prefill_warp_mma"][0] == 1
+
+
+def test_prefill_ragged_positions():
+    case = Case(seed=21, interval=33, batch=3, q_heads=8, kv_heads=2, max_seq=200, positions=[0, 100, 37])
+    _check(case, prefill_kernel=L.PREFILL_WARP_MMA)
+
+
+def test_chunked_prefill_equals_one_shot():
+    """position_index > 0: prefill in chunks of 48 gives the same rows as one pass of 144."""
+    dev = torch.device("cuda:0")
+    S, Hq, Hkv, chunk = 144, 8, 2, 48
+    full = Case(seed=33, interval=S, batch=1, q_heads=Hq, kv_heads=Hkv, max_seq=S, position_index=0, poison=False)
+    _, _, want_o, want_l = full.oracle()
+    strides = full.strides
+    ck = torch.full((1, Hkv, S, 128), float("nan"), dtype=torch.bfloat16, device=dev)
+    cv = torch.full_like(ck, float("nan"))
+    q = torch.zeros(chunk, 1, Hq, 128, dtype=torch.bfloat16, device=dev)
+    kn = torch.zeros(chunk, 1, Hkv, 128, dtype=torch.bfloat16, device=dev)
+    vn = torch.zeros_like(kn)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(chunk, 1, Hq, dtype=torch.float32, device=dev)
+    op = ellm_b200.Attention.new(q, ck, cv, out, 1, Hq, Hkv, 128, strides, full.scale, max_seq=S,
+                                 max_interval=chunk, lse=lse, k_new=kn, v_new=vn, prefill_kernel=L.PREFILL_WARP_MMA)
+    got_o, got_l = [], []
+    for p0 in range(0, S, chunk):
+        q.copy_(full.q[p0:p0 + chunk]); kn.copy_(full.k_new[p0:p0 + chunk]); vn.copy_(full.v_new[p0:p0 + chunk])
+        op.run(p0, chunk, 1, 1, 0)
+        got_o.append(bits(out).copy()); got_l.append(lse.cpu().numpy().copy())
+    assert_attention_close(full, np.concatenate(got_o), np.concatenate(got_l), want_o, want_l)
+    assert np.array_equal(bits(ck).reshape(Hkv, S, 128), bits(full.k_new).reshape(S, Hkv, 128).transpose(1, 0, 2))
+
+
+def test_run_host_copies_in_and_out():
+    case = Case(seed=40, interval=1, batch=3, q_heads=8, kv_heads=2, max_seq=500, positions=[499, 10, 255])
+    _check(case, use_run_host=True)
+    case = Case(seed=41, interval=20, batch=2, max_batch=3, q_heads=8, kv_heads=2, max_seq=64, position_index=5)
+    _check(case, use_run_host=True, prefill_kernel=L.PREFILL_WARP_MMA)
+
+
+def test_kv_append_standalone_bit_exact_with_canaries():
+    dev = torch.device("cuda:0")
+    case = Case(seed=50, interval=3, batch=2, max_batch=4, q_heads=2, kv_heads=2, max_seq=16, positions=[0, 13], poison=False)
+    want_k, _, _, _ = case.oracle()
+    ck = case.cache_k.to(dev)
+    ellm_b200.kv_append(ck, case.k_new.to(dev), case.strides, 4, 2, 128, 16, 0, 3, 2,
+                        positions=torch.tensor([0, 13], dtype=torch.int32, device=dev))
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(ck), want_k)
+
+
+def test_merge_partials_against_oracle():
+    import oracle
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(60)
+    parts, rows = 5, 37
+    o = torch.randn(parts, rows, 128, generator=g)
+    l = torch.randn(parts, rows, generator=g) * 3
+    l[2, 5] = float("-inf")   # a part that saw no key
+    l[:, 9] = float("-inf")   # a row no part saw
+    want_o, want_l = oracle.merge_partials(o.numpy(), l.numpy())
+    out = torch.zeros(rows, 128, dtype=torch.bfloat16, device=dev)
+    lse = torch.zeros(rows, dtype=torch.float32, device=dev)
+    ellm_b200.merge_partials(o.to(dev), l.to(dev), out, lse)
+    torch.cuda.synchronize()
+    keep = np.ones(rows, bool); keep[9] = False
+    assert np.abs(out.float().cpu().numpy()[keep] - want_o[keep]).max() < 2e-2
+    assert np.abs(lse.cpu().numpy()[keep] - want_l[keep]).max() < 1e-4
+    assert (out[9] == 0).all() and lse[9].item() == float("-inf")
+
+
+def test_split_window_partials_merge_to_the_full_result():
+    """Key windows [0,a), [a,b), [b,inf) merged == unsplit: decode and prefill."""
+    dev = torch.device("cuda:0")
+    for interval, pos in ((1, 700), (40, 300)):
+        case = Case(seed=70 + interval, interval=interval, batch=2, q_heads=8, kv_heads=2, max_seq=pos + interval,
+                    position_index=pos, poison=False)
+        want_k, want_v, want_o, want_l = case.oracle()
+        q = case.q.to(dev)
+        ck, cv = from_bits_dev(want_k, case, dev), from_bits_dev(want_v, case, dev)
+        out = torch.zeros_like(q)
+        op = ellm_b200.Attention.new(q, ck, cv, out, 2, 8, 2, 128, case.strides, case.scale, max_seq=case.max_seq,
+                                     max_interval=interval, prefill_kernel=L.PREFILL_WARP_MMA)
+        windows = [(0, 100), (100, 333), (333, 1 << 40)]
+        po = torch.zeros(len(windows), interval, 2, 8, 128, dtype=torch.float32, device=dev)
+        pl = torch.zeros(len(windows), interval, 2, 8, dtype=torch.float32, device=dev)
+        for i, (a, b) in enumerate(windows):
+            op.run_window(pos, interval, 2, a, b, po[i], pl[i])
+        rows = interval * 2 * 8
+        lse = torch.zeros(rows, dtype=torch.float32, device=dev)
+        ellm_b200.merge_partials(po.view(len(windows), rows, 128), pl.view(len(windows), rows), out, lse)
+        torch.cuda.synchronize()
+        assert_attention_close(case, bits(out), lse.view(interval, 2, 8).cpu().numpy(), want_o, want_l)
+
+
+def from_bits_dev(a, case, dev):
+    from helpers import from_bits
+    return from_bits(a).view(case.max_batch, case.kv_heads, case.max_seq, 128).to(dev)
+
+
+def test_error_paths_on_a_live_handle():
+    dev = torch.device("cuda:0")
+    q = torch.zeros(1, 2, 4, 128, dtype=torch.bfloat16, device=dev)
+    k = torch.zeros(2, 2, 16, 128, dtype=torch.bfloat16, device=dev)
+    out = torch.zeros_like(q)
+    op = ellm_b200.Attention.new(q, k, k.clone(), out, 2, 4, 2, 128, [2 * 16 * 128, 16 * 128, 128, 1], 0.1, max_seq=16)
+    with pytest.raises(ellm_b200.EllmError) as e:
+        op.run(16, 1, 1, 1, 0)          # position past max_seq
+    assert e.value.status == L.ERR_INVALID_ARG
+    with pytest.raises(ellm_b200.EllmError):
+        op.run(0, 1, 3, 1, 0)           # batch > max_batch
+    with pytest.raises(ellm_b200.EllmError):
+        op.run(0, 2, 1, 1, 0)           # interval > max_interval
+    with pytest.raises(ellm_b200.EllmError):
+        op.run(0, 1, 1, 2, 2)           # thread_id outside cpu_num
+    op.run(3, 1, 2, 8, 5)               # a non-zero thread id is a no-op
+    assert op.kernel_stats()["decode_splitkv"][0] == 0
+    op.run(3, 1, 2, 8, 0)
+    assert op.kernel_stats()["decode_splitkv"][0] == 1

@@ -1,0 +1,149 @@
+"""The oracle against every known-answer test the reference holds for the attention
+path, and against an independent float64 softmax.  CPU only."""
+import numpy as np
+import pytest
+
+import oracle
+from helpers import Case
+
+
+def test_dot_product_kat(oracle_lib):
+    # src/kernel/generic/flash_attention.rs:96-101
+    a = np.array([1, 2, 3], np.float32)
+    b = np.array([4, 5, 6], np.float32)
+    assert oracle_lib.oracle_dot_product_f32(a.ctypes.data, b.ctypes.data, 3) == 32.0
+
+
+def test_scalar_vector_mul_and_acc_kat(oracle_lib):
+    # src/kernel/generic/flash_attention.rs:103-116
+    o = np.ones(128, np.float32)
+    v = np.full(128, 2.0, np.float32)
+    oracle_lib.oracle_scalar_vector_mul_acc_f32(1.0, o.ctypes.data, 2.0, v.ctypes.data, 128)
+    assert np.abs(o - 5.0).max() < 1e-6
+
+
+@pytest.mark.parametrize("defect", [False, True])
+def test_flash_attention_all_ones_kat(defect):
+    # src/kernel/generic/flash_attention.rs:119-147: scale 1.0 hides the scale defect
+    q = np.ones(128, np.float32)
+    K = np.ones((8, 128), np.float32)
+    V = np.ones((8, 128), np.float32)
+    o = np.ones(128, np.float32)
+    lse = oracle.flash_attention_f32(q, K, V, o, 1.0, 7, faithful_scale_defect=defect)
+    assert np.abs(o - 1.0).max() < 1e-6
+    assert abs(lse - (128.0 + np.log(8.0))) < 1e-4
+
+
+def test_assign_kats():
+    # src/compiler/assign.rs:141-190
+    assert [oracle.assign(10, 3, i) for i in range(3)] == [(0, 4), (4, 7), (7, 10)]
+    assert [oracle.assign(11, 3, i) for i in range(3)] == [(0, 4), (4, 8), (8, 11)]
+    assert [oracle.assign(12, 3, i) for i in range(3)] == [(0, 4), (4, 8), (8, 12)]
+    assert oracle.assign(5, 8, 5) is None
+    assert oracle.assign(5, 8, 4) == (4, 5)
+
+
+def _f16_bits(x):
+    return np.asarray(x, np.float16).view(np.uint16)
+
+
+def test_f16_kernel_kats(oracle_lib):
+    if not oracle_lib.oracle_f16_available():
+        pytest.skip("CPU without avx512fp16 (the reference skips the same way)")
+    from oracle.binding import aligned_empty
+    # src/kernel/x86_64/f16_512/dot_product.rs:49-57
+    a = aligned_empty((128,), np.uint16); a[:] = _f16_bits(np.ones(128))
+    b = aligned_empty((128,), np.uint16); b[:] = a
+    assert oracle_lib.oracle_f16_dot_product(a.ctypes.data, b.ctypes.data, 128) == 128.0
+    # src/kernel/x86_64/f16_512/flash_attention.rs:100-133
+    o = aligned_empty((128,), np.uint16); o[:] = _f16_bits(np.ones(128))
+    v = aligned_empty((128,), np.uint16); v[:] = _f16_bits(np.full(128, 2.0))
+    oracle_lib.oracle_f16_scalar_vector_mul_acc(1.0, o.ctypes.data, 2.0, v.ctypes.data)
+    assert (o.view(np.float16) == 5.0).all()
+    # src/kernel/x86_64/f16_512/flash_attention.rs:135-157
+    q = aligned_empty((128,), np.uint16); q[:] = _f16_bits(np.ones(128))
+    K = aligned_empty((8, 128), np.uint16); K[:] = _f16_bits(np.ones((8, 128)))
+    V = aligned_empty((8, 128), np.uint16); V[:] = K
+    o[:] = 0
+    oracle_lib.oracle_f16_flash_attention(q.ctypes.data, K.ctypes.data, V.ctypes.data, o.ctypes.data, 1.0, 128, 128, 7)
+    assert np.abs(o.view(np.float16).astype(np.float32) - 1.0).max() < 1e-6
+
+
+def test_scale_defect_is_visible_with_real_scale():
+    # generic/flash_attention.rs:76 uses the unscaled score; with scale 1/sqrt(128) that
+    # departs from softmax, while the corrected oracle matches float64 softmax.
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal(128).astype(np.float32)
+    K = rng.standard_normal((64, 128)).astype(np.float32)
+    V = rng.standard_normal((64, 128)).astype(np.float32)
+    scale = 1.0 / np.sqrt(128.0)
+    want, want_lse = oracle.softmax_attention_f64(q, K, V, scale)
+    good = np.zeros(128, np.float32)
+    lse = oracle.flash_attention_f32(q, K, V, good, scale, 63)
+    assert np.abs(good - want).max() < 1e-5
+    assert abs(lse - want_lse) < 1e-5
+    bad = np.zeros(128, np.float32)
+    oracle.flash_attention_f32(q, K, V, bad, scale, 63, faithful_scale_defect=True)
+    assert np.abs(bad - want).max() > 1e-2
+
+
+@pytest.mark.parametrize("q_heads,kv_heads", [(4, 4), (8, 2), (8, 1)])
+def test_operator_walk_matches_float64_softmax(q_heads, kv_heads):
+    """Index walk, causal limit, GQA map and LSE of the operator-level oracle."""
+    case = Case(seed=11, interval=5, batch=2, q_heads=q_heads, kv_heads=kv_heads, max_seq=40,
+                position_index=17, max_batch=3)
+    ck, cv, out, lse = case.oracle(threads=3)
+    kf = oracle.bf16_bits_to_f32(ck).reshape(case.max_batch, kv_heads, case.max_seq, 128)
+    vf = oracle.bf16_bits_to_f32(cv).reshape(case.max_batch, kv_heads, case.max_seq, 128)
+    qf = case.q.float().numpy()
+    of = oracle.bf16_bits_to_f32(out)
+    g = q_heads // kv_heads
+    for h in range(case.interval):
+        for b in range(case.batch):
+            for qh in range(q_heads):
+                n = 17 + h + 1
+                want, want_lse = oracle.softmax_attention_f64(qf[h, b, qh], kf[b, qh // g, :n], vf[b, qh // g, :n], case.scale)
+                assert np.abs(of[h, b, qh] - want).max() < 8e-3  # bf16 rounding of O
+                assert abs(lse[h, b, qh] - want_lse) < 1e-5
+    # the dead batch slot (b = 2) is never touched
+    assert (out[:, 2] == 0).all()
+
+
+def test_serial_thread_ids_equal_threads():
+    # the reference's test idiom (for tid in 0..n: run(.., n, tid)) gives the same result
+    case = Case(seed=5, interval=3, batch=2, q_heads=4, kv_heads=2, max_seq=16, position_index=2)
+    ck, cv, out_t, lse_t = case.oracle(threads=4)
+    out_s, lse_s = oracle.attention_bf16(
+        __import__("helpers").bits(case.q), ck, cv, case.strides, 4, 2, case.scale, 2, 3, 2,
+        max_batch=2, serial_thread_ids=5)
+    assert np.array_equal(out_t, out_s) and np.array_equal(lse_t, lse_s)
+
+
+def test_kv_append_rows_and_canaries():
+    case = Case(seed=3, interval=2, batch=2, q_heads=2, kv_heads=2, max_seq=8, positions=[1, 5], max_batch=3)
+    before = __import__("helpers").bits(case.cache_k).copy()
+    ck, _, _, _ = case.oracle()
+    ck4 = ck.reshape(3, 2, 8, 128)
+    b4 = before.reshape(3, 2, 8, 128)
+    new = __import__("helpers").bits(case.k_new)
+    for b, base in ((0, 1), (1, 5)):
+        for h in range(2):
+            assert np.array_equal(ck4[b, :, base + h], new[h, b])
+    touched = np.zeros((3, 2, 8), bool)
+    touched[0, :, 1:3] = True
+    touched[1, :, 5:7] = True
+    assert np.array_equal(ck4[~touched], b4[~touched])
+
+
+def test_merge_partials_equals_unsplit():
+    rng = np.random.default_rng(1)
+    q = rng.standard_normal(128).astype(np.float32)
+    K = rng.standard_normal((96, 128)).astype(np.float32)
+    V = rng.standard_normal((96, 128)).astype(np.float32)
+    full, full_lse = oracle.softmax_attention_f64(q, K, V, 0.1)
+    parts_o, parts_l = [], []
+    for lo, hi in ((0, 10), (10, 64), (64, 96)):
+        o, l = oracle.softmax_attention_f64(q, K[lo:hi], V[lo:hi], 0.1)
+        parts_o.append(o[None]); parts_l.append([l])
+    o, l = oracle.merge_partials(np.stack(parts_o), np.array(parts_l))
+    assert np.abs(o[0] - full).max() < 1e-5 and abs(l[0] - full_lse) < 1e-5
