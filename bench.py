@@ -1,0 +1,378 @@
+#!/usr/bin/env python
+"""Benchmark of the attention path: batched decode over the static KV cache.
+
+Workload (N=1): 32 query / 4 KV heads, head_dim 128, bf16, 16 sequences with
+context lengths uniform in [1024, 32768] (seed 1), cache [16, 4, 32768, 128] for K
+and for V pre-filled N(0,1); one step = append one new token per sequence at
+position len_b and attend over len_b + 1 keys (KV append, split-KV decode, merge).
+The metric is the HBM rate of that step: algorithmic bytes / time, where the
+algorithmic bytes are 2 (K,V) * kv_heads * 128 * 2 B * sum(len_b + 1) plus Q, O, LSE
+and the appended rows.  Every step reads ~0.55 GB, far more than the 126 MB L2.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+With N > 1 (under torchrun) every rank runs the same workload on its own 16
+sequences (independent sequences, no data-path collective): weak scaling.
+`--impl reference` times the CPU restatement of the reference's AVX-512-FP16
+attention kernel on all host cores instead (rank 0 only).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HQ, HKV, D, BATCH, MAX_SEQ = 32, 4, 128, 16, 32768
+SCALE = 1.0 / np.sqrt(D)
+
+
+def workload_lens():
+    g = torch.Generator().manual_seed(1)
+    return torch.randint(1024, 32769, (BATCH,), generator=g).to(torch.int32)
+
+
+def algorithmic_bytes(lens):
+    keys = int((lens.to(torch.int64) + 1).sum())
+    kv = 2 * HKV * D * 2 * keys
+    qo = 2 * BATCH * HQ * D * 2
+    append = 2 * BATCH * HKV * D * 2
+    lse = BATCH * HQ * 4
+    return kv + qo + append + lse, kv + qo // 2  # (whole step, decode kernel alone: K/V + Q)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (no MEASURED_PEAKS.json)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_reference_leg(lens, steps, warmup, budget_s=20.0):
+    """The reference's AVX-512-FP16 kernel (restated in oracle/) on all host cores, over the
+    same 16 sequences.  Returns (GB/s, cores, sample text, ms per step) or None."""
+    import oracle
+    from oracle.binding import aligned_empty
+    lib = oracle.load()
+    cores = os.cpu_count() or 1
+    if not lib.oracle_f16_available():
+        return None
+    g = torch.Generator().manual_seed(1234)
+    strides = [HKV * MAX_SEQ * D, MAX_SEQ * D, D, 1]
+    k = aligned_empty((BATCH, HKV, MAX_SEQ, D), np.uint16)
+    v = aligned_empty((BATCH, HKV, MAX_SEQ, D), np.uint16)
+    for b in range(BATCH):  # only the rows a sequence reads need values
+        n = int(lens[b]) + 1
+        k[b, :, :n] = torch.randn(HKV, n, D, generator=g).to(torch.float16).view(torch.int16).numpy().view(np.uint16)
+        v[b, :, :n] = torch.randn(HKV, n, D, generator=g).to(torch.float16).view(torch.int16).numpy().view(np.uint16)
+    q = aligned_empty((1, BATCH, HQ, D), np.uint16)
+    q[:] = torch.randn(1, BATCH, HQ, D, generator=g).to(torch.float16).view(torch.int16).numpy().view(np.uint16)
+    pos = lens.numpy().astype(np.int32)
+    total, _ = algorithmic_bytes(lens)
+    for _ in range(max(1, warmup)):
+        _, secs = oracle.attention_f16_timed(q, k, v, strides, HQ, HKV, SCALE, 0, 1, BATCH, BATCH, positions=pos, threads=cores)
+    reps = max(1, min(steps, int(budget_s / max(secs, 1e-3))))
+    _, secs = oracle.attention_f16_timed(q, k, v, strides, HQ, HKV, SCALE, 0, 1, BATCH, BATCH, positions=pos, threads=cores, repeats=reps)
+    per = secs / reps
+    sample = (f"full workload (16 sequences, sum(len+1)={int((lens.to(torch.int64) + 1).sum())} keys, 32 query heads), "
+              f"{reps} passes, AVX-512-FP16 kernel, one pinned thread per core + spin barrier")
+    return total / per / 1e9, cores, sample, per * 1e3, reps
+
+
+def cpu_info():
+    model, flags = "", set()
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("model name") and not model:
+                    model = line.split(":", 1)[1].strip()
+                if line.startswith("flags") and not flags:
+                    flags = set(line.split(":", 1)[1].split())
+    except OSError:
+        pass
+    return {"model": model, "avx512_fp16": "avx512_fp16" in flags, "amx_bf16": "amx_bf16" in flags,
+            "amx_used": False}
+
+
+def run_reference(args, lens):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    leg = cpu_reference_leg(lens, args.steps, args.warmup)
+    if leg is None:
+        print(json.dumps({"impl": "reference", "unavailable": "host CPU lacks avx512_fp16, which the reference's attention kernel requires"}))
+        return
+    gbs, cores, sample, ms, reps = leg
+    line = {
+        "impl": "reference", "metric": "decode attn HBM GB/s", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": reps, "warmup": max(1, args.warmup), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": config_dict(lens),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample, **cpu_info()},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def config_dict(lens):
+    return {"workload": "batched decode attention over the static KV cache (BASELINE configs[1]): 16 sequences, "
+                        "32 q / 4 kv heads, head_dim 128, bf16, context lengths U[1024,32768] seed 1, max_seq 32768",
+            "batch": BATCH, "q_heads": HQ, "kv_heads": HKV, "head_dim": D, "max_seq": MAX_SEQ,
+            "sum_len_plus_1": int((lens.to(torch.int64) + 1).sum()),
+            "l2": "inputs larger than L2 (each step streams ~0.55 GB of K/V)",
+            "per_rank": "every rank runs this workload on its own 16 sequences"}
+
+
+def prefill_extra(dev, stream_ptr, steps, warmup):
+    """Secondary figure: causal prefill of BASELINE configs[0] (seq 2048, 32/32 heads)."""
+    from ellm_b200 import Attention
+    S, H = 2048, 32
+    g = torch.Generator(device=dev).manual_seed(0)
+    q = torch.randn(S, 1, H, D, device=dev, generator=g).to(torch.bfloat16)
+    kn = torch.randn(S, 1, H, D, device=dev, generator=g).to(torch.bfloat16)
+    vn = torch.randn(S, 1, H, D, device=dev, generator=g).to(torch.bfloat16)
+    ck = torch.zeros(1, H, 4096, D, dtype=torch.bfloat16, device=dev)
+    cv = torch.zeros_like(ck)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(S, 1, H, dtype=torch.float32, device=dev)
+    op = Attention.new(q, ck, cv, out, 1, H, H, D, [H * 4096 * D, 4096 * D, D, 1], SCALE, max_seq=4096,
+                       max_interval=S, lse=lse, k_new=kn, v_new=vn, device=dev.index, stream=stream_ptr, async_=True)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(max(3, warmup)):
+        op.run(0, S, 1, 1, 0)
+    torch.cuda.synchronize(dev)
+    times = []
+    for _ in range(max(5, min(steps, 20))):
+        flush.zero_()  # write a buffer larger than L2 between timed iterations
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); op.run(0, S, 1, 1, 0); e1.record()
+        torch.cuda.synchronize(dev)
+        times.append(e0.elapsed_time(e1))
+    ms = statistics.median(times)
+    flops = 4 * D * H * S * (S + 1) / 2
+    stats = op.kernel_stats()
+    kernel = "prefill_tcgen05" if stats["prefill_tcgen05"][0] else "prefill_warp_mma"
+    op.close()
+    return {"workload": "causal prefill, seq 2048, 32/32 heads (BASELINE configs[0]), KV append included, L2 flushed between iterations",
+            "ttft_ms": ms, "tflops": flops / ms / 1e9, "kernel": kernel}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    lens = workload_lens()
+
+    if args.impl == "reference":
+        run_reference(args, lens)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU fallback")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    from ellm_b200 import Attention, StaticKVCache
+
+    stream = torch.cuda.current_stream(dev)
+    cache = StaticKVCache(1, BATCH, HKV, MAX_SEQ, D, device=dev)
+    g = torch.Generator(device=dev).manual_seed(1 + 1000 * rank)
+    for t in (cache.k, cache.v):
+        for b in range(BATCH):
+            t[0, b].copy_(torch.randn(HKV, MAX_SEQ, D, device=dev, generator=g))
+    q = torch.randn(1, BATCH, HQ, D, device=dev, generator=g).to(torch.bfloat16)
+    k_new = torch.randn(1, BATCH, HKV, D, device=dev, generator=g).to(torch.bfloat16)
+    v_new = torch.randn(1, BATCH, HKV, D, device=dev, generator=g).to(torch.bfloat16)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(1, BATCH, HQ, dtype=torch.float32, device=dev)
+    positions = lens.to(dev)
+    op = Attention.new(q, cache.k[0], cache.v[0], out, BATCH, HQ, HKV, D, cache.strides, SCALE,
+                       max_seq=MAX_SEQ, max_interval=1, lse=lse, k_new=k_new, v_new=v_new,
+                       device=local, stream=stream.cuda_stream, async_=True)
+    total_bytes, kernel_bytes = algorithmic_bytes(lens)
+
+    def step():
+        op.run_ragged(positions, 1, BATCH, 1, 0)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(args.warmup):
+        step()
+    before = op.kernel_stats()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    ms = timed(step, args.steps)
+    after = op.kernel_stats()
+    # keep the device under the same load a little longer so that the clock sampler sees it
+    t_end = time.time() + 1.0
+    while rank == 0 and time.time() < t_end and len(sampler.rows) < 5:
+        for _ in range(50):
+            step()
+        torch.cuda.synchronize(dev)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = sum(after[k][0] - before[k][0] for k in after) if rank == 0 else 0
+    ms_per_step = ms / args.steps
+    value = world * total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # dominant kernel alone: CUDA events around each split-KV decode launch
+    op.set_profiling(True)
+    p0 = op.kernel_stats()["decode_splitkv"]
+    timed(step, args.steps)
+    p1 = op.kernel_stats()["decode_splitkv"]
+    op.set_profiling(False)
+    k_ms = (p1[2] - p0[2]) / max(1, p1[1] - p0[1])
+    peak, peak_src = measured_peaks()
+    achieved = kernel_bytes / (k_ms * 1e-3) / 1e9
+
+    # end to end: host buffers in, host result out, through the host-buffer entry point
+    qh = q.cpu().pin_memory(); knh = k_new.cpu().pin_memory(); vnh = v_new.cpu().pin_memory()
+    oh = torch.zeros_like(qh).pin_memory()
+    lh = torch.zeros(1, BATCH, HQ, dtype=torch.float32).pin_memory()
+    ph = lens.clone().pin_memory()
+
+    def step_host():
+        op.run_host(qh, oh, 0, 1, BATCH, k_new_host=knh, v_new_host=vnh, lse_host=lh, positions_host=ph)
+
+    for _ in range(args.warmup):
+        step_host()
+    ms_e2e = timed(step_host, args.steps) / args.steps
+    e2e = world * total_bytes / (ms_e2e * 1e-3) / 1e9
+    h2d = qh.numel() * 2 + knh.numel() * 2 + vnh.numel() * 2 + ph.numel() * 4
+    d2h = oh.numel() * 2 + lh.numel() * 4 + 4  # + the kernel status word
+    if not torch.isfinite(oh.float()).all():
+        raise SystemExit("bench: non-finite attention output")
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    line = {
+        "metric": "decode attn HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": config_dict(lens),
+        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e, "entry": "ellm_attn_run_host"},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "decode_splitkv_kernel", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
+                     "frac_of_nominal_8tbs": achieved / 8000.0, "kernel_ms": k_ms,
+                     "algorithmic_bytes_per_launch": kernel_bytes, "traffic": TRAFFIC_BYTES_PER_LAUNCH},
+        "tpot_attn_ms": ms_per_step,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        leg = cpu_reference_leg(lens, 20, 1, budget_s=15.0)
+        if leg:
+            line["cpu_baseline"] = {"value": leg[0], "unit": "GB/s", "cores": leg[1], "kind": "port",
+                                    "sample": leg[2], "ms_per_step": leg[3], **cpu_info()}
+        else:
+            line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+                                    "sample": "not run: host CPU lacks avx512_fp16", **cpu_info()}
+    if world == 1 and not args.no_extra:
+        line["extra"] = {"prefill": prefill_extra(dev, stream.cuda_stream, args.steps, args.warmup)}
+    print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_splitkv_kernel launch on this
+# workload, from the ncu capture summarised under profiles/; None until captured.
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+if __name__ == "__main__":
+    main()
