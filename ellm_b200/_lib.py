@@ -13,6 +13,7 @@ OK, ERR_INVALID_ARG, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_UNSUPPORTED, ERR_NO_MEMOR
 DTYPE_BF16 = 0
 PREFILL_AUTO, PREFILL_TCGEN05, PREFILL_WARP_MMA = 0, 1, 2
 KERNEL_KV_APPEND, KERNEL_DECODE_SPLITKV, KERNEL_MERGE, KERNEL_PREFILL_TCGEN05, KERNEL_PREFILL_WARP_MMA = range(5)
+NOALLOC_MAX_SLOTS, NOALLOC_MAX_BATCH = 1024, 1024
 KERNEL_NAMES = ["kv_append", "decode_splitkv", "merge", "prefill_tcgen05", "prefill_warp_mma"]
 
 
@@ -47,6 +48,7 @@ _SIGNATURES = {
     "ellm_kv_append": (_I, [_VP, _VP, C.POINTER(_SZ), _SZ, _SZ, _SZ, _SZ, _SZ, _VP, _SZ, _SZ, _I, _VP]),
     "ellm_attn_merge_partials": (_I, [_VP, _VP, _SZ, _SZ, _SZ, _VP, _VP, _I, _VP]),
     "ellm_attn_run_window": (_I, [_VP, _SZ, _SZ, _SZ, _SZ, _SZ, _VP, _VP]),
+    "ellm_attn_decode_noalloc": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _SZ, _SZ, _SZ, _SZ, _SZ, C.POINTER(_SZ), _SZ, C.c_float, _I, _VP]),
     "ellm_attn_set_profiling": (_I, [_VP, _I]),
     "ellm_attn_kernel_stats": (_I, [_VP, _I, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
     "ellm_last_error": (C.c_char_p, []),

@@ -108,3 +108,21 @@ def merge_partials(o_parts, lse_parts, out, lse_out=None, device=0, stream=None)
     parts, rows, d = o_parts.shape
     L.check(L.load().ellm_attn_merge_partials(_ptr(o_parts), _ptr(lse_parts), parts, rows, d,
                                               _ptr(out), _ptr(lse_out), device, stream))
+
+
+def decode_noalloc(q, k_cache, v_cache, out, batch_size, q_heads, kv_heads, head_size, kv_strides,
+                   scale, *, max_seq, positions=None, position_index=0, lse=None, device=0,
+                   stream=None):
+    """One decode step without any device allocation (ellm_attn_decode_noalloc).
+
+    For callers that may not allocate at run time - a serving loop whose memory was all
+    planned and handed out up front, or a process in which another allocator already owns
+    the GPU's memory.  The split-KV partials go to a fixed array inside the library, shared
+    by every call on the device, so calls must not overlap on the GPU; sizes beyond the
+    array (see NOALLOC_MAX_SLOTS / NOALLOC_MAX_BATCH) raise EllmError(ERR_UNSUPPORTED).
+    The new token's K/V must already be in the cache.  Only enqueues; no synchronise.
+    """
+    L.check(L.load().ellm_attn_decode_noalloc(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(lse), _ptr(positions), position_index,
+        batch_size, q_heads, kv_heads, head_size, (C.c_size_t * 4)(*[int(s) for s in kv_strides]),
+        max_seq, float(scale), device, stream))

@@ -558,3 +558,122 @@ int ellm_attn_kernel_stats(ellm_attn* h, int kernel_id, uint64_t* launches, uint
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free decode entry point.
+//
+// For callers that must not (or cannot) obtain device memory while serving: all
+// memory was handed out when the graph was planned, or another allocator in the
+// process already owns the whole HBM.  The split-KV partials live in the fixed
+// array below instead of a handle's cudaMalloc'd workspace.  Every GPU that loads
+// this library holds the array until the process exits.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kNoAllocPartOBytes = static_cast<size_t>(ELLM_NOALLOC_MAX_SLOTS) * 16 * ellm::kHeadDim * sizeof(float);
+constexpr size_t kNoAllocPartLseBytes = static_cast<size_t>(ELLM_NOALLOC_MAX_SLOTS) * 16 * sizeof(float);
+constexpr size_t kNoAllocPrefixBytes = ((static_cast<size_t>(ELLM_NOALLOC_MAX_BATCH) + 1) * sizeof(int) + 255) / 256 * 256;
+constexpr size_t kNoAllocBytes = kNoAllocPartOBytes + kNoAllocPartLseBytes + kNoAllocPrefixBytes;
+static_assert(ELLM_NOALLOC_MAX_BATCH <= ellm::kDecMaxBatch, "the decode kernel's prefix table bounds the batch");
+
+// In host code this name is only a stand-in for the symbol, never a device address:
+// the address each device uses is looked up with cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+struct NoAllocDevice {
+    unsigned char* scratch = nullptr;  // device address of g_noalloc_scratch on this device
+    int sm_count = 0;
+    bool ready = false;
+};
+NoAllocDevice g_noalloc_dev[kNoAllocMaxDevices];
+std::mutex g_noalloc_mu;
+
+// Once per device, with that device current.
+int noalloc_setup(int device, NoAllocDevice** out) {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    NoAllocDevice& nd = g_noalloc_dev[device];
+    if (!nd.ready) {
+        void* ptr = nullptr;
+        ELLM_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        if (!ptr) return fail(ELLM_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        ELLM_CUDA(cudaDeviceGetAttribute(&nd.sm_count, cudaDevAttrMultiProcessorCount, device));
+        int major = 0;
+        ELLM_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+        if (major != 10) return fail(ELLM_ERR_UNSUPPORTED, "device %d is not sm_100", device);
+        ELLM_CUDA(cudaFuncSetAttribute(ellm::decode_splitkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kDecSmemBytes));
+        nd.scratch = static_cast<unsigned char*>(ptr);
+        nd.ready = true;
+    }
+    *out = &nd;
+    return ELLM_OK;
+}
+
+}  // namespace
+
+extern "C" int ellm_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                        float* lse, const int32_t* positions, size_t position_index,
+                                        size_t batch_size, size_t q_heads, size_t kv_heads, size_t head_size,
+                                        const size_t kv_strides[4], size_t max_seq, float scale, int device,
+                                        void* stream) {
+    if (!q || !k_cache || !v_cache || !out || !kv_strides)
+        return fail(ELLM_ERR_INVALID_ARG, "q, k_cache, v_cache, out and kv_strides must be non-NULL");
+    if (head_size != static_cast<size_t>(ellm::kHeadDim)) return fail(ELLM_ERR_UNSUPPORTED, "head_size %zu: only 128", head_size);
+    if (q_heads == 0 || kv_heads == 0 || q_heads % kv_heads != 0)
+        return fail(ELLM_ERR_INVALID_ARG, "q_heads %zu must be a non-zero multiple of kv_heads %zu", q_heads, kv_heads);
+    if (kv_strides[3] != 1) return fail(ELLM_ERR_UNSUPPORTED, "kv_strides[3] must be 1");
+    for (int i = 0; i < 3; ++i)
+        if (kv_strides[i] == 0 || kv_strides[i] % 8 != 0)
+            return fail(ELLM_ERR_INVALID_ARG, "kv_strides[%d] must be a non-zero multiple of 8 elements", i);
+    if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out))
+        return fail(ELLM_ERR_INVALID_ARG, "device buffers must be 16-byte aligned");
+    if (!(scale > 0.0f) || !std::isfinite(scale)) return fail(ELLM_ERR_INVALID_ARG, "scale must be finite and > 0");
+    if (max_seq == 0) return fail(ELLM_ERR_INVALID_ARG, "max_seq must be > 0");
+    if (!positions && position_index + 1 > max_seq)
+        return fail(ELLM_ERR_INVALID_ARG, "position_index %zu is past max_seq %zu", position_index, max_seq);
+    if (device < 0 || device >= kNoAllocMaxDevices) return fail(ELLM_ERR_INVALID_ARG, "device %d out of range", device);
+    if (batch_size == 0) return ELLM_OK;
+    if (batch_size > static_cast<size_t>(ELLM_NOALLOC_MAX_BATCH))
+        return fail(ELLM_ERR_UNSUPPORTED, "batch_size %zu exceeds ELLM_NOALLOC_MAX_BATCH %d of the allocation-free entry point",
+                    batch_size, ELLM_NOALLOC_MAX_BATCH);
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    NoAllocDevice* nd = nullptr;
+    int rc = noalloc_setup(device, &nd);
+    if (rc) return rc;
+    const int group = static_cast<int>(q_heads / kv_heads), gtiles = (group + 15) / 16;
+    const int num_ctas = 2 * nd->sm_count;
+    const size_t slots = static_cast<size_t>(num_ctas) + batch_size * kv_heads * gtiles;
+    if (slots > static_cast<size_t>(ELLM_NOALLOC_MAX_SLOTS))
+        return fail(ELLM_ERR_UNSUPPORTED,
+                    "allocation-free decode needs %zu partial slots (2*%d SMs + batch %zu * kv_heads %zu * head tiles %d) "
+                    "but its fixed scratch holds ELLM_NOALLOC_MAX_SLOTS = %d; use a handle (ellm_attn_create) for this size",
+                    slots, nd->sm_count, batch_size, kv_heads, gtiles, ELLM_NOALLOC_MAX_SLOTS);
+    ellm::DecodeParams p;
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+    p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+    p.part_o = reinterpret_cast<float*>(nd->scratch);
+    p.part_lse = reinterpret_cast<float*>(nd->scratch + kNoAllocPartOBytes);
+    p.prefix_out = reinterpret_cast<int*>(nd->scratch + kNoAllocPartOBytes + kNoAllocPartLseBytes);
+    p.positions = positions;
+    p.uniform_len = static_cast<long long>(position_index) + 1;
+    p.len_cap = static_cast<long long>(max_seq);
+    p.key_begin = 0;
+    p.s0 = kv_strides[0]; p.s1 = kv_strides[1]; p.s2 = kv_strides[2];
+    p.batch = static_cast<int>(batch_size);
+    p.q_heads = static_cast<int>(q_heads);
+    p.kv_heads = static_cast<int>(kv_heads);
+    p.group = group;
+    p.gtiles = gtiles;
+    p.scale_log2 = scale * ellm::kLog2e;
+    p.num_ctas = num_ctas;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    ellm::decode_splitkv_kernel<<<num_ctas, ellm::kDecThreads, ellm::kDecSmemBytes, s>>>(p);
+    ELLM_CUDA(cudaGetLastError());
+    const unsigned blocks = static_cast<unsigned>((batch_size * q_heads + 3) / 4);
+    ellm::decode_merge_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(p, static_cast<__nv_bfloat16*>(out), lse);
+    ELLM_CUDA(cudaGetLastError());
+    return ELLM_OK;
+}
+

@@ -162,6 +162,47 @@ int ellm_attn_set_profiling(ellm_attn* h, int on);
 int ellm_attn_kernel_stats(ellm_attn* h, int kernel_id, uint64_t* launches,
                            uint64_t* timed_launches, double* total_ms);
 
+/* Decode step (one query row per sequence, split-KV + merge) that allocates nothing.
+ *
+ * It has no counterpart in the reference; it exists for callers that cannot obtain
+ * device memory at run time.  eLLM plans every buffer while the graph is built and
+ * gives all memory out there, and a serving process often shares its GPU with a
+ * framework whose caching allocator already holds the whole HBM: in both cases
+ * cudaMalloc inside the step loop either is forbidden or simply fails, so
+ * ellm_attn_create (which allocates a workspace per handle) is not an option.
+ *
+ * Instead of a handle's workspace this entry point keeps the split-KV partials in
+ * one fixed array that is part of the library image (a file-scope __device__ array,
+ * about 8.1 MB, held by every GPU that loads the library until the process exits).
+ * The caller passes every input and output; no handle is involved and the call makes
+ * no cudaMalloc / cudaFree and uses no allocating library routine.
+ *
+ * Limit: batch_size * kv_heads * ceil((q_heads / kv_heads) / 16) + 2 * (SMs of the
+ * device) must not exceed ELLM_NOALLOC_MAX_SLOTS, and batch_size must not exceed
+ * ELLM_NOALLOC_MAX_BATCH; larger requests return ELLM_ERR_UNSUPPORTED and touch
+ * nothing.  (On a 148-SM B200: batch_size * kv_heads * head tiles <= 728.)
+ *
+ * The first call on a device looks the array's device address up and sets the
+ * kernel's shared-memory attribute for that device; make that first call before any
+ * stream capture begins.  All calls on one device share the array, and it keeps
+ * whatever the previous call left in it.  Nothing in it has to start at zero - each
+ * call writes every slot before reading it - so sequential calls on one stream are
+ * independent of one another, but two calls whose kernels overlap on the GPU (two
+ * streams, two host threads) race on the array: serialise them.
+ *
+ * Arguments as in ellm_attn_desc / ellm_attn_run_ragged: q, out [max-batch rows >=
+ * batch_size, q_heads, head_size] bf16; lse [batch_size, q_heads] fp32 or NULL;
+ * positions device int32[batch_size] or NULL (then position_index for all); sequence
+ * b attends keys 0..=position_b, which must already be in the cache.  Enqueues on
+ * `stream` and returns without waiting. */
+#define ELLM_NOALLOC_MAX_SLOTS 1024
+#define ELLM_NOALLOC_MAX_BATCH 1024
+int ellm_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                             float* lse, const int32_t* positions, size_t position_index,
+                             size_t batch_size, size_t q_heads, size_t kv_heads, size_t head_size,
+                             const size_t kv_strides[4], size_t max_seq, float scale, int device,
+                             void* stream);
+
 const char* ellm_last_error(void);   /* thread-local text of the last failure */
 const char* ellm_status_string(int status);
 int ellm_attn_abi_version(void);
