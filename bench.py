@@ -371,8 +371,8 @@ def main():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_splitkv_kernel launch on this
-# workload, from the ncu capture summarised under profiles/; None until captured.
-TRAFFIC_BYTES_PER_LAUNCH = None
+# workload, from the ncu capture summarised in profiles/decode_splitkv_bench_workload.md.
+TRAFFIC_BYTES_PER_LAUNCH = 613.95e6
 
 if __name__ == "__main__":
     main()
