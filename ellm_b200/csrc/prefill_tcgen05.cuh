@@ -1,20 +1,571 @@
-// K1 (fast form): causal grouped-query flash-attention prefill on tcgen05 / TMEM / TMA.
+// K1 (fast form): causal grouped-query flash-attention prefill on the Blackwell
+// tensor cores: tcgen05.mma with accumulators in tensor memory, operands staged in
+// shared memory by TMA (no cluster, no multicast), online softmax in fp32.
+//
+// Replaces, for chunks of many rows, the item walk of the reference's
+// Attention::run (src/compiler/mul/attention.rs:85-153) and the per-row key loop
+// it calls (src/kernel/generic/flash_attention.rs:60-89): chunk row r of sequence
+// b is the token at position base + r and attends keys 0..=base + r.
+//
+// One CTA owns 256 packed rows of one (sequence, KV head): packed row rho = r*G + g
+// (g = query head inside its group, fastest), split in two tiles of 128 rows, so
+// the G query heads of a group share every K/V tile - the reference's "one KV
+// head at a time" locality.  Warp roles:
+//   warps 0-3  softmax / correction / epilogue of tile 0 (thread = one row)
+//   warps 4-7  the same for tile 1
+//   warp  8    TMA producer (one lane): Q tiles once, then K_j, V_j through a ring
+//   warp  9    MMA issuer (one lane) and owner of the tensor-memory allocation
+// Per 128-key tile j and row tile t:  S_t = Q_t K_j^T (tensor memory) -> softmax
+// threads read S_t, write P_t (bf16) to shared memory and, when the running max
+// moved by more than 2^8, rescale O_t in tensor memory -> O_t += P_t V_j.
+// The two row tiles alternate on the tensor core, so one tile's softmax overlaps
+// the other's MMAs.
+//
+// Every wait is bounded (about two seconds): when one runs out the kernel sets a
+// status word, all roles leave their loops, tensor memory is released and the
+// kernel returns; the host turns the status into ELLM_ERR_DEVICE_TIMEOUT.
 #pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
 #include "../../include/ellm_attn.h"
 #include "common.cuh"
 
 namespace ellm {
 
+constexpr int kTcTileRows = 128;   // rows per tile = tensor-memory lanes
+constexpr int kTcTiles = 2;        // row tiles per CTA
+constexpr int kTcKeys = 128;       // keys per K/V tile
+constexpr int kTcStages = 3;       // ring slots, each holds one K or one V tile
+constexpr int kTcTileBytes = kTcKeys * kRowBytes;          // 32 KB: two 16 KB halves of 128 rows x 128 B
+constexpr int kTcHalfBytes = kTcTileBytes / 2;
+constexpr int kTcThreads = (kTcTiles * 4 + 2) * 32;        // 320
+constexpr int kTcSmemQ = 0;
+constexpr int kTcSmemP = kTcSmemQ + kTcTiles * kTcTileBytes;
+constexpr int kTcSmemRing = kTcSmemP + kTcTiles * kTcTileBytes;
+constexpr int kTcSmemBar = kTcSmemRing + kTcStages * kTcTileBytes;
+constexpr int kTcSmemBytes = kTcSmemBar + 256 + 1024;       // barriers + slack to align the base to 1024
+constexpr float kTcRescaleThreshold = 8.0f;                 // log2 units
+
 struct Tcgen05Plan {
     bool ready = false;
-    char why[160] = "not built yet";
+    char why[160] = "";
+    void* encode = nullptr;  // cuTensorMapEncodeTiled, fetched from the driver at run time
+    int sm_count = 0;
 };
 
-inline void tcgen05_plan_init(Tcgen05Plan&, const ellm_attn_desc&, int) {}
-inline bool tcgen05_prefers(const Tcgen05Plan&, size_t, int) { return false; }
-inline int launch_prefill_tcgen05(Tcgen05Plan&, const ellm_attn_desc&, const int32_t*, size_t, size_t, size_t,
-                                  float*, int*, cudaStream_t) {
-    return ELLM_ERR_UNSUPPORTED;
+struct TcParams {
+    __nv_bfloat16* out;
+    float* lse;
+    int* status;            // device word: non-zero = a bounded wait ran out
+    long long base;         // position of chunk row 0
+    int interval, batch, max_batch;
+    int q_heads, kv_heads, group;
+    int pair_tiles;         // CTAs along x = ceil(interval * group / 256)
+    float scale_log2;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait.  Returns false when the CTA has been told to give up (abort word set by
+// any thread) or when this wait itself ran out, in which case it sets both words.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_word, int* status,
+                                            int code) {
+    const unsigned long long t0 = global_timer_ns();
+    for (;;) {
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_word) return false;
+        if (global_timer_ns() - t0 > 2000000000ull) {
+            *abort_word = code;
+            atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_word, int* status,
+                                          int code) {
+    for (int i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_word, status, code);
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                            int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                            int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle: rows of 128 bytes, 8-row groups
+// `sbo` bytes apart, 64-element column blocks `lbo` bytes apart (used by MN-major operands).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>((lbo >> 4) & 0x3fffu) << 16;
+    d |= static_cast<uint64_t>((sbo >> 4) & 0x3fffu) << 32;
+    d |= 1ull << 46;   // descriptor version of this architecture
+    d |= 2ull << 61;   // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: bf16 x bf16 -> fp32, M = 128, N = 128; b_mn_major selects a B
+// operand whose N dimension is contiguous in shared memory.
+__host__ __device__ constexpr uint32_t umma_idesc(bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((128u >> 3) << 17) |
+           ((128u >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 consecutive fp32 columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Status codes written by a wait that ran out (which wait gave up).
+enum { kTcWaitQ = 1, kTcWaitKvFull = 2, kTcWaitKvEmpty = 3, kTcWaitSFull = 4, kTcWaitPFull = 5, kTcWaitPvDone = 6 };
+
+// Key tiles row tile t of this CTA needs (0 when the tile has no valid row).
+__device__ __forceinline__ int tc_tile_steps(const TcParams& p, int rho0, int total_rows) {
+    if (rho0 >= total_rows) return 0;
+    const int rho_last = min(rho0 + kTcTileRows, total_rows) - 1;
+    const long long kend = p.base + rho_last / p.group + 1;
+    return static_cast<int>((kend + kTcKeys - 1) / kTcKeys);
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // barriers (8 bytes each) and two words behind them
+    const uint32_t bar0 = smem_base + kTcSmemBar;
+    auto bar_q = [&](int t) { return bar0 + 8u * t; };
+    auto bar_kv_full = [&](int s) { return bar0 + 8u * (2 + s); };
+    auto bar_kv_empty = [&](int s) { return bar0 + 8u * (2 + kTcStages + s); };
+    auto bar_s_full = [&](int t) { return bar0 + 8u * (2 + 2 * kTcStages + t); };
+    auto bar_p_full = [&](int t) { return bar0 + 8u * (4 + 2 * kTcStages + t); };
+    auto bar_pv_done = [&](int t) { return bar0 + 8u * (6 + 2 * kTcStages + t); };
+    constexpr int kNumBars = 8 + 2 * kTcStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kTcSmemBar + 8 * kNumBars);
+    volatile int* abort_word = reinterpret_cast<volatile int*>(smem + kTcSmemBar + 8 * kNumBars + 8);
+
+    const int pair = p.pair_tiles - 1 - static_cast<int>(blockIdx.x);  // heaviest row tiles first
+    const int kvh = blockIdx.y, b = blockIdx.z;
+    const int total_rows = p.interval * p.group;
+    int steps[kTcTiles];
+#pragma unroll
+    for (int t = 0; t < kTcTiles; ++t) steps[t] = tc_tile_steps(p, (pair * kTcTiles + t) * kTcTileRows, total_rows);
+    const int nsteps = max(steps[0], steps[1]);
+
+    if (threadIdx.x == 0) {
+        for (int t = 0; t < kTcTiles; ++t) {
+            mbar_init(bar_q(t), 1);
+            mbar_init(bar_s_full(t), 1);
+            mbar_init(bar_p_full(t), kTcTileRows);
+            mbar_init(bar_pv_done(t), 1);
+        }
+        for (int s = 0; s < kTcStages; ++s) {
+            mbar_init(bar_kv_full(s), 1);
+            mbar_init(bar_kv_empty(s), 1);
+        }
+        *abort_word = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kTcTiles * 4 + 1) {  // the MMA warp owns tensor memory: all 512 columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    // columns: S_0 [0,128), S_1 [128,256), O_0 [256,384), O_1 [384,512)
+
+    if (warp < kTcTiles * 4) {
+        // =============================== softmax / correction / epilogue ===============================
+        const int t = warp >> 2;
+        const int row = (warp & 3) * 32 + lane;                 // row of the tile = tensor-memory lane
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t tS = tmem + lane_base + t * 128;
+        const uint32_t tO = tmem + lane_base + 256 + t * 128;
+        const int rho = (pair * kTcTiles + t) * kTcTileRows + row;
+        const bool valid = rho < total_rows;
+        const int pos = valid ? rho / p.group : 0, g = valid ? rho % p.group : 0;
+        const long long lim = valid ? p.base + pos : -1;        // last key this row may see
+        const long long tile_min_lim = p.base + ((pair * kTcTiles + t) * kTcTileRows) / p.group;
+        unsigned char* p_row = smem + kTcSmemP + t * kTcTileBytes + row * 128;
+        const int my_steps = steps[t];
+        float m_used = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < my_steps && ok; ++j) {
+            ok = mbar_wait(bar_s_full(t), j & 1, abort_word, p.status, kTcWaitSFull);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            float s[128];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
+            tmem_wait_ld();
+            const long long key0 = static_cast<long long>(j) * kTcKeys;
+            if (key0 + kTcKeys - 1 > tile_min_lim) {  // the causal edge crosses this tile
+                const long long d = lim - key0;                // last column this row may see
+                const int rel = d < 0 ? -1 : (d > 127 ? 127 : static_cast<int>(d));
+#pragma unroll
+                for (int c = 0; c < 128; ++c) s[c] = (c <= rel) ? s[c] : -INFINITY;
+            }
+            float mx = s[0];
+#pragma unroll
+            for (int c = 1; c < 128; ++c) mx = fmaxf(mx, s[c]);
+            const float m_new = fmaxf(m_used, mx * p.scale_log2);
+            // rescale O only when the maximum moved far enough to matter; otherwise keep
+            // exponentiating against the stale maximum (O and l stay consistent with it)
+            const bool need = (m_new - m_used > kTcRescaleThreshold) || (m_used == -INFINITY && m_new != -INFINITY);
+            const bool rescale = __any_sync(0xffffffffu, need);
+            float corr = 1.0f;
+            if (rescale) {
+                corr = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
+                m_used = m_new;
+            }
+            const float msub = (m_used == -INFINITY) ? 0.0f : m_used;
+            float sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 128; ++c) {
+                s[c] = fast_exp2(fmaf(s[c], p.scale_log2, -msub));
+                sum += s[c];
+            }
+            l = l * corr + sum;
+            if (j > 0) {  // P_t and O_t are in use until PV(t, j-1) has completed
+                ok = mbar_wait(bar_pv_done(t), (j - 1) & 1, abort_word, p.status, kTcWaitPvDone);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+            }
+            // P row -> shared memory, K-major 128-byte-swizzled: 16-byte chunk c8 of the row sits
+            // in half (c8 >> 3) at chunk position (c8 & 7) ^ (row & 7)
+#pragma unroll
+            for (int c8 = 0; c8 < 16; ++c8) {
+                uint4 v;
+                v.x = pack_bf16(s[c8 * 8 + 0], s[c8 * 8 + 1]);
+                v.y = pack_bf16(s[c8 * 8 + 2], s[c8 * 8 + 3]);
+                v.z = pack_bf16(s[c8 * 8 + 4], s[c8 * 8 + 5]);
+                v.w = pack_bf16(s[c8 * 8 + 6], s[c8 * 8 + 7]);
+                *reinterpret_cast<uint4*>(p_row + (c8 >> 3) * kTcHalfBytes + (((c8 & 7) ^ (row & 7)) << 4)) = v;
+            }
+            if (rescale && j > 0) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float o[32];
+                    tmem_ld32(tO + c * 32, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] *= corr;
+                    tmem_st32(tO + c * 32, o);
+                }
+                tmem_wait_st();
+            }
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(bar_p_full(t));
+        }
+        if (ok && my_steps > 0) {
+            ok = mbar_wait(bar_pv_done(t), (my_steps - 1) & 1, abort_word, p.status, kTcWaitPvDone);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok && my_steps > 0) {
+            tc_fence_after();
+            const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
+            const long long row_index = (static_cast<long long>(pos) * p.max_batch + b) * p.q_heads + kvh * p.group + g;
+            __nv_bfloat16* orow = p.out + row_index * kHeadDim;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float o[32];
+                tmem_ld32(tO + c * 32, o);
+                tmem_wait_ld();
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 v;
+                        v.x = pack_bf16(o[i * 8 + 0] * inv, o[i * 8 + 1] * inv);
+                        v.y = pack_bf16(o[i * 8 + 2] * inv, o[i * 8 + 3] * inv);
+                        v.z = pack_bf16(o[i * 8 + 4] * inv, o[i * 8 + 5] * inv);
+                        v.w = pack_bf16(o[i * 8 + 6] * inv, o[i * 8 + 7] * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = v;
+                    }
+                }
+            }
+            if (valid && p.lse) p.lse[row_index] = (m_used + log2f(l)) * kLn2;
+            tc_fence_before();
+        }
+    } else if (warp == kTcTiles * 4) {
+        // =============================== TMA producer ===============================
+        if (lane == 0) {
+            bool ok = true;
+            for (int t = 0; t < kTcTiles; ++t) {
+                if (steps[t] == 0) continue;
+                const int rho0 = (pair * kTcTiles + t) * kTcTileRows;
+                mbar_arrive_expect_tx(bar_q(t), kTcTileBytes);
+                for (int h = 0; h < 2; ++h)
+                    tma_load_5d(smem_base + kTcSmemQ + t * kTcTileBytes + h * kTcHalfBytes, &map_q, bar_q(t), h * 64, 0,
+                                rho0 / p.group, kvh, b);
+            }
+            for (int item = 0; item < 2 * nsteps && ok; ++item) {  // K_0, V_0, K_1, V_1, ...
+                const int slot = item % kTcStages, round = item / kTcStages;
+                ok = mbar_wait(bar_kv_empty(slot), (round & 1) ^ 1, abort_word, p.status, kTcWaitKvEmpty);
+                if (!ok) break;
+                const CUtensorMap* map = (item & 1) ? &map_v : &map_k;
+                const int key0 = (item >> 1) * kTcKeys;
+                mbar_arrive_expect_tx(bar_kv_full(slot), kTcTileBytes);
+                for (int h = 0; h < 2; ++h)
+                    tma_load_4d(smem_base + kTcSmemRing + slot * kTcTileBytes + h * kTcHalfBytes, map, bar_kv_full(slot),
+                                h * 64, key0, kvh, b);
+            }
+        }
+    } else {
+        // =============================== MMA issuer ===============================
+        if (lane == 0) {
+            bool ok = true;
+            constexpr uint32_t idesc_qk = umma_idesc(false), idesc_pv = umma_idesc(true);
+            auto issue_qk = [&](int t, int slot) {  // S_t = Q_t K^T: 8 steps of 16 over head_dim
+                const uint32_t q_addr = smem_base + kTcSmemQ + t * kTcTileBytes;
+                const uint32_t k_addr = smem_base + kTcSmemRing + slot * kTcTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t off = (ks >> 2) * kTcHalfBytes + (ks & 3) * 32;
+                    umma_bf16(tmem + t * 128, umma_desc(q_addr + off, 0, 1024), umma_desc(k_addr + off, 0, 1024), idesc_qk,
+                              ks > 0);
+                }
+                umma_commit(bar_s_full(t));
+            };
+            auto issue_pv = [&](int t, int slot, bool first) {  // O_t += P_t V: 8 steps of 16 keys
+                const uint32_t p_addr = smem_base + kTcSmemP + t * kTcTileBytes;
+                const uint32_t v_addr = smem_base + kTcSmemRing + slot * kTcTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t a_off = (ks >> 2) * kTcHalfBytes + (ks & 3) * 32;
+                    const uint32_t b_off = ks * 16 * 128;  // 16 key rows of 128 bytes
+                    umma_bf16(tmem + 256 + t * 128, umma_desc(p_addr + a_off, 0, 1024),
+                              umma_desc(v_addr + b_off, kTcHalfBytes, 1024), idesc_pv, !(first && ks == 0));
+                }
+                umma_commit(bar_pv_done(t));
+            };
+            for (int t = 0; t < kTcTiles && ok; ++t)
+                if (steps[t] > 0) ok = mbar_wait(bar_q(t), 0, abort_word, p.status, kTcWaitQ);
+            if (ok && nsteps > 0) {
+                ok = mbar_wait(bar_kv_full(0), 0, abort_word, p.status, kTcWaitKvFull);
+                if (ok) {
+                    tc_fence_after();
+                    for (int t = 0; t < kTcTiles; ++t)
+                        if (steps[t] > 0) issue_qk(t, 0);
+                    umma_commit(bar_kv_empty(0));
+                }
+            }
+            for (int j = 0; j < nsteps && ok; ++j) {
+                const int item_v = 2 * j + 1, slot_v = item_v % kTcStages;
+                const int item_k = 2 * j + 2, slot_k = item_k % kTcStages;
+                bool have_v = false, have_k = false;
+                for (int t = 0; t < kTcTiles && ok; ++t) {
+                    if (j >= steps[t]) continue;
+                    ok = mbar_wait(bar_p_full(t), j & 1, abort_word, p.status, kTcWaitPFull);
+                    if (!ok) break;
+                    if (!have_v) {
+                        ok = mbar_wait(bar_kv_full(slot_v), (item_v / kTcStages) & 1, abort_word, p.status, kTcWaitKvFull);
+                        if (!ok) break;
+                        have_v = true;
+                    }
+                    tc_fence_after();
+                    issue_pv(t, slot_v, j == 0);
+                    if (j + 1 < steps[t]) {
+                        if (!have_k) {
+                            ok = mbar_wait(bar_kv_full(slot_k), (item_k / kTcStages) & 1, abort_word, p.status, kTcWaitKvFull);
+                            if (!ok) break;
+                            have_k = true;
+                            tc_fence_after();
+                        }
+                        issue_qk(t, slot_k);
+                    }
+                }
+                if (!ok) break;
+                umma_commit(bar_kv_empty(slot_v));                      // V_j free once every MMA so far is done
+                if (j + 1 < nsteps) umma_commit(bar_kv_empty(slot_k));  // and K_{j+1}
+            }
+        }
+        __syncwarp();
+    }
+
+    // teardown: every role gets here (all waits are bounded)
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kTcTiles * 4 + 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline void tcgen05_plan_init(Tcgen05Plan& plan, const ellm_attn_desc& d, int sm_count) {
+    plan.ready = false;
+    plan.sm_count = sm_count;
+    const size_t group = d.q_heads / d.kv_heads;
+    if (group > 128 || (128 % group) != 0) {
+        snprintf(plan.why, sizeof(plan.why), "query heads per KV head (%zu) must divide 128", group);
+        return;
+    }
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
+        qres != cudaDriverEntryPointSuccess) {
+        cudaGetLastError();
+        snprintf(plan.why, sizeof(plan.why), "driver does not export cuTensorMapEncodeTiled");
+        return;
+    }
+    if (cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) != cudaSuccess) {
+        snprintf(plan.why, sizeof(plan.why), "cannot reserve %d bytes of shared memory: %s", kTcSmemBytes,
+                 cudaGetErrorString(cudaGetLastError()));
+        return;
+    }
+    plan.encode = fn;
+    plan.ready = true;
+}
+
+// AUTO picks this kernel when the chunk fills at least one 256-row CTA.
+inline bool tcgen05_prefers(const Tcgen05Plan& plan, size_t interval, int group) {
+    return plan.ready && interval * static_cast<size_t>(group) >= 256;
+}
+
+// Uniform chunk start only (positions == nullptr): the K/V tensor maps are bounded at
+// position_index + interval so that TMA zero-fills rows the chunk must not read.
+inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, const int32_t* positions,
+                                  size_t position_index, size_t interval, size_t batch, float* lse, int* status,
+                                  cudaStream_t stream) {
+    if (!plan.ready) return ELLM_ERR_UNSUPPORTED;
+    if (positions) {
+        snprintf(plan.why, sizeof(plan.why), "ragged positions are served by the warp-MMA kernel");
+        return ELLM_ERR_UNSUPPORTED;
+    }
+    const int group = static_cast<int>(d.q_heads / d.kv_heads);
+    EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(plan.encode);
+    CUtensorMap map_q, map_k, map_v;
+    {
+        // q viewed as [head_dim, g, chunk row, kv head, sequence]; a box is 64 x G x (128/G) packed rows
+        cuuint64_t dims[5] = {128, static_cast<cuuint64_t>(group), interval, d.kv_heads, d.max_batch};
+        cuuint64_t strides[4] = {256, d.max_batch * d.q_heads * 256, static_cast<cuuint64_t>(group) * 256, d.q_heads * 256};
+        cuuint32_t box[5] = {64, static_cast<cuuint32_t>(group), static_cast<cuuint32_t>(128 / group), 1, 1};
+        cuuint32_t es[5] = {1, 1, 1, 1, 1};
+        if (encode(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(d.q), dims, strides, box, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            snprintf(plan.why, sizeof(plan.why), "cuTensorMapEncodeTiled(q) failed");
+            return ELLM_ERR_UNSUPPORTED;
+        }
+    }
+    for (int which = 0; which < 2; ++which) {
+        cuuint64_t dims[4] = {128, position_index + interval, d.kv_heads, batch};
+        cuuint64_t strides[3] = {d.kv_strides[2] * 2, d.kv_strides[1] * 2, d.kv_strides[0] * 2};
+        cuuint32_t box[4] = {64, 128, 1, 1};
+        cuuint32_t es[4] = {1, 1, 1, 1};
+        if (encode(which ? &map_v : &map_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, which ? d.v_cache : d.k_cache, dims,
+                   strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            snprintf(plan.why, sizeof(plan.why), "cuTensorMapEncodeTiled(k/v) failed");
+            return ELLM_ERR_UNSUPPORTED;
+        }
+    }
+    TcParams p;
+    p.out = static_cast<__nv_bfloat16*>(d.out);
+    p.lse = lse;
+    p.status = status;
+    p.base = static_cast<long long>(position_index);
+    p.interval = static_cast<int>(interval);
+    p.batch = static_cast<int>(batch);
+    p.max_batch = static_cast<int>(d.max_batch);
+    p.q_heads = static_cast<int>(d.q_heads);
+    p.kv_heads = static_cast<int>(d.kv_heads);
+    p.group = group;
+    p.pair_tiles = static_cast<int>((interval * group + kTcTiles * kTcTileRows - 1) / (kTcTiles * kTcTileRows));
+    p.scale_log2 = d.scale * kLog2e;
+    if (batch > 65535 || d.kv_heads > 65535) {
+        snprintf(plan.why, sizeof(plan.why), "batch / kv_heads exceed the grid limit");
+        return ELLM_ERR_UNSUPPORTED;
+    }
+    dim3 grid(p.pair_tiles, p.kv_heads, p.batch);
+    prefill_tcgen05_kernel<<<grid, kTcThreads, kTcSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    return cudaGetLastError() == cudaSuccess ? ELLM_OK : ELLM_ERR_CUDA;
 }
 
 }  // namespace ellm

@@ -1,0 +1,73 @@
+"""Parity of the tcgen05 / TMEM / TMA prefill kernel with the CPU oracle (B200 only)."""
+import numpy as np
+import pytest
+import torch
+
+import ellm_b200
+from ellm_b200 import _lib as L
+from helpers import Case, assert_attention_close, assert_cache_bit_exact, bits
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(case):
+    want_k, want_v, want_o, want_l = case.oracle()
+    got_k, got_v, got_o, got_l = case.gpu(prefill_kernel=L.PREFILL_TCGEN05)
+    assert_cache_bit_exact(got_k, got_v, want_k, want_v)
+    assert case.last_stats["prefill_tcgen05"][0] == 1 and case.last_stats["prefill_warp_mma"][0] == 0
+    return assert_attention_close(case, got_o, got_l, want_o, want_l)
+
+
+@pytest.mark.parametrize("interval,position_index", [(2, 0), (127, 0), (128, 0), (129, 0), (255, 0), (256, 0), (257, 0),
+                                                     (384, 0), (100, 28), (130, 128), (513, 300)])
+@pytest.mark.parametrize("q_heads,kv_heads", [(2, 2), (8, 1), (4, 2), (32, 2)])
+def test_tcgen05_prefill_shapes(interval, position_index, q_heads, kv_heads):
+    case = Case(seed=700 + interval + q_heads, interval=interval, batch=2, q_heads=q_heads, kv_heads=kv_heads,
+                max_seq=position_index + interval + 9, position_index=position_index, max_batch=3)
+    _check(case)
+
+
+def test_tcgen05_prefill_llama7b_shape_one_head_group():
+    # BASELINE configs[0] geometry (seq 2048, MHA) on 4 of its 32 heads to keep the oracle quick
+    case = Case(seed=0, interval=2048, batch=1, q_heads=4, kv_heads=4, max_seq=4096, position_index=0)
+    _check(case)
+
+
+def test_tcgen05_prefill_reference_layout_seq_major_cache():
+    """The stride vector the reference model code produces (src/qwen3_moe/attention.rs:149-166):
+    K/V physically [seq, batch, kv_head, d], passed as strides [Hkv*D, D, batch*Hkv*D, 1]."""
+    dev = torch.device("cuda:0")
+    S, B, Hq, Hkv = 200, 2, 8, 2
+    case = Case(seed=77, interval=S, batch=B, q_heads=Hq, kv_heads=Hkv, max_seq=S, position_index=0, poison=False)
+    _, _, want_o, want_l = case.oracle()
+    k_seq_major = case.k_new.to(dev).contiguous()  # [S, B, Hkv, D] is exactly the chunk's rows
+    v_seq_major = case.v_new.to(dev).contiguous()
+    q = case.q.to(dev)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(S, B, Hq, dtype=torch.float32, device=dev)
+    op = ellm_b200.Attention.new(q, k_seq_major, v_seq_major, out, B, Hq, Hkv, 128, [Hkv * 128, 128, B * Hkv * 128, 1],
+                                 case.scale, max_seq=S, max_interval=S, lse=lse, prefill_kernel=L.PREFILL_TCGEN05)
+    op.run(0, S, B, 1, 0)
+    assert_attention_close(case, bits(out), lse.cpu().numpy(), want_o, want_l)
+
+
+def test_auto_picks_tcgen05_for_large_chunks_and_warp_mma_for_small():
+    big = Case(seed=1, interval=256, batch=1, q_heads=2, kv_heads=2, max_seq=256)
+    big.gpu()
+    assert big.last_stats["prefill_tcgen05"][0] == 1
+    small = Case(seed=1, interval=16, batch=1, q_heads=2, kv_heads=2, max_seq=32)
+    small.gpu()
+    assert small.last_stats["prefill_warp_mma"][0] == 1
+    ragged = Case(seed=1, interval=256, batch=2, q_heads=2, kv_heads=2, max_seq=600, positions=[0, 300])
+    ragged.gpu()   # ragged chunk starts are served by the warp-MMA kernel
+    assert ragged.last_stats["prefill_warp_mma"][0] == 1
+
+
+def test_tcgen05_unsupported_group_is_reported():
+    dev = torch.device("cuda:0")
+    q = torch.zeros(4, 1, 6, 128, dtype=torch.bfloat16, device=dev)
+    k = torch.zeros(1, 2, 8, 128, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(ellm_b200.EllmError) as e:   # 3 query heads per KV head does not divide 128
+        ellm_b200.Attention.new(q, k, k.clone(), torch.zeros_like(q), 1, 6, 2, 128, [2 * 8 * 128, 8 * 128, 128, 1], 0.1,
+                                max_seq=8, max_interval=4, prefill_kernel=L.PREFILL_TCGEN05)
+    assert e.value.status == L.ERR_UNSUPPORTED
