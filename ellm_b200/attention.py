@@ -103,11 +103,12 @@ def kv_append(cache, src, kv_strides, max_batch, kv_heads, head_size, max_seq, p
                                _ptr(positions), position_interval, batch_size, device, stream))
 
 
-def merge_partials(o_parts, lse_parts, out, lse_out=None, device=0, stream=None):
-    """o_parts [parts, rows, 128] fp32, lse_parts [parts, rows] fp32 -> out [rows, 128] bf16."""
+def merge_partials(o_parts, lse_parts, out, lse_out=None, device=0, stream=None, out_f32=False):
+    """o_parts [parts, rows, 128] fp32, lse_parts [parts, rows] fp32 -> out [rows, 128] bf16
+    (or fp32 with out_f32=True)."""
     parts, rows, d = o_parts.shape
-    L.check(L.load().ellm_attn_merge_partials(_ptr(o_parts), _ptr(lse_parts), parts, rows, d,
-                                              _ptr(out), _ptr(lse_out), device, stream))
+    fn = L.load().ellm_attn_merge_partials_f32 if out_f32 else L.load().ellm_attn_merge_partials
+    L.check(fn(_ptr(o_parts), _ptr(lse_parts), parts, rows, d, _ptr(out), _ptr(lse_out), device, stream))
 
 
 def decode_noalloc(q, k_cache, v_cache, out, batch_size, q_heads, kv_heads, head_size, kv_strides,

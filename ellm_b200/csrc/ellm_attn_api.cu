@@ -259,9 +259,11 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
     if (batch > h->d.max_batch) return fail(ELLM_ERR_INVALID_ARG, "batch_size %zu > max_batch %zu", batch, h->d.max_batch);
     if (interval > h->d.max_interval)
         return fail(ELLM_ERR_INVALID_ARG, "position_interval %zu > max_interval %zu", interval, h->d.max_interval);
-    if (!positions && position_index + interval > h->d.max_seq)
-        return fail(ELLM_ERR_INVALID_ARG, "position_index %zu + interval %zu exceeds max_seq %zu", position_index, interval, h->d.max_seq);
     if (key_begin < 0 || key_end < key_begin) return fail(ELLM_ERR_INVALID_ARG, "bad key window");
+    // a windowed call may place its rows past the cache (a later chunk of a sharded sequence
+    // attending an earlier chunk's keys): only the keys it reads must be inside the cache
+    if (!positions && position_index + interval > h->d.max_seq && key_end > static_cast<long long>(h->d.max_seq))
+        return fail(ELLM_ERR_INVALID_ARG, "position_index %zu + interval %zu exceeds max_seq %zu", position_index, interval, h->d.max_seq);
     DeviceGuard guard(h->d.device);
     if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", h->d.device);
     std::lock_guard<std::mutex> lock(h->mu);
@@ -275,7 +277,7 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
         rc = launch_decode(h, positions, position_index, batch, key_begin, key_end, out_f32, lse_out);
     } else {
         bool use_tc = false;
-        if (!out_f32 && key_begin == 0 && key_end >= static_cast<long long>(h->d.max_seq)) {
+        if (key_begin == 0) {
             if (h->d.prefill_kernel == ELLM_PREFILL_TCGEN05) use_tc = true;
             else if (h->d.prefill_kernel == ELLM_PREFILL_AUTO) use_tc = !positions && ellm::tcgen05_prefers(h->tc, interval, h->group);
         }
@@ -284,8 +286,8 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
                 return fail(ELLM_ERR_UNSUPPORTED, "tcgen05 prefill unavailable for this handle: %s", h->tc.why);
             {
                 LaunchScope ls(h, ELLM_KERNEL_PREFILL_TCGEN05);
-                rc = ellm::launch_prefill_tcgen05(h->tc, h->d, positions, position_index, interval, batch, lse_out,
-                                                  h->status_dev, h->stream);
+                rc = ellm::launch_prefill_tcgen05(h->tc, h->d, positions, position_index, interval, batch, key_end, out_f32,
+                                                  lse_out, h->status_dev, h->stream);
             }
             if (rc == ELLM_ERR_UNSUPPORTED) return fail(rc, "tcgen05 prefill: %s", h->tc.why);
             if (rc) return fail(rc, "tcgen05 prefill launch failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -508,8 +510,8 @@ int ellm_kv_append(void* cache, const void* src, const size_t kv_strides[4], siz
                          kv_heads, max_seq, position_index, positions, position_interval, batch_size);
 }
 
-int ellm_attn_merge_partials(const float* o_parts, const float* lse_parts, size_t parts, size_t rows,
-                             size_t head_size, void* out, float* lse_out, int device, void* stream) {
+static int merge_partials_impl(const float* o_parts, const float* lse_parts, size_t parts, size_t rows,
+                               size_t head_size, void* out, bool out_f32, float* lse_out, int device, void* stream) {
     if (!o_parts || !lse_parts || !out) return fail(ELLM_ERR_INVALID_ARG, "o_parts, lse_parts and out must be non-NULL");
     if (head_size != static_cast<size_t>(ellm::kHeadDim)) return fail(ELLM_ERR_UNSUPPORTED, "head_size %zu: only 128", head_size);
     if (parts == 0 || parts > 65535) return fail(ELLM_ERR_INVALID_ARG, "parts %zu out of range", parts);
@@ -518,10 +520,24 @@ int ellm_attn_merge_partials(const float* o_parts, const float* lse_parts, size_
     DeviceGuard guard(device);
     if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
     const unsigned blocks = static_cast<unsigned>((rows + 3) / 4);
-    ellm::merge_partials_kernel<__nv_bfloat16><<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        o_parts, lse_parts, static_cast<int>(parts), static_cast<long long>(rows), static_cast<__nv_bfloat16*>(out), lse_out);
+    if (out_f32)
+        ellm::merge_partials_kernel<float><<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+            o_parts, lse_parts, static_cast<int>(parts), static_cast<long long>(rows), static_cast<float*>(out), lse_out);
+    else
+        ellm::merge_partials_kernel<__nv_bfloat16><<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+            o_parts, lse_parts, static_cast<int>(parts), static_cast<long long>(rows), static_cast<__nv_bfloat16*>(out), lse_out);
     ELLM_CUDA(cudaGetLastError());
     return ELLM_OK;
+}
+
+int ellm_attn_merge_partials(const float* o_parts, const float* lse_parts, size_t parts, size_t rows,
+                             size_t head_size, void* out, float* lse_out, int device, void* stream) {
+    return merge_partials_impl(o_parts, lse_parts, parts, rows, head_size, out, false, lse_out, device, stream);
+}
+
+int ellm_attn_merge_partials_f32(const float* o_parts, const float* lse_parts, size_t parts, size_t rows,
+                                 size_t head_size, float* out, float* lse_out, int device, void* stream) {
+    return merge_partials_impl(o_parts, lse_parts, parts, rows, head_size, out, true, lse_out, device, stream);
 }
 
 int ellm_attn_set_profiling(ellm_attn* h, int on) {

@@ -55,10 +55,12 @@ struct Tcgen05Plan {
 };
 
 struct TcParams {
-    __nv_bfloat16* out;
+    void* out;              // bf16, or fp32 for a partial result over a key window
+
     float* lse;
     int* status;            // device word: non-zero = a bounded wait ran out
     long long base;         // position of chunk row 0
+    long long key_end;      // rows attend keys [0, min(position + 1, key_end))
     int interval, batch, max_batch;
     int q_heads, kv_heads, group;
     int pair_tiles;         // CTAs along x = ceil(interval * group / 256)
@@ -197,10 +199,12 @@ enum { kTcWaitQ = 1, kTcWaitKvFull = 2, kTcWaitKvEmpty = 3, kTcWaitSFull = 4, kT
 __device__ __forceinline__ int tc_tile_steps(const TcParams& p, int rho0, int total_rows) {
     if (rho0 >= total_rows) return 0;
     const int rho_last = min(rho0 + kTcTileRows, total_rows) - 1;
-    const long long kend = p.base + rho_last / p.group + 1;
+    long long kend = p.base + rho_last / p.group + 1;
+    if (kend > p.key_end) kend = p.key_end;
     return static_cast<int>((kend + kTcKeys - 1) / kTcKeys);
 }
 
+template <typename OutT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const TcParams p) {
@@ -263,8 +267,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int rho = (pair * kTcTiles + t) * kTcTileRows + row;
         const bool valid = rho < total_rows;
         const int pos = valid ? rho / p.group : 0, g = valid ? rho % p.group : 0;
-        const long long lim = valid ? p.base + pos : -1;        // last key this row may see
-        const long long tile_min_lim = p.base + ((pair * kTcTiles + t) * kTcTileRows) / p.group;
+        const long long lim = valid ? min(p.base + pos, p.key_end - 1) : -1;   // last key this row may see
+        const long long tile_min_lim = min(p.base + ((pair * kTcTiles + t) * kTcTileRows) / p.group, p.key_end - 1);
         unsigned char* p_row = smem + kTcSmemP + t * kTcTileBytes + row * 128;
         const int my_steps = steps[t];
         float m_used = -INFINITY, l = 0.0f;
@@ -347,21 +351,28 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_fence_after();
             const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
             const long long row_index = (static_cast<long long>(pos) * p.max_batch + b) * p.q_heads + kvh * p.group + g;
-            __nv_bfloat16* orow = p.out + row_index * kHeadDim;
+            OutT* orow = reinterpret_cast<OutT*>(p.out) + row_index * kHeadDim;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 float o[32];
                 tmem_ld32(tO + c * 32, o);
                 tmem_wait_ld();
                 if (valid) {
+                    if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint4 v;
-                        v.x = pack_bf16(o[i * 8 + 0] * inv, o[i * 8 + 1] * inv);
-                        v.y = pack_bf16(o[i * 8 + 2] * inv, o[i * 8 + 3] * inv);
-                        v.z = pack_bf16(o[i * 8 + 4] * inv, o[i * 8 + 5] * inv);
-                        v.w = pack_bf16(o[i * 8 + 6] * inv, o[i * 8 + 7] * inv);
-                        *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = v;
+                        for (int i = 0; i < 8; ++i)
+                            *reinterpret_cast<float4*>(orow + c * 32 + i * 4) =
+                                make_float4(o[i * 4 + 0] * inv, o[i * 4 + 1] * inv, o[i * 4 + 2] * inv, o[i * 4 + 3] * inv);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint4 v;
+                            v.x = pack_bf16(o[i * 8 + 0] * inv, o[i * 8 + 1] * inv);
+                            v.y = pack_bf16(o[i * 8 + 2] * inv, o[i * 8 + 3] * inv);
+                            v.z = pack_bf16(o[i * 8 + 4] * inv, o[i * 8 + 5] * inv);
+                            v.w = pack_bf16(o[i * 8 + 6] * inv, o[i * 8 + 7] * inv);
+                            *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = v;
+                        }
                     }
                 }
             }
@@ -494,7 +505,8 @@ inline void tcgen05_plan_init(Tcgen05Plan& plan, const ellm_attn_desc& d, int sm
         snprintf(plan.why, sizeof(plan.why), "driver does not export cuTensorMapEncodeTiled");
         return;
     }
-    if (cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) != cudaSuccess) {
+    if (cudaFuncSetAttribute(prefill_tcgen05_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_tcgen05_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) != cudaSuccess) {
         snprintf(plan.why, sizeof(plan.why), "cannot reserve %d bytes of shared memory: %s", kTcSmemBytes,
                  cudaGetErrorString(cudaGetLastError()));
         return;
@@ -509,16 +521,24 @@ inline bool tcgen05_prefers(const Tcgen05Plan& plan, size_t interval, int group)
 }
 
 // Uniform chunk start only (positions == nullptr): the K/V tensor maps are bounded at
-// position_index + interval so that TMA zero-fills rows the chunk must not read.
+// min(position_index + interval, key_end) so that TMA zero-fills rows the chunk must not read.
+// out_f32 != nullptr writes an fp32 partial result there instead of bf16 to d.out.
 inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, const int32_t* positions,
-                                  size_t position_index, size_t interval, size_t batch, float* lse, int* status,
-                                  cudaStream_t stream) {
+                                  size_t position_index, size_t interval, size_t batch, long long key_end,
+                                  float* out_f32, float* lse, int* status, cudaStream_t stream) {
     if (!plan.ready) return ELLM_ERR_UNSUPPORTED;
     if (positions) {
         snprintf(plan.why, sizeof(plan.why), "ragged positions are served by the warp-MMA kernel");
         return ELLM_ERR_UNSUPPORTED;
     }
     const int group = static_cast<int>(d.q_heads / d.kv_heads);
+    long long kv_rows = static_cast<long long>(position_index + interval);
+    if (kv_rows > key_end) kv_rows = key_end;
+    if (kv_rows > static_cast<long long>(d.max_seq)) kv_rows = static_cast<long long>(d.max_seq);
+    if (kv_rows <= 0) {
+        snprintf(plan.why, sizeof(plan.why), "empty key window");
+        return ELLM_ERR_UNSUPPORTED;
+    }
     EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(plan.encode);
     CUtensorMap map_q, map_k, map_v;
     {
@@ -535,7 +555,7 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
         }
     }
     for (int which = 0; which < 2; ++which) {
-        cuuint64_t dims[4] = {128, position_index + interval, d.kv_heads, batch};
+        cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(kv_rows), d.kv_heads, batch};
         cuuint64_t strides[3] = {d.kv_strides[2] * 2, d.kv_strides[1] * 2, d.kv_strides[0] * 2};
         cuuint32_t box[4] = {64, 128, 1, 1};
         cuuint32_t es[4] = {1, 1, 1, 1};
@@ -547,7 +567,8 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
         }
     }
     TcParams p;
-    p.out = static_cast<__nv_bfloat16*>(d.out);
+    p.out = out_f32 ? static_cast<void*>(out_f32) : d.out;
+    p.key_end = kv_rows;
     p.lse = lse;
     p.status = status;
     p.base = static_cast<long long>(position_index);
@@ -564,7 +585,10 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
         return ELLM_ERR_UNSUPPORTED;
     }
     dim3 grid(p.pair_tiles, p.kv_heads, p.batch);
-    prefill_tcgen05_kernel<<<grid, kTcThreads, kTcSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    if (out_f32)
+        prefill_tcgen05_kernel<float><<<grid, kTcThreads, kTcSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    else
+        prefill_tcgen05_kernel<__nv_bfloat16><<<grid, kTcThreads, kTcSmemBytes, stream>>>(map_q, map_k, map_v, p);
     return cudaGetLastError() == cudaSuccess ? ELLM_OK : ELLM_ERR_CUDA;
 }
 

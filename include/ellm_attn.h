@@ -138,6 +138,12 @@ int ellm_attn_merge_partials(const float* o_parts, const float* lse_parts, size_
                              size_t rows, size_t head_size, void* out, float* lse_out,
                              int device, void* stream);
 
+/* Same combine with an fp32 result (out [rows, head_size] fp32): the local pre-merge of a
+ * rank that holds several key chunks, before its partial travels to the rows' owner. */
+int ellm_attn_merge_partials_f32(const float* o_parts, const float* lse_parts, size_t parts,
+                                 size_t rows, size_t head_size, float* out, float* lse_out,
+                                 int device, void* stream);
+
 /* Attention over an explicit key window, fp32 partial output: chunk rows attend
  * keys [key_begin, min(key_end, position+1)) only.  Used by sequence-chunk
  * sharding, where each GPU holds one contiguous slice of the keys.

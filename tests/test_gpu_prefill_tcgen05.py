@@ -71,3 +71,41 @@ def test_tcgen05_unsupported_group_is_reported():
         ellm_b200.Attention.new(q, k, k.clone(), torch.zeros_like(q), 1, 6, 2, 128, [2 * 8 * 128, 8 * 128, 128, 1], 0.1,
                                 max_seq=8, max_interval=4, prefill_kernel=L.PREFILL_TCGEN05)
     assert e.value.status == L.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("kernel", [L.PREFILL_TCGEN05, L.PREFILL_WARP_MMA])
+def test_sequence_chunks_as_key_windows_merge_to_the_full_result(kernel):
+    """What sequence-chunk sharding does, on one GPU: the keys are cut into chunks held in
+    separate caches; a query chunk takes an fp32 partial (O, LSE) against each earlier chunk
+    (placed past that cache's end, so it sees all of its keys) and a causal one against its
+    own; the merged partials equal the unsplit result."""
+    dev = torch.device("cuda:0")
+    S, Hq, Hkv, chunk = 768, 8, 2, 256
+    full = Case(seed=88, interval=S, batch=1, q_heads=Hq, kv_heads=Hkv, max_seq=S, position_index=0, poison=False)
+    _, _, want_o, want_l = full.oracle()
+    n = S // chunk
+    strides = [Hkv * chunk * 128, chunk * 128, 128, 1]
+    # chunk caches [1, Hkv, chunk, 128] from the chunk's rows [chunk, 1, Hkv, 128]
+    caches = [(full.k_new[c * chunk:(c + 1) * chunk, 0].permute(1, 0, 2).contiguous().to(dev)[None],
+               full.v_new[c * chunk:(c + 1) * chunk, 0].permute(1, 0, 2).contiguous().to(dev)[None]) for c in range(n)]
+    got_o = np.zeros((S, 1, Hq, 128), np.uint16)
+    got_l = np.zeros((S, 1, Hq), np.float32)
+    for i in range(n):
+        q = full.q[i * chunk:(i + 1) * chunk].contiguous().to(dev)
+        po = torch.zeros(i + 1, chunk, 1, Hq, 128, dtype=torch.float32, device=dev)
+        pl = torch.zeros(i + 1, chunk, 1, Hq, dtype=torch.float32, device=dev)
+        for k in range(i + 1):
+            ck, cv = caches[k]
+            op = ellm_b200.Attention.new(q, ck, cv, torch.zeros_like(q), 1, Hq, Hkv, 128, strides, full.scale,
+                                         max_seq=chunk, max_interval=chunk, prefill_kernel=kernel)
+            op.run_window((i - k) * chunk, chunk, 1, 0, chunk, po[k], pl[k])
+            name = "prefill_tcgen05" if kernel == L.PREFILL_TCGEN05 else "prefill_warp_mma"
+            assert op.kernel_stats()[name][0] == 1
+            op.close()
+        out = torch.zeros(chunk * Hq, 128, dtype=torch.bfloat16, device=dev)
+        lse = torch.zeros(chunk * Hq, dtype=torch.float32, device=dev)
+        ellm_b200.merge_partials(po.view(i + 1, chunk * Hq, 128), pl.view(i + 1, chunk * Hq), out, lse)
+        torch.cuda.synchronize()
+        got_o[i * chunk:(i + 1) * chunk] = bits(out).reshape(chunk, 1, Hq, 128)
+        got_l[i * chunk:(i + 1) * chunk] = lse.cpu().numpy().reshape(chunk, 1, Hq)
+    assert_attention_close(full, got_o, got_l, want_o, want_l)
