@@ -16,8 +16,9 @@
 //   warp  8    TMA producer (one lane): Q tiles once, then K_j, V_j through a ring
 //   warp  9    MMA issuer (one lane) and owner of the tensor-memory allocation
 // Per 128-key tile j and row tile t:  S_t = Q_t K_j^T (tensor memory) -> softmax
-// threads read S_t, write P_t (bf16) to shared memory and, when the running max
-// moved by more than 2^8, rescale O_t in tensor memory -> O_t += P_t V_j.
+// threads read S_t, write P_t (bf16) back into the first 64 columns of S_t and,
+// when the running max moved by more than 2^8, rescale O_t in tensor memory ->
+// O_t += P_t V_j with P_t read from tensor memory as the A operand.
 // The two row tiles alternate on the tensor core, so one tile's softmax overlaps
 // the other's MMAs.
 //
@@ -36,13 +37,12 @@ namespace ellm {
 constexpr int kTcTileRows = 128;   // rows per tile = tensor-memory lanes
 constexpr int kTcTiles = 2;        // row tiles per CTA
 constexpr int kTcKeys = 128;       // keys per K/V tile
-constexpr int kTcStages = 3;       // ring slots, each holds one K or one V tile
+constexpr int kTcStages = 5;       // ring slots, each holds one K or one V tile
 constexpr int kTcTileBytes = kTcKeys * kRowBytes;          // 32 KB: two 16 KB halves of 128 rows x 128 B
 constexpr int kTcHalfBytes = kTcTileBytes / 2;
 constexpr int kTcThreads = (kTcTiles * 4 + 2) * 32;        // 320
 constexpr int kTcSmemQ = 0;
-constexpr int kTcSmemP = kTcSmemQ + kTcTiles * kTcTileBytes;
-constexpr int kTcSmemRing = kTcSmemP + kTcTiles * kTcTileBytes;
+constexpr int kTcSmemRing = kTcSmemQ + kTcTiles * kTcTileBytes;
 constexpr int kTcSmemBar = kTcSmemRing + kTcStages * kTcTileBytes;
 constexpr int kTcSmemBytes = kTcSmemBar + 256 + 1024;       // barriers + slack to align the base to 1024
 constexpr float kTcRescaleThreshold = 8.0f;                 // log2 units
@@ -161,6 +161,15 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Same with the A operand in tensor memory (128 lanes x 8 columns of packed bf16 pairs per 16-wide K step).
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -178,8 +187,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t* r);
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
-    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    tmem_st32u(taddr, reinterpret_cast<const uint32_t*>(v));
+}
+__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t* r) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
         "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
@@ -269,7 +281,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int pos = valid ? rho / p.group : 0, g = valid ? rho % p.group : 0;
         const long long lim = valid ? min(p.base + pos, p.key_end - 1) : -1;   // last key this row may see
         const long long tile_min_lim = min(p.base + ((pair * kTcTiles + t) * kTcTileRows) / p.group, p.key_end - 1);
-        unsigned char* p_row = smem + kTcSmemP + t * kTcTileBytes + row * 128;
         const int my_steps = steps[t];
         float m_used = -INFINITY, l = 0.0f;
         bool ok = true;
@@ -310,22 +321,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 sum += s[c];
             }
             l = l * corr + sum;
-            if (j > 0) {  // P_t and O_t are in use until PV(t, j-1) has completed
-                ok = mbar_wait(bar_pv_done(t), (j - 1) & 1, abort_word, p.status, kTcWaitPvDone);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-            }
-            // P row -> shared memory, K-major 128-byte-swizzled: 16-byte chunk c8 of the row sits
-            // in half (c8 >> 3) at chunk position (c8 & 7) ^ (row & 7)
+            // S_t(j) complete implies P.V(t, j-1) complete (MMAs of one thread finish in issue
+            // order), so the columns of S_t can take P_t and O_t can be rescaled right away.
+            // P row -> tensor memory: bf16 pairs (k, k+1) per 32-bit column, 64 columns.
+            {
+                uint32_t pk[64];
 #pragma unroll
-            for (int c8 = 0; c8 < 16; ++c8) {
-                uint4 v;
-                v.x = pack_bf16(s[c8 * 8 + 0], s[c8 * 8 + 1]);
-                v.y = pack_bf16(s[c8 * 8 + 2], s[c8 * 8 + 3]);
-                v.z = pack_bf16(s[c8 * 8 + 4], s[c8 * 8 + 5]);
-                v.w = pack_bf16(s[c8 * 8 + 6], s[c8 * 8 + 7]);
-                *reinterpret_cast<uint4*>(p_row + (c8 >> 3) * kTcHalfBytes + (((c8 & 7) ^ (row & 7)) << 4)) = v;
+                for (int c = 0; c < 64; ++c) pk[c] = pack_bf16(s[2 * c], s[2 * c + 1]);
+                tmem_st32u(tS, pk);
+                tmem_st32u(tS + 32, pk + 32);
             }
             if (rescale && j > 0) {
 #pragma unroll
@@ -337,9 +341,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     for (int i = 0; i < 32; ++i) o[i] *= corr;
                     tmem_st32(tO + c * 32, o);
                 }
-                tmem_wait_st();
             }
-            fence_async_smem();
+            tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar_p_full(t));
         }
@@ -420,14 +423,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 umma_commit(bar_s_full(t));
             };
             auto issue_pv = [&](int t, int slot, bool first) {  // O_t += P_t V: 8 steps of 16 keys
-                const uint32_t p_addr = smem_base + kTcSmemP + t * kTcTileBytes;
                 const uint32_t v_addr = smem_base + kTcSmemRing + slot * kTcTileBytes;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t a_off = (ks >> 2) * kTcHalfBytes + (ks & 3) * 32;
                     const uint32_t b_off = ks * 16 * 128;  // 16 key rows of 128 bytes
-                    umma_bf16(tmem + 256 + t * 128, umma_desc(p_addr + a_off, 0, 1024),
-                              umma_desc(v_addr + b_off, kTcHalfBytes, 1024), idesc_pv, !(first && ks == 0));
+                    umma_bf16_a_tmem(tmem + 256 + t * 128, tmem + t * 128 + ks * 8,
+                                     umma_desc(v_addr + b_off, kTcHalfBytes, 1024), idesc_pv, !(first && ks == 0));
                 }
                 umma_commit(bar_pv_done(t));
             };
