@@ -69,7 +69,8 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    path = _build.build()
+    # ELLM_ATTN_LIB points at an already built library (skips the in-tree build)
+    path = os.environ.get("ELLM_ATTN_LIB") or _build.build()
     lib = C.CDLL(path)
     for name, (res, args) in _SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol

@@ -46,6 +46,13 @@ constexpr int kTcSmemRing = kTcSmemQ + kTcTiles * kTcTileBytes;
 constexpr int kTcSmemBar = kTcSmemRing + kTcStages * kTcTileBytes;
 constexpr int kTcSmemBytes = kTcSmemBar + 256 + 1024;       // barriers + slack to align the base to 1024
 constexpr float kTcRescaleThreshold = 8.0f;                 // log2 units
+#ifndef ELLM_TC_SPLIT_P
+#define ELLM_TC_SPLIT_P 0   // hand the first 64 keys of P to the MMA issuer before the rest is computed
+#endif
+#ifndef ELLM_TC_POLY_EVERY
+#define ELLM_TC_POLY_EVERY 0
+#endif
+constexpr int kTcPolyEvery = ELLM_TC_POLY_EVERY;            // every n-th pair of a row uses the polynomial exp2 (0 = none)
 
 struct Tcgen05Plan {
     bool ready = false;
@@ -204,6 +211,52 @@ __device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t* r) {
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// ---- packed fp32 pair arithmetic and the exp2 helpers of the softmax passes ----
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+// 2^x for a pair, x <= ~8, without the exp2 unit: x = n + f with n = round(x) (magic-number
+// add), 2^f from a degree-3 polynomial on [-0.5, 0.5] (max relative error 7.5e-5, below the
+// bf16 rounding P gets anyway), 2^n added into the exponent field.
+__device__ __forceinline__ uint64_t exp2_poly2(uint64_t x2) {
+    float x0, x1;
+    unpack2(x2, x0, x1);
+    const uint64_t xc = pack2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+    const uint64_t magic = pack2(12582912.0f, 12582912.0f), neg_magic = pack2(-12582912.0f, -12582912.0f);
+    const uint64_t r2 = add2(xc, magic);              // low mantissa bits now hold round(x)
+    const uint64_t n2 = add2(r2, neg_magic);          // round(x) as a float
+    const uint64_t f2 = fma2(n2, pack2(-1.0f, -1.0f), xc);
+    uint64_t p2 = fma2(f2, pack2(0.0551716685295105f, 0.0551716685295105f), pack2(0.2426111251115799f, 0.2426111251115799f));
+    p2 = fma2(p2, f2, pack2(0.6932609677314758f, 0.6932609677314758f));
+    p2 = fma2(p2, f2, pack2(0.9999280571937561f, 0.9999280571937561f));
+    float r0, r1, p0, p1;
+    unpack2(r2, r0, r1);
+    unpack2(p2, p0, p1);
+    const float y0 = __int_as_float(__float_as_int(p0) + (__float_as_int(r0) << 23));
+    const float y1 = __int_as_float(__float_as_int(p1) + (__float_as_int(r1) << 23));
+    return pack2(y0, y1);
+}
+
 // Status codes written by a wait that ran out (which wait gave up).
 enum { kTcWaitQ = 1, kTcWaitKvFull = 2, kTcWaitKvEmpty = 3, kTcWaitSFull = 4, kTcWaitPFull = 5, kTcWaitPvDone = 6 };
 
@@ -233,7 +286,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     auto bar_s_full = [&](int t) { return bar0 + 8u * (2 + 2 * kTcStages + t); };
     auto bar_p_full = [&](int t) { return bar0 + 8u * (4 + 2 * kTcStages + t); };
     auto bar_pv_done = [&](int t) { return bar0 + 8u * (6 + 2 * kTcStages + t); };
-    constexpr int kNumBars = 8 + 2 * kTcStages;
+    auto bar_p_half = [&](int t) { return bar0 + 8u * (8 + 2 * kTcStages + t); };
+    constexpr int kNumBars = 10 + 2 * kTcStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kTcSmemBar + 8 * kNumBars);
     volatile int* abort_word = reinterpret_cast<volatile int*>(smem + kTcSmemBar + 8 * kNumBars + 8);
 
@@ -250,6 +304,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(bar_q(t), 1);
             mbar_init(bar_s_full(t), 1);
             mbar_init(bar_p_full(t), kTcTileRows);
+            mbar_init(bar_p_half(t), kTcTileRows);
             mbar_init(bar_pv_done(t), 1);
         }
         for (int s = 0; s < kTcStages; ++s) {
@@ -289,20 +344,42 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            float s[128];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
-            tmem_wait_ld();
+#if defined(ELLM_WHATIF_NOSOFTMAX)
+            tc_fence_before();
+            mbar_arrive(bar_p_full(t));
+            continue;
+#endif
             const long long key0 = static_cast<long long>(j) * kTcKeys;
-            if (key0 + kTcKeys - 1 > tile_min_lim) {  // the causal edge crosses this tile
-                const long long d = lim - key0;                // last column this row may see
-                const int rel = d < 0 ? -1 : (d > 127 ? 127 : static_cast<int>(d));
+            const bool edge = key0 + kTcKeys - 1 > tile_min_lim;   // the causal edge crosses this tile
+            const long long dlim = lim - key0;                     // last column this row may see
+            const int rel = dlim < 0 ? -1 : (dlim > 127 ? 127 : static_cast<int>(dlim));
+            // pass 1 over S_t: row maximum (3-input max, two chains per 32-column chunk).  The
+            // scores are read again in pass 2 rather than kept: tensor-memory reads are cheap and
+            // 128 live registers per thread are not.
+            float mx = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < 128; ++c) s[c] = (c <= rel) ? s[c] : -INFINITY;
+            for (int h = 0; h < 2; ++h) {
+                float s[64];
+                tmem_ld32(tS + h * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
+                tmem_ld32(tS + h * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+                tmem_wait_ld();
+                if (edge) {
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) s[c] = (h * 64 + c <= rel) ? s[c] : -INFINITY;
+                }
+                float m0 = max3(s[0], s[1], s[2]), m1 = max3(s[3], s[4], s[5]);
+                float m2 = max3(s[6], s[7], s[8]), m3 = max3(s[9], s[10], s[11]);
+#pragma unroll
+                for (int c = 12; c < 60; c += 8) {
+                    m0 = max3(m0, s[c], s[c + 1]);
+                    m1 = max3(m1, s[c + 2], s[c + 3]);
+                    m2 = max3(m2, s[c + 4], s[c + 5]);
+                    m3 = max3(m3, s[c + 6], s[c + 7]);
+                }
+                m0 = max3(m0, s[60], s[61]);
+                m1 = max3(m1, s[62], s[63]);
+                mx = max3(mx, fmaxf(m0, m1), fmaxf(m2, m3));
             }
-            float mx = s[0];
-#pragma unroll
-            for (int c = 1; c < 128; ++c) mx = fmaxf(mx, s[c]);
             const float m_new = fmaxf(m_used, mx * p.scale_log2);
             // rescale O only when the maximum moved far enough to matter; otherwise keep
             // exponentiating against the stale maximum (O and l stay consistent with it)
@@ -314,24 +391,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 m_used = m_new;
             }
             const float msub = (m_used == -INFINITY) ? 0.0f : m_used;
-            float sum = 0.0f;
-#pragma unroll
-            for (int c = 0; c < 128; ++c) {
-                s[c] = fast_exp2(fmaf(s[c], p.scale_log2, -msub));
-                sum += s[c];
-            }
-            l = l * corr + sum;
             // S_t(j) complete implies P.V(t, j-1) complete (MMAs of one thread finish in issue
-            // order), so the columns of S_t can take P_t and O_t can be rescaled right away.
-            // P row -> tensor memory: bf16 pairs (k, k+1) per 32-bit column, 64 columns.
-            {
-                uint32_t pk[64];
-#pragma unroll
-                for (int c = 0; c < 64; ++c) pk[c] = pack_bf16(s[2 * c], s[2 * c + 1]);
-                tmem_st32u(tS, pk);
-                tmem_st32u(tS + 32, pk + 32);
-            }
-            if (rescale && j > 0) {
+            // order), so O_t can be rescaled and the columns of S_t can take P_t right away.
+            if (rescale && j > 0) {   // before any P.V of this step may start
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     float o[32];
@@ -342,9 +404,60 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     tmem_st32(tO + c * 32, o);
                 }
             }
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar_p_full(t));
+            // pass 2: p = exp2(s * scale - m) on packed pairs (a fixed share of the pairs may take
+            // the polynomial route on the FMA pipe instead of the 16-per-clock exp2 unit);
+            // P row -> tensor memory as bf16 pairs (k, k+1) per 32-bit column, 64 columns, over
+            // the first half of S_t.  The first 64 keys' P is handed to the MMA warp before the
+            // second half is computed.
+            {
+                const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-msub, -msub);
+                uint64_t sum_a = pack2(0.0f, 0.0f), sum_b = sum_a;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    // keys [64*half, 64*half+64) of S sit in columns [64*half, +64); their P goes to
+                    // columns [32*half, +32), which never overlap a half of S not yet read
+                    float s[64];
+                    tmem_ld32(tS + half * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
+                    tmem_ld32(tS + half * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+                    tmem_wait_ld();
+                    if (edge) {
+#pragma unroll
+                        for (int c = 0; c < 64; ++c) s[c] = (half * 64 + c <= rel) ? s[c] : -INFINITY;
+                    }
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int cc = 0; cc < 32; ++cc) {
+                        const int c = half * 32 + cc;
+                        const uint64_t x2 = fma2(pack2(s[2 * cc], s[2 * cc + 1]), scale2, negm2);
+                        uint64_t p2;
+#if defined(ELLM_WHATIF_NOEXP)
+                        if (true) { p2 = x2; } else
+#endif
+                        if (kTcPolyEvery > 0 && (c % kTcPolyEvery) == kTcPolyEvery - 1) {
+                            p2 = exp2_poly2(x2);
+                        } else {
+                            float x0, x1;
+                            unpack2(x2, x0, x1);
+                            p2 = pack2(fast_exp2(x0), fast_exp2(x1));
+                        }
+                        if (c & 1) sum_b = add2(sum_b, p2); else sum_a = add2(sum_a, p2);
+                        float p0, p1;
+                        unpack2(p2, p0, p1);
+                        pk[cc] = pack_bf16(p0, p1);
+                    }
+                    tmem_st32u(tS + half * 32, pk);
+                    tmem_wait_st();
+                    tc_fence_before();
+#if ELLM_TC_SPLIT_P
+                    mbar_arrive(half == 0 ? bar_p_half(t) : bar_p_full(t));
+#else
+                    if (half == 1) mbar_arrive(bar_p_full(t));
+#endif
+                }
+                float sa, sb;
+                unpack2(add2(sum_a, sum_b), sa, sb);
+                l = l * corr + (sa + sb);
+            }
         }
         if (ok && my_steps > 0) {
             ok = mbar_wait(bar_pv_done(t), (my_steps - 1) & 1, abort_word, p.status, kTcWaitPvDone);
@@ -408,6 +521,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
     } else {
         // =============================== MMA issuer ===============================
+        // One thread issues every MMA, one GEMM after the other: two issuing threads were tried and
+        // lost 20 % because their GEMMs interleave on the tensor pipe and both finish late.
         if (lane == 0) {
             bool ok = true;
             constexpr uint32_t idesc_qk = umma_idesc(false), idesc_pv = umma_idesc(true);
@@ -422,20 +537,26 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
                 umma_commit(bar_s_full(t));
             };
-            auto issue_pv = [&](int t, int slot, bool first) {  // O_t += P_t V: 8 steps of 16 keys
+            // O_t += P_t V for keys [64*half, 64*half + 64): 4 steps of 16 keys
+            auto issue_pv_half = [&](int t, int slot, bool first, int half) {
                 const uint32_t v_addr = smem_base + kTcSmemRing + slot * kTcTileBytes;
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    const int ks = half * 4 + k4;
                     const uint32_t b_off = ks * 16 * 128;  // 16 key rows of 128 bytes
                     umma_bf16_a_tmem(tmem + 256 + t * 128, tmem + t * 128 + ks * 8,
                                      umma_desc(v_addr + b_off, kTcHalfBytes, 1024), idesc_pv, !(first && ks == 0));
                 }
-                umma_commit(bar_pv_done(t));
+                if (half == 1) umma_commit(bar_pv_done(t));
+            };
+            // item i of the ring: K_(i/2) for even i, V_(i/2) for odd i
+            auto wait_item = [&](int item) {
+                return mbar_wait(bar_kv_full(item % kTcStages), (item / kTcStages) & 1, abort_word, p.status, kTcWaitKvFull);
             };
             for (int t = 0; t < kTcTiles && ok; ++t)
                 if (steps[t] > 0) ok = mbar_wait(bar_q(t), 0, abort_word, p.status, kTcWaitQ);
             if (ok && nsteps > 0) {
-                ok = mbar_wait(bar_kv_full(0), 0, abort_word, p.status, kTcWaitKvFull);
+                ok = wait_item(0);
                 if (ok) {
                     tc_fence_after();
                     for (int t = 0; t < kTcTiles; ++t)
@@ -449,18 +570,28 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 bool have_v = false, have_k = false;
                 for (int t = 0; t < kTcTiles && ok; ++t) {
                     if (j >= steps[t]) continue;
+#if ELLM_TC_SPLIT_P
+                    ok = mbar_wait(bar_p_half(t), j & 1, abort_word, p.status, kTcWaitPFull);
+#else
                     ok = mbar_wait(bar_p_full(t), j & 1, abort_word, p.status, kTcWaitPFull);
+#endif
                     if (!ok) break;
                     if (!have_v) {
-                        ok = mbar_wait(bar_kv_full(slot_v), (item_v / kTcStages) & 1, abort_word, p.status, kTcWaitKvFull);
+                        ok = wait_item(item_v);
                         if (!ok) break;
                         have_v = true;
                     }
                     tc_fence_after();
-                    issue_pv(t, slot_v, j == 0);
+                    issue_pv_half(t, slot_v, j == 0, 0);
+#if ELLM_TC_SPLIT_P
+                    ok = mbar_wait(bar_p_full(t), j & 1, abort_word, p.status, kTcWaitPFull);
+                    if (!ok) break;
+                    tc_fence_after();
+#endif
+                    issue_pv_half(t, slot_v, j == 0, 1);
                     if (j + 1 < steps[t]) {
                         if (!have_k) {
-                            ok = mbar_wait(bar_kv_full(slot_k), (item_k / kTcStages) & 1, abort_word, p.status, kTcWaitKvFull);
+                            ok = wait_item(item_k);
                             if (!ok) break;
                             have_k = true;
                             tc_fence_after();
