@@ -353,86 +353,29 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const bool edge = key0 + kTcKeys - 1 > tile_min_lim;   // the causal edge crosses this tile
             const long long dlim = lim - key0;                     // last column this row may see
             const int rel = dlim < 0 ? -1 : (dlim > 127 ? 127 : static_cast<int>(dlim));
-            // pass 1 over S_t: row maximum (3-input max, two chains per 32-column chunk).  The
-            // scores are read again in pass 2 rather than kept: tensor-memory reads are cheap and
-            // 128 live registers per thread are not.
-            float mx = -INFINITY;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                float s[64];
-                tmem_ld32(tS + h * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
-                tmem_ld32(tS + h * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
-                tmem_wait_ld();
-                if (edge) {
-#pragma unroll
-                    for (int c = 0; c < 64; ++c) s[c] = (h * 64 + c <= rel) ? s[c] : -INFINITY;
-                }
-                float m0 = max3(s[0], s[1], s[2]), m1 = max3(s[3], s[4], s[5]);
-                float m2 = max3(s[6], s[7], s[8]), m3 = max3(s[9], s[10], s[11]);
-#pragma unroll
-                for (int c = 12; c < 60; c += 8) {
-                    m0 = max3(m0, s[c], s[c + 1]);
-                    m1 = max3(m1, s[c + 2], s[c + 3]);
-                    m2 = max3(m2, s[c + 4], s[c + 5]);
-                    m3 = max3(m3, s[c + 6], s[c + 7]);
-                }
-                m0 = max3(m0, s[60], s[61]);
-                m1 = max3(m1, s[62], s[63]);
-                mx = max3(mx, fmaxf(m0, m1), fmaxf(m2, m3));
-            }
-            const float m_new = fmaxf(m_used, mx * p.scale_log2);
-            // rescale O only when the maximum moved far enough to matter; otherwise keep
-            // exponentiating against the stale maximum (O and l stay consistent with it)
-            const bool need = (m_new - m_used > kTcRescaleThreshold) || (m_used == -INFINITY && m_new != -INFINITY);
-            const bool rescale = __any_sync(0xffffffffu, need);
-            float corr = 1.0f;
-            if (rescale) {
-                corr = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
-                m_used = m_new;
-            }
-            const float msub = (m_used == -INFINITY) ? 0.0f : m_used;
-            // S_t(j) complete implies P.V(t, j-1) complete (MMAs of one thread finish in issue
-            // order), so O_t can be rescaled and the columns of S_t can take P_t right away.
-            if (rescale && j > 0) {   // before any P.V of this step may start
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    float o[32];
-                    tmem_ld32(tO + c * 32, o);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] *= corr;
-                    tmem_st32(tO + c * 32, o);
-                }
-            }
-            // pass 2: p = exp2(s * scale - m) on packed pairs (a fixed share of the pairs may take
-            // the polynomial route on the FMA pipe instead of the 16-per-clock exp2 unit);
-            // P row -> tensor memory as bf16 pairs (k, k+1) per 32-bit column, 64 columns, over
-            // the first half of S_t.  The first 64 keys' P is handed to the MMA warp before the
-            // second half is computed.
-            {
-                const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-msub, -msub);
+            // Fast path (every step but the first, unless the row maximum jumps): exponentiate
+            // against the maximum already in use and track the new maximum in the same pass.  P is
+            // held in registers until the maximum is known to have moved by at most 2^8 - then it is
+            // consistent with O and l as they stand and goes to tensor memory as is.  Otherwise S_t is
+            // still intact and the two-pass slow path below redoes the step with a rescale of O_t.
+            bool slow = (j == 0) || edge;
+            if (!slow) {
+                const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_used, -m_used);
                 uint64_t sum_a = pack2(0.0f, 0.0f), sum_b = sum_a;
+                uint32_t pk[64];
+                float mxa = -INFINITY, mxb = -INFINITY;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
-                    // keys [64*half, 64*half+64) of S sit in columns [64*half, +64); their P goes to
-                    // columns [32*half, +32), which never overlap a half of S not yet read
                     float s[64];
                     tmem_ld32(tS + half * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
                     tmem_ld32(tS + half * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
                     tmem_wait_ld();
-                    if (edge) {
-#pragma unroll
-                        for (int c = 0; c < 64; ++c) s[c] = (half * 64 + c <= rel) ? s[c] : -INFINITY;
-                    }
-                    uint32_t pk[32];
 #pragma unroll
                     for (int cc = 0; cc < 32; ++cc) {
                         const int c = half * 32 + cc;
+                        if (cc & 1) mxb = max3(mxb, s[2 * cc], s[2 * cc + 1]); else mxa = max3(mxa, s[2 * cc], s[2 * cc + 1]);
                         const uint64_t x2 = fma2(pack2(s[2 * cc], s[2 * cc + 1]), scale2, negm2);
                         uint64_t p2;
-#if defined(ELLM_WHATIF_NOEXP)
-                        if (true) { p2 = x2; } else
-#endif
                         if (kTcPolyEvery > 0 && (c % kTcPolyEvery) == kTcPolyEvery - 1) {
                             p2 = exp2_poly2(x2);
                         } else {
@@ -443,20 +386,128 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         if (c & 1) sum_b = add2(sum_b, p2); else sum_a = add2(sum_a, p2);
                         float p0, p1;
                         unpack2(p2, p0, p1);
-                        pk[cc] = pack_bf16(p0, p1);
+                        pk[c] = pack_bf16(p0, p1);
                     }
-                    tmem_st32u(tS + half * 32, pk);
+                }
+                const float m_new = fmaxf(mxa, mxb) * p.scale_log2;
+                slow = __any_sync(0xffffffffu, m_new - m_used > kTcRescaleThreshold);
+                if (!slow) {
+                    float sa, sb;
+                    unpack2(add2(sum_a, sum_b), sa, sb);
+                    l += sa + sb;
+                    tmem_st32u(tS, pk);
+                    tmem_st32u(tS + 32, pk + 32);
                     tmem_wait_st();
                     tc_fence_before();
-#if ELLM_TC_SPLIT_P
-                    mbar_arrive(half == 0 ? bar_p_half(t) : bar_p_full(t));
-#else
-                    if (half == 1) mbar_arrive(bar_p_full(t));
-#endif
+                    mbar_arrive(bar_p_full(t));
                 }
-                float sa, sb;
-                unpack2(add2(sum_a, sum_b), sa, sb);
-                l = l * corr + (sa + sb);
+            }
+            if (slow) {
+                // pass 1 over S_t: row maximum (3-input max, two chains per 32-column chunk).  The
+                // scores are read again in pass 2 rather than kept: tensor-memory reads are cheap and
+                // 128 live registers per thread are not.
+                float mx = -INFINITY;
+    #pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float s[64];
+                    tmem_ld32(tS + h * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
+                    tmem_ld32(tS + h * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+                    tmem_wait_ld();
+                    if (edge) {
+    #pragma unroll
+                        for (int c = 0; c < 64; ++c) s[c] = (h * 64 + c <= rel) ? s[c] : -INFINITY;
+                    }
+                    float m0 = max3(s[0], s[1], s[2]), m1 = max3(s[3], s[4], s[5]);
+                    float m2 = max3(s[6], s[7], s[8]), m3 = max3(s[9], s[10], s[11]);
+    #pragma unroll
+                    for (int c = 12; c < 60; c += 8) {
+                        m0 = max3(m0, s[c], s[c + 1]);
+                        m1 = max3(m1, s[c + 2], s[c + 3]);
+                        m2 = max3(m2, s[c + 4], s[c + 5]);
+                        m3 = max3(m3, s[c + 6], s[c + 7]);
+                    }
+                    m0 = max3(m0, s[60], s[61]);
+                    m1 = max3(m1, s[62], s[63]);
+                    mx = max3(mx, fmaxf(m0, m1), fmaxf(m2, m3));
+                }
+                const float m_new = fmaxf(m_used, mx * p.scale_log2);
+                // rescale O only when the maximum moved far enough to matter; otherwise keep
+                // exponentiating against the stale maximum (O and l stay consistent with it)
+                const bool need = (m_new - m_used > kTcRescaleThreshold) || (m_used == -INFINITY && m_new != -INFINITY);
+                const bool rescale = __any_sync(0xffffffffu, need);
+                float corr = 1.0f;
+                if (rescale) {
+                    corr = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
+                    m_used = m_new;
+                }
+                const float msub = (m_used == -INFINITY) ? 0.0f : m_used;
+                // S_t(j) complete implies P.V(t, j-1) complete (MMAs of one thread finish in issue
+                // order), so O_t can be rescaled and the columns of S_t can take P_t right away.
+                if (rescale && j > 0) {   // before any P.V of this step may start
+    #pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float o[32];
+                        tmem_ld32(tO + c * 32, o);
+                        tmem_wait_ld();
+    #pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] *= corr;
+                        tmem_st32(tO + c * 32, o);
+                    }
+                }
+                // pass 2: p = exp2(s * scale - m) on packed pairs (a fixed share of the pairs may take
+                // the polynomial route on the FMA pipe instead of the 16-per-clock exp2 unit);
+                // P row -> tensor memory as bf16 pairs (k, k+1) per 32-bit column, 64 columns, over
+                // the first half of S_t.  The first 64 keys' P is handed to the MMA warp before the
+                // second half is computed.
+                {
+                    const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-msub, -msub);
+                    uint64_t sum_a = pack2(0.0f, 0.0f), sum_b = sum_a;
+    #pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        // keys [64*half, 64*half+64) of S sit in columns [64*half, +64); their P goes to
+                        // columns [32*half, +32), which never overlap a half of S not yet read
+                        float s[64];
+                        tmem_ld32(tS + half * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
+                        tmem_ld32(tS + half * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+                        tmem_wait_ld();
+                        if (edge) {
+    #pragma unroll
+                            for (int c = 0; c < 64; ++c) s[c] = (half * 64 + c <= rel) ? s[c] : -INFINITY;
+                        }
+                        uint32_t pk[32];
+    #pragma unroll
+                        for (int cc = 0; cc < 32; ++cc) {
+                            const int c = half * 32 + cc;
+                            const uint64_t x2 = fma2(pack2(s[2 * cc], s[2 * cc + 1]), scale2, negm2);
+                            uint64_t p2;
+    #if defined(ELLM_WHATIF_NOEXP)
+                            if (true) { p2 = x2; } else
+    #endif
+                            if (kTcPolyEvery > 0 && (c % kTcPolyEvery) == kTcPolyEvery - 1) {
+                                p2 = exp2_poly2(x2);
+                            } else {
+                                float x0, x1;
+                                unpack2(x2, x0, x1);
+                                p2 = pack2(fast_exp2(x0), fast_exp2(x1));
+                            }
+                            if (c & 1) sum_b = add2(sum_b, p2); else sum_a = add2(sum_a, p2);
+                            float p0, p1;
+                            unpack2(p2, p0, p1);
+                            pk[cc] = pack_bf16(p0, p1);
+                        }
+                        tmem_st32u(tS + half * 32, pk);
+                        tmem_wait_st();
+                        tc_fence_before();
+    #if ELLM_TC_SPLIT_P
+                        mbar_arrive(half == 0 ? bar_p_half(t) : bar_p_full(t));
+    #else
+                        if (half == 1) mbar_arrive(bar_p_full(t));
+    #endif
+                    }
+                    float sa, sb;
+                    unpack2(add2(sum_a, sum_b), sa, sb);
+                    l = l * corr + (sa + sb);
+                }
             }
         }
         if (ok && my_steps > 0) {
