@@ -13,7 +13,11 @@
 // contiguous tile range; each maximal run inside one segment is a *piece* and
 // yields one fp32 partial (O, LSE) in the workspace, slot = cta + segment (unique
 // because consecutive pieces advance the CTA index, the segment index or both).
-// merge_partials.cuh then combines the pieces of each segment.
+// merge_partials.cuh then combines the pieces of each segment; it is launched as a
+// programmatic dependent grid so that its set-up overlaps this kernel's tail.  (Merging
+// inside this kernel - the CTA that finishes a segment's last piece combines them - was
+// measured 12 us slower: the serial reads of the other pieces sit at the kernel's tail.)
+// The append of the new token's K/V row rides along in this kernel.
 //
 // Inside a CTA the 4 warps are independent streams: warp w owns keys
 // [16w, 16w+16) of every tile, copies them global->shared itself (cp.async, 16 B
@@ -51,7 +55,21 @@ struct DecodeParams {
     int gtiles;                    // ceil(group / 16)
     float scale_log2;              // scale * log2(e)
     int num_ctas;
+    // Fused KV append: when k_new is set, the new token's K/V row of sequence b (at position
+    // positions[b], or uniform_len - 1) is read from k_new / v_new [max_batch, kv_heads, 128]
+    // instead of the cache, and written into the cache by the CTA that streams it.
+    const __nv_bfloat16* k_new = nullptr;
+    const __nv_bfloat16* v_new = nullptr;
+    __nv_bfloat16* k_cache_w = nullptr;
+    __nv_bfloat16* v_cache_w = nullptr;
 };
+
+// CTA index owning tile t under assign_range(total, n, .)
+__device__ __forceinline__ long long cta_of_tile(long long total, long long n, long long t) {
+    const long long q = total / n, r = total % n;
+    if (t < (q + 1) * r) return t / (q + 1);
+    return r + (t - (q + 1) * r) / q;
+}
 
 // Keys sequence b attends: its new token sits at positions[b], so positions[b] + 1.
 __device__ __forceinline__ long long dec_seq_len(const DecodeParams& p, int b) {
@@ -97,6 +115,8 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t warp_smem = smem_u32(smem) + warp * kDecStages * kDecWarpStageBytes;
 
+    // let a dependent grid (the merge) be set up while this one runs
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     dec_build_prefix(p, prefix);
     if (blockIdx.x == 0)
         for (int i = threadIdx.x; i <= p.batch; i += kDecThreads) p.prefix_out[i] = prefix[i];
@@ -124,6 +144,11 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
         const long long key0 = p.key_begin + static_cast<long long>(tile0) * kDecTileKeys + warp * 16;
         const __nv_bfloat16* kbase = p.k_cache + b * p.s0 + kvh * p.s1;
         const __nv_bfloat16* vbase = p.v_cache + b * p.s0 + kvh * p.s1;
+        // fused append: position of the new token's row and where its K/V come from
+        long long new_pos = p.k_new ? (p.positions ? static_cast<long long>(p.positions[b]) : p.uniform_len - 1) : -1;
+        if (new_pos >= len) new_pos = -1;   // past the cache: nothing is read or written there
+        const __nv_bfloat16* knew = p.k_new ? p.k_new + (static_cast<long long>(b) * p.kv_heads + kvh) * kHeadDim : nullptr;
+        const __nv_bfloat16* vnew = p.k_new ? p.v_new + (static_cast<long long>(b) * p.kv_heads + kvh) * kHeadDim : nullptr;
 
         // ---- cp.async ring: lane copies chunk (lane&15) of rows (lane>>4) + 2*i ----
         auto issue = [&](int it) {
@@ -131,14 +156,38 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
             const uint32_t sK = warp_smem + (it % kDecStages) * kDecWarpStageBytes;
             const uint32_t sV = sK + 16 * kRowBytes;
             const int chunk = lane & 15;
+            // only the 16 keys that hold the segment's last key can contain the row being appended
+            const bool has_new = new_pos >= kfirst && new_pos < kfirst + 16;
+            if (!has_new) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int row = (lane >> 4) + 2 * i;
-                const long long key = kfirst + row;
-                const bool ok = key < len;
-                const long long off = (ok ? key : 0) * p.s2 + chunk * 8;
-                cp_async_16(sK + swz_off(row, chunk), kbase + off, ok ? 16 : 0);
-                cp_async_16(sV + swz_off(row, chunk), vbase + off, ok ? 16 : 0);
+                for (int i = 0; i < 8; ++i) {
+                    const int row = (lane >> 4) + 2 * i;
+                    const long long key = kfirst + row;
+                    const bool ok = key < len;
+                    const long long off = (ok ? key : 0) * p.s2 + chunk * 8;
+                    cp_async_16(sK + swz_off(row, chunk), kbase + off, ok ? 16 : 0);
+                    cp_async_16(sV + swz_off(row, chunk), vbase + off, ok ? 16 : 0);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int row = (lane >> 4) + 2 * i;
+                    const long long key = kfirst + row;
+                    const bool ok = key < len;
+                    const long long off = (ok ? key : 0) * p.s2 + chunk * 8;
+                    if (key == new_pos) {   // stream the new row from k_new / v_new ...
+                        cp_async_16(sK + swz_off(row, chunk), knew + chunk * 8, 16);
+                        cp_async_16(sV + swz_off(row, chunk), vnew + chunk * 8, 16);
+                        if (gt == 0) {      // ... and put it into the cache (once per KV head)
+                            const long long woff = b * p.s0 + kvh * p.s1 + key * p.s2 + chunk * 8;
+                            *reinterpret_cast<uint4*>(p.k_cache_w + woff) = *reinterpret_cast<const uint4*>(knew + chunk * 8);
+                            *reinterpret_cast<uint4*>(p.v_cache_w + woff) = *reinterpret_cast<const uint4*>(vnew + chunk * 8);
+                        }
+                    } else {
+                        cp_async_16(sK + swz_off(row, chunk), kbase + off, ok ? 16 : 0);
+                        cp_async_16(sV + swz_off(row, chunk), vbase + off, ok ? 16 : 0);
+                    }
+                }
             }
         };
 #pragma unroll

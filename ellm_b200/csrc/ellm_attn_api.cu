@@ -160,7 +160,7 @@ int launch_append(ellm_attn* h, cudaStream_t stream, void* k_cache, void* v_cach
 // Decode (interval == 1): K2 then K3.  out_f32 != nullptr selects the fp32
 // partial output of the windowed form.
 int launch_decode(ellm_attn* h, const int32_t* positions, size_t position_index, size_t batch,
-                  long long key_begin, long long key_end, float* out_f32, float* lse_out) {
+                  long long key_begin, long long key_end, float* out_f32, float* lse_out, bool append) {
     if (batch > static_cast<size_t>(ellm::kDecMaxBatch))
         return fail(ELLM_ERR_UNSUPPORTED, "decode batch %zu exceeds %d", batch, ellm::kDecMaxBatch);
     ellm::DecodeParams p;
@@ -184,6 +184,12 @@ int launch_decode(ellm_attn* h, const int32_t* positions, size_t position_index,
     p.gtiles = h->gtiles;
     p.scale_log2 = h->d.scale * ellm::kLog2e;
     p.num_ctas = h->dec_ctas;
+    if (append) {   // the new token's K/V rows ride along with the decode kernel
+        p.k_new = static_cast<const __nv_bfloat16*>(h->d.k_new);
+        p.v_new = static_cast<const __nv_bfloat16*>(h->d.v_new);
+        p.k_cache_w = static_cast<__nv_bfloat16*>(h->d.k_cache);
+        p.v_cache_w = static_cast<__nv_bfloat16*>(h->d.v_cache);
+    }
     {
         LaunchScope ls(h, ELLM_KERNEL_DECODE_SPLITKV);
         ellm::decode_splitkv_kernel<<<h->dec_ctas, ellm::kDecThreads, ellm::kDecSmemBytes, h->stream>>>(p);
@@ -191,12 +197,25 @@ int launch_decode(ellm_attn* h, const int32_t* positions, size_t position_index,
     ELLM_CUDA(cudaGetLastError());
     const unsigned blocks = static_cast<unsigned>((batch * h->d.q_heads + 3) / 4);
     {
+        // programmatic dependent launch: the merge grid is set up while the decode grid drains;
+        // its first instruction waits for the decode grid's memory to be visible
         LaunchScope ls(h, ELLM_KERNEL_MERGE);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(blocks);
+        cfg.blockDim = dim3(128);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = h->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e;
         if (out_f32)
-            ellm::decode_merge_kernel<float><<<blocks, 128, 0, h->stream>>>(p, out_f32, lse_out);
+            e = cudaLaunchKernelEx(&cfg, ellm::decode_merge_kernel<float>, p, out_f32, lse_out);
         else
-            ellm::decode_merge_kernel<__nv_bfloat16><<<blocks, 128, 0, h->stream>>>(
-                p, static_cast<__nv_bfloat16*>(h->d.out), lse_out);
+            e = cudaLaunchKernelEx(&cfg, ellm::decode_merge_kernel<__nv_bfloat16>, p, static_cast<__nv_bfloat16*>(h->d.out), lse_out);
+        if (e != cudaSuccess) return fail(ELLM_ERR_CUDA, "merge launch failed: %s", cudaGetErrorString(e));
     }
     ELLM_CUDA(cudaGetLastError());
     return ELLM_OK;
@@ -268,13 +287,14 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
     if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", h->d.device);
     std::lock_guard<std::mutex> lock(h->mu);
     int rc;
-    if (append && h->d.k_new) {
+    const bool do_append = append && h->d.k_new;
+    if (do_append && interval > 1) {   // a decode step appends inside its own kernel
         rc = launch_append(h, h->stream, h->d.k_cache, h->d.v_cache, h->d.k_new, h->d.v_new, h->d.kv_strides,
                            h->d.max_batch, h->d.kv_heads, h->d.max_seq, position_index, positions, interval, batch);
         if (rc) return rc;
     }
     if (interval == 1) {
-        rc = launch_decode(h, positions, position_index, batch, key_begin, key_end, out_f32, lse_out);
+        rc = launch_decode(h, positions, position_index, batch, key_begin, key_end, out_f32, lse_out, do_append);
     } else {
         bool use_tc = false;
         if (key_begin == 0) {

@@ -25,17 +25,13 @@ __device__ __forceinline__ void store_row4<__nv_bfloat16>(__nv_bfloat16* dst, fl
     *reinterpret_cast<uint2*>(dst) = u;
 }
 
-// CTA index owning tile t under assign_range(total, n, .)
-__device__ __forceinline__ long long cta_of_tile(long long total, long long n, long long t) {
-    const long long q = total / n, r = total % n;
-    if (t < (q + 1) * r) return t / (q + 1);
-    return r + (t - (q + 1) * r) / q;
-}
-
 // Combines the pieces the decode kernel left in its workspace.  Grid: one warp per
 // (sequence, query head).  out: [max_batch, q_heads, 128], lse: [max_batch, q_heads].
 template <typename OutT>
 __global__ void __launch_bounds__(128) decode_merge_kernel(const DecodeParams p, OutT* out, float* lse) {
+    // under a programmatic dependent launch: wait until the decode grid's writes are visible
+    // (a no-op for an ordinary launch)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
     if (row >= static_cast<long long>(p.batch) * p.q_heads) return;

@@ -44,8 +44,9 @@ def test_decode_ragged(lens, q_heads, kv_heads):
     case = Case(seed=100 + len(lens), interval=1, batch=len(lens), q_heads=q_heads, kv_heads=kv_heads,
                 max_seq=max(lens) + 3, positions=pos)
     _check(case)
-    assert case.last_stats["kv_append"][0] == 1 and case.last_stats["decode_splitkv"][0] == 1
-    assert case.last_stats["merge"][0] == 1
+    # two launches per decode step: the append rides in the decode kernel, then the merge
+    assert case.last_stats["decode_splitkv"][0] == 1 and case.last_stats["merge"][0] == 1
+    assert case.last_stats["kv_append"][0] == 0
 
 
 def test_decode_uniform_position_and_dead_batch_slots():
