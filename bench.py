@@ -182,6 +182,51 @@ def config_dict(lens):
             "per_rank": "every rank runs this workload on its own 16 sequences"}
 
 
+def measured_tensor_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d["bf16_tflops_sustained"]), "measured (MEASURED_PEAKS.json)"
+    return 1590.0, 1400.0, "fallback (no MEASURED_PEAKS.json)"
+
+
+def prefill_long(dev, stream_ptr):
+    """Secondary figure: the tcgen05 prefill kernel where it is not launch-bound - one sequence of
+    32768 tokens, 32 q / 4 kv heads (one layer of BASELINE configs[3]); Q+K+V+O = 0.3 GB > L2."""
+    from ellm_b200 import Attention
+    S, Hq, Hkv = 32768, 32, 4
+    g = torch.Generator(device=dev).manual_seed(3)
+    q = torch.randn(S, 1, Hq, D, device=dev, generator=g).to(torch.bfloat16)
+    ck = torch.randn(1, Hkv, S, D, device=dev, generator=g).to(torch.bfloat16)
+    cv = torch.randn(1, Hkv, S, D, device=dev, generator=g).to(torch.bfloat16)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(S, 1, Hq, dtype=torch.float32, device=dev)
+    op = Attention.new(q, ck, cv, out, 1, Hq, Hkv, D, [Hkv * S * D, S * D, D, 1], SCALE, max_seq=S, max_interval=S,
+                       lse=lse, device=dev.index, stream=stream_ptr, async_=True)
+    for _ in range(3):
+        op.run(0, S, 1, 1, 0)
+    torch.cuda.synchronize(dev)
+    times = []
+    for _ in range(7):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); op.run(0, S, 1, 1, 0); e1.record()
+        torch.cuda.synchronize(dev)
+        times.append(e0.elapsed_time(e1))
+    ms = statistics.median(times)
+    flops = 4 * D * Hq * S * (S + 1) / 2
+    burst, sustained, src = measured_tensor_peaks()
+    tf = flops / ms / 1e9
+    stats = op.kernel_stats()
+    op.close()
+    return {"workload": "causal prefill, seq 32768, 32 q / 4 kv heads, one layer (BASELINE configs[3] shape)",
+            "kernel": "prefill_tcgen05_kernel" if stats["prefill_tcgen05"][0] else "prefill_warp_mma_kernel",
+            "ms": ms, "tflops": tf,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": burst, "unit": "TFLOP/s", "frac": tf / burst,
+                         "frac_of_sustained_peak": tf / sustained, "frac_of_nominal_2250": tf / 2250.0,
+                         "peak_source": src + " bf16_tflops (burst: the kernel is timed alone)"}}
+
+
 def prefill_extra(dev, stream_ptr, steps, warmup):
     """Secondary figure: causal prefill of BASELINE configs[0] (seq 2048, 32/32 heads)."""
     from ellm_b200 import Attention
@@ -329,7 +374,7 @@ def main():
     ms_e2e = timed(step_host, args.steps) / args.steps
     e2e = world * total_bytes / (ms_e2e * 1e-3) / 1e9
     h2d = qh.numel() * 2 + knh.numel() * 2 + vnh.numel() * 2 + ph.numel() * 4
-    d2h = oh.numel() * 2 + lh.numel() * 4 + 4  # + the kernel status word
+    d2h = oh.numel() * 2 + lh.numel() * 4
     if not torch.isfinite(oh.float()).all():
         raise SystemExit("bench: non-finite attention output")
 
@@ -363,7 +408,8 @@ def main():
             line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
                                     "sample": "not run: host CPU lacks avx512_fp16", **cpu_info()}
     if world == 1 and not args.no_extra:
-        line["extra"] = {"prefill": prefill_extra(dev, stream.cuda_stream, args.steps, args.warmup)}
+        line["extra"] = {"prefill": prefill_extra(dev, stream.cuda_stream, args.steps, args.warmup),
+                         "prefill_long": prefill_long(dev, stream.cuda_stream)}
     print(json.dumps(line))
     if world > 1:
         dist.barrier()

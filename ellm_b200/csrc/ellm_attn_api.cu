@@ -257,6 +257,14 @@ int launch_prefill_warp_mma(ellm_attn* h, const int32_t* positions, size_t posit
     return ELLM_OK;
 }
 
+// [rows][pitch bytes] block of which `width` bytes per row are live: one flat copy when the rows are
+// contiguous (live batch == allocated batch), a pitched copy otherwise.
+cudaError_t copy_rows(void* dst, const void* src, size_t pitch, size_t width, size_t rows, cudaMemcpyKind kind,
+                      cudaStream_t stream) {
+    if (width == pitch || rows == 1) return cudaMemcpyAsync(dst, src, rows == 1 ? width : pitch * rows, kind, stream);
+    return cudaMemcpy2DAsync(dst, pitch, src, pitch, width, rows, kind, stream);
+}
+
 int finish(ellm_attn* h) {
     if (h->d.async) return ELLM_OK;
     ELLM_CUDA(cudaStreamSynchronize(h->stream));
@@ -316,7 +324,7 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
         }
     }
     if (rc) return rc;
-    if (h->status_dev && !h->d.async)
+    if (h->status_dev && !h->d.async && interval > 1)
         cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream);
     return finish(h);
 }
@@ -454,25 +462,28 @@ int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
     const size_t q_pitch = h->d.max_batch * h->d.q_heads * D * 2, q_width = batch_size * h->d.q_heads * D * 2;
     const size_t kv_pitch = h->d.max_batch * h->d.kv_heads * D * 2, kv_width = batch_size * h->d.kv_heads * D * 2;
     const size_t l_pitch = h->d.max_batch * h->d.q_heads * 4, l_width = batch_size * h->d.q_heads * 4;
-    ELLM_CUDA(cudaMemcpy2DAsync(const_cast<void*>(h->d.q), q_pitch, q_host, q_pitch, q_width, position_interval, cudaMemcpyHostToDevice, h->stream));
+    ELLM_CUDA(copy_rows(const_cast<void*>(h->d.q), q_host, q_pitch, q_width, position_interval, cudaMemcpyHostToDevice, h->stream));
     if (k_new_host) {
-        ELLM_CUDA(cudaMemcpy2DAsync(const_cast<void*>(h->d.k_new), kv_pitch, k_new_host, kv_pitch, kv_width, position_interval, cudaMemcpyHostToDevice, h->stream));
-        ELLM_CUDA(cudaMemcpy2DAsync(const_cast<void*>(h->d.v_new), kv_pitch, v_new_host, kv_pitch, kv_width, position_interval, cudaMemcpyHostToDevice, h->stream));
+        ELLM_CUDA(copy_rows(const_cast<void*>(h->d.k_new), k_new_host, kv_pitch, kv_width, position_interval, cudaMemcpyHostToDevice, h->stream));
+        ELLM_CUDA(copy_rows(const_cast<void*>(h->d.v_new), v_new_host, kv_pitch, kv_width, position_interval, cudaMemcpyHostToDevice, h->stream));
     }
     const int32_t* positions = nullptr;
     if (positions_host) {
         ELLM_CUDA(cudaMemcpyAsync(h->positions_dev, positions_host, batch_size * sizeof(int32_t), cudaMemcpyHostToDevice, h->stream));
         positions = h->positions_dev;
     }
+    const uint64_t tc_before = h->launches[ELLM_KERNEL_PREFILL_TCGEN05];
     const int was_async = h->d.async;
     h->d.async = 1;
     int rc = run_impl(h, positions, position_index, position_interval, batch_size, 0, INT64_MAX, nullptr, h->d.lse, k_new_host != nullptr);
     h->d.async = was_async;
     if (rc) return rc;
-    ELLM_CUDA(cudaMemcpy2DAsync(out_host, q_pitch, h->d.out, q_pitch, q_width, position_interval, cudaMemcpyDeviceToHost, h->stream));
+    ELLM_CUDA(copy_rows(out_host, h->d.out, q_pitch, q_width, position_interval, cudaMemcpyDeviceToHost, h->stream));
     if (lse_host)
-        ELLM_CUDA(cudaMemcpy2DAsync(lse_host, l_pitch, h->d.lse, l_pitch, l_width, position_interval, cudaMemcpyDeviceToHost, h->stream));
-    ELLM_CUDA(cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
+        ELLM_CUDA(copy_rows(lse_host, h->d.lse, l_pitch, l_width, position_interval, cudaMemcpyDeviceToHost, h->stream));
+    // only the tcgen05 kernel has device-side waits that can run out
+    const bool read_status = h->launches[ELLM_KERNEL_PREFILL_TCGEN05] != tc_before;
+    if (read_status) ELLM_CUDA(cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
     ELLM_CUDA(cudaStreamSynchronize(h->stream));
     if (*h->status_host != 0) {
         const int code = *h->status_host;
