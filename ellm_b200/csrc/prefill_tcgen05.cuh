@@ -70,7 +70,8 @@ struct TcParams {
     long long key_end;      // rows attend keys [0, min(position + 1, key_end))
     int interval, batch, max_batch;
     int q_heads, kv_heads, group;
-    int pair_tiles;         // CTAs along x = ceil(interval * group / 256)
+    int pair_tiles;         // 256-row CTA tiles per (sequence, kv head) = ceil(interval * group / 256)
+    int pair_major;         // CTA order: 1 = all heads of the heaviest tile first, 0 = head by head
     float scale_log2;
 };
 
@@ -291,8 +292,23 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kTcSmemBar + 8 * kNumBars);
     volatile int* abort_word = reinterpret_cast<volatile int*>(smem + kTcSmemBar + 8 * kNumBars + 8);
 
-    const int pair = p.pair_tiles - 1 - static_cast<int>(blockIdx.x);  // heaviest row tiles first
-    const int kvh = blockIdx.y, b = blockIdx.z;
+    // CTAs are taken in block-index order.  Later row tiles have more keys, so they go first; when
+    // all heads' K/V fit in L2 together the order is heaviest-first over the whole grid, else
+    // head by head so that one head's K/V stays resident while its row tiles are worked off.
+    int pair, kvh, b;
+    {
+        const int heads = p.kv_heads * p.batch;
+        int head;
+        if (p.pair_major) {
+            pair = p.pair_tiles - 1 - static_cast<int>(blockIdx.x / heads);
+            head = static_cast<int>(blockIdx.x % heads);
+        } else {
+            head = static_cast<int>(blockIdx.x / p.pair_tiles);
+            pair = p.pair_tiles - 1 - static_cast<int>(blockIdx.x % p.pair_tiles);
+        }
+        kvh = head % p.kv_heads;
+        b = head / p.kv_heads;
+    }
     const int total_rows = p.interval * p.group;
     int steps[kTcTiles];
 #pragma unroll
@@ -763,11 +779,15 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
     p.group = group;
     p.pair_tiles = static_cast<int>((interval * group + kTcTiles * kTcTileRows - 1) / (kTcTiles * kTcTileRows));
     p.scale_log2 = d.scale * kLog2e;
-    if (batch > 65535 || d.kv_heads > 65535) {
-        snprintf(plan.why, sizeof(plan.why), "batch / kv_heads exceed the grid limit");
+    const unsigned long long ctas = static_cast<unsigned long long>(p.pair_tiles) * p.kv_heads * p.batch;
+    if (ctas > 0x7fffffffull) {
+        snprintf(plan.why, sizeof(plan.why), "too many row tiles for one launch");
         return ELLM_ERR_UNSUPPORTED;
     }
-    dim3 grid(p.pair_tiles, p.kv_heads, p.batch);
+    // K and V rows this launch can touch, all heads and sequences together
+    const unsigned long long kv_bytes = 2ull * static_cast<unsigned long long>(kv_rows) * 256ull * d.kv_heads * batch;
+    p.pair_major = kv_bytes <= (96ull << 20) ? 1 : 0;
+    dim3 grid(static_cast<unsigned>(ctas));
     if (out_f32)
         prefill_tcgen05_kernel<float><<<grid, kTcThreads, kTcSmemBytes, stream>>>(map_q, map_k, map_v, p);
     else
