@@ -20,6 +20,7 @@
 #include "merge_partials.cuh"
 #include "prefill_warp_mma.cuh"
 #include "prefill_tcgen05.cuh"
+#include "qk_norm_rope_append.cuh"
 
 namespace {
 
@@ -539,6 +540,58 @@ int ellm_kv_append(void* cache, const void* src, const size_t kv_strides[4], siz
     if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
     return launch_append(nullptr, static_cast<cudaStream_t>(stream), cache, nullptr, src, nullptr, kv_strides, max_batch,
                          kv_heads, max_seq, position_index, positions, position_interval, batch_size);
+}
+
+int ellm_qk_norm_rope_append(const void* q_in, const void* k_in, const void* v_in, void* q_out, void* k_cache,
+                             void* v_cache, const float* q_weight, const float* k_weight, const float* rope,
+                             size_t rope_rows, const size_t kv_strides[4], size_t max_batch, size_t q_heads,
+                             size_t kv_heads, size_t head_size, size_t max_seq, size_t position_index,
+                             const int32_t* positions, size_t position_interval, size_t batch_size, float eps,
+                             int device, void* stream) {
+    if (!q_in || !k_in || !v_in || !q_out || !k_cache || !v_cache || !rope || !kv_strides)
+        return fail(ELLM_ERR_INVALID_ARG, "q_in, k_in, v_in, q_out, k_cache, v_cache, rope and kv_strides must be non-NULL");
+    if (head_size != static_cast<size_t>(ellm::kHeadDim)) return fail(ELLM_ERR_UNSUPPORTED, "head_size %zu: only 128", head_size);
+    if (kv_strides[3] != 1) return fail(ELLM_ERR_UNSUPPORTED, "kv_strides[3] must be 1");
+    for (int i = 0; i < 3; ++i)
+        if (kv_strides[i] % 8 != 0 || kv_strides[i] == 0) return fail(ELLM_ERR_INVALID_ARG, "kv_strides[%d] must be a non-zero multiple of 8 elements", i);
+    if (!aligned16(q_in) || !aligned16(k_in) || !aligned16(v_in) || !aligned16(q_out) || !aligned16(k_cache) ||
+        !aligned16(v_cache) || !aligned16(rope) || !aligned16(q_weight) || !aligned16(k_weight))
+        return fail(ELLM_ERR_INVALID_ARG, "buffers must be 16-byte aligned");
+    if (q_heads == 0 || kv_heads == 0 || max_batch == 0) return fail(ELLM_ERR_INVALID_ARG, "q_heads, kv_heads, max_batch must be > 0");
+    if (batch_size > max_batch) return fail(ELLM_ERR_INVALID_ARG, "batch_size %zu > max_batch %zu", batch_size, max_batch);
+    if (!positions && position_index + position_interval > max_seq)
+        return fail(ELLM_ERR_INVALID_ARG, "position_index %zu + interval %zu exceeds max_seq %zu", position_index, position_interval, max_seq);
+    if (!positions && position_index + position_interval > rope_rows)
+        return fail(ELLM_ERR_INVALID_ARG, "the rope table has %zu rows, position %zu is needed", rope_rows, position_index + position_interval - 1);
+    if (!(eps >= 0.0f)) return fail(ELLM_ERR_INVALID_ARG, "eps must be >= 0");
+    if (position_interval == 0 || batch_size == 0) return ELLM_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    ellm::NormRopeParams p;
+    p.q_in = static_cast<const __nv_bfloat16*>(q_in);
+    p.k_in = static_cast<const __nv_bfloat16*>(k_in);
+    p.v_in = static_cast<const __nv_bfloat16*>(v_in);
+    p.q_out = static_cast<__nv_bfloat16*>(q_out);
+    p.k_cache = static_cast<__nv_bfloat16*>(k_cache);
+    p.v_cache = static_cast<__nv_bfloat16*>(v_cache);
+    p.q_weight = q_weight; p.k_weight = k_weight; p.rope = rope;
+    p.positions = positions;
+    p.position_index = static_cast<long long>(position_index);
+    p.s0 = kv_strides[0]; p.s1 = kv_strides[1]; p.s2 = kv_strides[2];
+    p.max_seq = static_cast<long long>(max_seq);
+    p.rope_rows = static_cast<long long>(rope_rows);
+    p.interval = static_cast<int>(position_interval);
+    p.batch = static_cast<int>(batch_size);
+    p.max_batch = static_cast<int>(max_batch);
+    p.q_heads = static_cast<int>(q_heads);
+    p.kv_heads = static_cast<int>(kv_heads);
+    p.eps = eps;
+    const long long warps = static_cast<long long>(position_interval) * batch_size * (q_heads + 2 * kv_heads);
+    const long long blocks = (warps + 7) / 8;
+    if (blocks > 0x7fffffffll) return fail(ELLM_ERR_UNSUPPORTED, "too many rows for one launch");
+    ellm::qk_norm_rope_append_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    ELLM_CUDA(cudaGetLastError());
+    return ELLM_OK;
 }
 
 static int merge_partials_impl(const float* o_parts, const float* lse_parts, size_t parts, size_t rows,

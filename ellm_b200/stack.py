@@ -1,0 +1,193 @@
+"""Attention-only decoder stack: the callers either side of the attention operator.
+
+Per layer, following the reference's decoder layer and attention block minus the MoE part
+(src/qwen3_moe/decoder_layer.rs:139-165, src/qwen3_moe/attention.rs:126-196):
+
+    h   = rms(x)                                   input norm, weight-free (generic/rms_norm.rs:6-26)
+    q,k,v = h Wq^T, h Wk^T, h Wv^T                 matmul3 (src/compiler/mul/matmul3.rs:289-385)
+    q,k = rope(qk_norm(q, k)); cache <- k, v       ellm_qk_norm_rope_append
+    a   = Attention(q, cache)                      ellm_attn_run
+    x   = x + a Wo^T                               matmul_add (src/compiler/mul/matmul_add.rs:186-226)
+
+The projections and the input norm are library calls (torch / cuBLAS): they are the path's
+neighbours, not the path.  The norm+rope+append step and attention are this repository's
+kernels.  Decode steps can be captured once in a CUDA graph and replayed: every kernel takes
+the per-sequence positions from a device array that the graph itself advances.
+"""
+import numpy as np
+import torch
+
+from . import _lib as L
+from .attention import Attention, qk_norm_rope_append
+from .kv_cache import StaticKVCache
+from .rope import precompute_freqs_cis
+
+
+def rms(x, eps):
+    """y = x / (sqrt(mean x^2) + eps) over the last dimension, fp32 inside, bf16 out."""
+    xf = x.float()
+    return (xf / (xf.pow(2).mean(-1, keepdim=True).sqrt() + eps)).to(torch.bfloat16)
+
+
+class AttentionStack:
+    def __init__(self, layers, hidden, q_heads, kv_heads, max_seq, max_interval, *, head_dim=128, theta=1e6,
+                 eps=1e-6, seed=3, device="cuda:0", stream=None, max_batch=1):
+        dev = torch.device(device)
+        self.dev, self.layers, self.hidden = dev, layers, hidden
+        self.q_heads, self.kv_heads, self.head_dim = q_heads, kv_heads, head_dim
+        self.max_seq, self.max_interval, self.max_batch, self.eps = max_seq, max_interval, max_batch, eps
+        self.stream = stream if stream is not None else torch.cuda.current_stream(dev)
+        g = torch.Generator(device=dev).manual_seed(seed)
+
+        def w(*shape, std=0.02, mean=0.0, dtype=torch.bfloat16):
+            return (torch.randn(*shape, device=dev, generator=g) * std + mean).to(dtype)
+
+        qd, kd = q_heads * head_dim, kv_heads * head_dim
+        # N x K row-major, like the reference's W_nt (matmul3.rs:22-28)
+        self.wq = [w(qd, hidden) for _ in range(layers)]
+        self.wk = [w(kd, hidden) for _ in range(layers)]
+        self.wv = [w(kd, hidden) for _ in range(layers)]
+        self.wo = [w(hidden, qd) for _ in range(layers)]
+        self.q_norm = [w(head_dim, mean=1.0, dtype=torch.float32) for _ in range(layers)]
+        self.k_norm = [w(head_dim, mean=1.0, dtype=torch.float32) for _ in range(layers)]
+        self.rope = torch.from_numpy(precompute_freqs_cis(head_dim, max_seq, theta)).to(dev)
+        self.cache = StaticKVCache(layers, max_batch, kv_heads, max_seq, head_dim, device=dev)
+        rows = max_interval * max_batch
+        self.q = torch.zeros(max_interval, max_batch, q_heads, head_dim, dtype=torch.bfloat16, device=dev)
+        self.k = torch.zeros(max_interval, max_batch, kv_heads, head_dim, dtype=torch.bfloat16, device=dev)
+        self.v = torch.zeros_like(self.k)
+        self.a = torch.zeros_like(self.q)
+        self.positions = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+        self.scale = 1.0 / np.sqrt(head_dim)
+        self.ops = []
+        for i in range(layers):
+            ck, cv = self.cache.layer(i)
+            self.ops.append(Attention.new(self.q, ck, cv, self.a, max_batch, q_heads, kv_heads, head_dim,
+                                          self.cache.strides, self.scale, max_seq=max_seq, max_interval=max_interval,
+                                          device=dev.index or 0, stream=self.stream.cuda_stream, async_=True))
+        self._rows = rows
+
+    def _layer(self, i, x, n, batch, position_index, ragged):
+        """x: [n * max_batch, hidden] bf16 (rows ordered chunk row, then sequence)."""
+        rows = n * self.max_batch
+        h = rms(x, self.eps)
+        q, k, v, a = self.q[:n], self.k[:n], self.v[:n], self.a[:n]
+        torch.matmul(h, self.wq[i].t(), out=q.view(rows, -1))
+        torch.matmul(h, self.wk[i].t(), out=k.view(rows, -1))
+        torch.matmul(h, self.wv[i].t(), out=v.view(rows, -1))
+        ck, cv = self.cache.layer(i)
+        qk_norm_rope_append(q, k, v, q, ck, cv, self.rope, self.cache.strides, self.max_batch, self.q_heads,
+                            self.kv_heads, self.head_dim, self.max_seq, position_index, n, batch, self.eps,
+                            q_weight=self.q_norm[i], k_weight=self.k_norm[i],
+                            positions=self.positions if ragged else None, device=self.dev.index or 0,
+                            stream=self.stream.cuda_stream)
+        if ragged:
+            self.ops[i].run_ragged(self.positions, n, batch, 1, 0)
+        else:
+            self.ops[i].run(position_index, n, batch, 1, 0)
+        return torch.addmm(x, a.view(rows, -1), self.wo[i].t())
+
+    def forward(self, x, position_index, batch=None, ragged=False):
+        """One pass of all layers over a chunk: x [n, max_batch, hidden] -> same shape."""
+        n = x.shape[0]
+        batch = self.max_batch if batch is None else batch
+        y = x.reshape(n * self.max_batch, self.hidden)
+        with torch.cuda.stream(self.stream):
+            for i in range(self.layers):
+                y = self._layer(i, y, n, batch, position_index, ragged)
+        return y.view(n, self.max_batch, self.hidden)
+
+    def capture_decode_step(self, x_static):
+        """Captures one decode step (all layers, positions read from self.positions and advanced
+        by one at the end) into a CUDA graph; returns (graph, output tensor).  Replay with
+        graph.replay() after writing the step's input into x_static."""
+        # warm up outside the capture (library handles, cuBLAS workspaces)
+        saved = self.positions.clone()
+        for _ in range(2):
+            self.forward(x_static, 0, ragged=True)
+        self.stream.synchronize()
+        self.positions.copy_(saved)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=self.stream):
+            out = self.forward(x_static, 0, ragged=True)
+            self.positions.add_(1)
+        return graph, out
+
+    def close(self):
+        for op in self.ops:
+            op.close()
+
+
+def main():
+    """TTFT / TPOT of the attention path on the 48-layer stack (BASELINE configs[3] by default):
+
+        python -m ellm_b200.stack --layers 48 --prefill 32768 --decode 256
+    """
+    import argparse
+    import json
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--hidden", type=int, default=2048)
+    ap.add_argument("--q-heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=4)
+    ap.add_argument("--prefill", type=int, default=32768)
+    ap.add_argument("--decode", type=int, default=256)
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    stream = torch.cuda.Stream(dev)
+    S = args.prefill
+    max_seq = S + args.decode + 8
+    stack = AttentionStack(args.layers, args.hidden, args.q_heads, args.kv_heads, max_seq, S, stream=stream)
+    g = torch.Generator(device=dev).manual_seed(3)
+    x0 = torch.randn(S, 1, args.hidden, device=dev, generator=g).to(torch.bfloat16)
+    with torch.cuda.stream(stream):
+        stack.forward(x0, 0)            # warm-up pass (also fills the cache)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        y = stack.forward(x0, 0)
+        e1.record(stream)
+    stream.synchronize()
+    ttft = e0.elapsed_time(e1)
+    flops_attn = 4 * 128 * args.q_heads * S * (S + 1) / 2 * args.layers
+    flops_proj = 2 * S * args.hidden * (args.q_heads * 128 * 2 + args.kv_heads * 128 * 2) * args.layers
+    # decode: positions start at S; the graph advances them
+    x1 = y[-1:].clone()
+    stack.positions.fill_(S)
+    times = []
+    with torch.cuda.stream(stream):
+        if args.no_graph:
+            for _ in range(args.decode):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                x1 = stack.forward(x1, 0, ragged=True)
+                stack.positions.add_(1)
+                e1.record(stream)
+                stream.synchronize()
+                times.append(e0.elapsed_time(e1))
+        else:
+            graph, out = stack.capture_decode_step(x1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(args.decode):
+                graph.replay()
+                x1.copy_(out)
+            e1.record(stream)
+            stream.synchronize()
+            times = [e0.elapsed_time(e1) / args.decode]
+    tpot = float(np.mean(times))
+    kv_bytes = 2 * args.kv_heads * 128 * 2 * (S + args.decode / 2) * args.layers
+    w_bytes = 2 * args.hidden * (args.q_heads * 128 * 2 + args.kv_heads * 128 * 2) * args.layers
+    print(json.dumps({
+        "workload": f"{args.layers}-layer attention-only stack, hidden {args.hidden}, {args.q_heads} q / {args.kv_heads} kv heads, "
+                    f"prefill {S} then {args.decode} decode steps, 1 sequence, synthetic weights and activations",
+        "ttft_ms": ttft, "prefill_tflops": (flops_attn + flops_proj) / ttft / 1e9,
+        "prefill_attention_flops_share": flops_attn / (flops_attn + flops_proj),
+        "tpot_ms": tpot, "decode_gbs": (kv_bytes + w_bytes) / tpot / 1e6, "decode_cuda_graph": not args.no_graph,
+        "final_positions": int(stack.positions[0]), "finite": bool(torch.isfinite(x1.float()).all())}))
+    stack.close()
+
+
+if __name__ == "__main__":
+    main()

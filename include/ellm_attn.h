@@ -128,6 +128,25 @@ int ellm_kv_append(void* cache, const void* src, const size_t kv_strides[4], siz
                    const int32_t* positions, size_t position_interval, size_t batch_size,
                    int device, void* stream);
 
+/* The step between the QKV projection and attention, fused: per-head RMSNorm
+ * (y = x / (sqrt(mean x^2) + eps), src/kernel/generic/rms_norm.rs:6-26), interleaved RoPE
+ * (src/kernel/generic/complex_mul.rs:3-20) on every Q and K head - the reference's
+ * matmul_finalize_rmsnorm_rope_inplace_3x128, src/kernel/x86_64/f16_512/
+ * matmul_rms_complex.rs:76-96 - and the write of K and V into the cache at the chunk's
+ * positions (output_to_kv, src/compiler/zip_map/complex_zip.rs:92-98).
+ * q_in/q_out [rows, max_batch, q_heads, 128] (may alias), k_in/v_in [rows, max_batch, kv_heads,
+ * 128], bf16; q_weight/k_weight fp32[128] or NULL (the reference's norm has no weight);
+ * rope fp32 [rope_rows, 128] of interleaved (cos, sin), row = absolute position
+ * (src/qwen3_moe/rope.rs:7-28); positions as in ellm_attn_run_ragged or NULL. */
+int ellm_qk_norm_rope_append(const void* q_in, const void* k_in, const void* v_in, void* q_out,
+                             void* k_cache, void* v_cache, const float* q_weight,
+                             const float* k_weight, const float* rope, size_t rope_rows,
+                             const size_t kv_strides[4], size_t max_batch, size_t q_heads,
+                             size_t kv_heads, size_t head_size, size_t max_seq,
+                             size_t position_index, const int32_t* positions,
+                             size_t position_interval, size_t batch_size, float eps, int device,
+                             void* stream);
+
 /* Combine `parts` partial results of the same query rows taken over disjoint key
  * sets: L = log sum_i exp(L_i), O = sum_i O_i exp(L_i - L).  No counterpart in the
  * reference (it never splits the key range); it is the exchange step of the

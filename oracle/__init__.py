@@ -15,5 +15,7 @@ from .binding import (  # noqa: F401
     kv_append_bf16,
     load,
     merge_partials,
+    qk_norm_rope_append_bf16,
+    rope_table,
     softmax_attention_f64,
 )

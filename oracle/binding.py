@@ -50,6 +50,15 @@ def load():
     lib.oracle_kv_append_bf16.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_size_t)] + [C.c_size_t] * 6 + [C.c_void_p]
     lib.oracle_merge_partials_f32.restype = None
     lib.oracle_merge_partials_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p]
+    lib.oracle_rms_norm_f32.restype = None
+    lib.oracle_rms_norm_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_float]
+    lib.oracle_complex_mul_f32.restype = None
+    lib.oracle_complex_mul_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
+    lib.oracle_precompute_freqs_cis.restype = None
+    lib.oracle_precompute_freqs_cis.argtypes = [C.c_size_t, C.c_size_t, C.c_float, C.c_void_p, C.c_int]
+    lib.oracle_qk_norm_rope_append_bf16.restype = None
+    lib.oracle_qk_norm_rope_append_bf16.argtypes = ([C.c_void_p] * 9 + [C.POINTER(C.c_size_t)] + [C.c_size_t] * 5
+                                                     + [C.c_void_p, C.c_size_t, C.c_size_t, C.c_float])
     lib.oracle_f32_to_bf16.restype = C.c_uint16
     lib.oracle_f32_to_bf16.argtypes = [C.c_float]
     lib.oracle_f16_available.restype = C.c_int
@@ -190,3 +199,29 @@ def softmax_attention_f64(q, K, V, scale):
     p = np.exp(s - m)
     d = p.sum()
     return (p / d) @ V.astype(np.float64), m + np.log(d)
+
+
+def rope_table(dim, rows, theta, faithful_to_polar=False):
+    """[rows, dim] float32 of interleaved (cos, sin) pairs (precompute_freqs_cis)."""
+    out = np.zeros((rows, dim), dtype=np.float32)
+    load().oracle_precompute_freqs_cis(dim, rows, theta, _ptr(out), int(faithful_to_polar))
+    return out
+
+
+def qk_norm_rope_append_bf16(q_in, k_in, v_in, k_cache, v_cache, rope, kv_strides, q_heads, kv_heads,
+                             position_index, position_interval, batch_size, eps, q_weight=None,
+                             k_weight=None, positions=None, max_batch=None):
+    """RMSNorm + RoPE on the Q and K heads, K and V written into the caches (in place); returns q_out."""
+    q_in = np.ascontiguousarray(q_in, dtype=np.uint16)
+    interval, mb, hq, d = q_in.shape
+    max_batch = mb if max_batch is None else max_batch
+    q_out = np.zeros_like(q_in)
+    pos = None if positions is None else np.ascontiguousarray(positions, dtype=np.int32)
+    qw = None if q_weight is None else np.ascontiguousarray(q_weight, dtype=np.float32)
+    kw = None if k_weight is None else np.ascontiguousarray(k_weight, dtype=np.float32)
+    rope = np.ascontiguousarray(rope, dtype=np.float32)
+    load().oracle_qk_norm_rope_append_bf16(
+        _ptr(q_in), _ptr(np.ascontiguousarray(k_in, dtype=np.uint16)), _ptr(np.ascontiguousarray(v_in, dtype=np.uint16)),
+        _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(qw), _ptr(kw), _ptr(rope), (C.c_size_t * 4)(*kv_strides),
+        max_batch, q_heads, kv_heads, d, position_index, _ptr(pos), position_interval, batch_size, eps)
+    return q_out

@@ -16,6 +16,10 @@
 //   oracle_kv_append              row write at [position] with the semantics of
 //                                 the output_to_kv branch,
 //                                 src/compiler/zip_map/complex_zip.rs:92-98
+//   oracle_rms_norm_f32           src/kernel/generic/rms_norm.rs:6-26
+//   oracle_complex_mul_f32        src/kernel/generic/complex_mul.rs:3-20
+//   oracle_precompute_freqs_cis   src/qwen3_moe/rope.rs:7-28
+//   oracle_qk_norm_rope_append    src/kernel/x86_64/f16_512/matmul_rms_complex.rs:76-96
 //
 // Pinning.  The reference's own tests for this path hold only uniform-input
 // known-answer cases (all-ones attention -> all-ones output, 1*1+2*2=5,
@@ -305,6 +309,94 @@ void oracle_merge_partials_f32(const float* o_parts, const float* lse_parts, siz
         }
         lse[r] = L;
     }
+}
+
+// ---- the step before attention: per-head RMSNorm + interleaved RoPE + cache write ----
+
+// src/kernel/generic/rms_norm.rs:6-26: y = x / (sqrt(mean(x^2)) + eps) - note eps is added to
+// the root, not under it, and there is no weight.
+void oracle_rms_norm_f32(const float* input, float* output, size_t length, float eps) {
+    float sum = input[0] * input[0];
+    for (size_t i = 1; i < length; ++i) sum = sum + input[i] * input[i];
+    const float variance = sum / static_cast<float>(length);
+    const float rrms = 1.0f / (std::sqrt(variance) + eps);
+    for (size_t i = 0; i < length; ++i) output[i] = input[i] * rrms;
+}
+
+// src/kernel/generic/complex_mul.rs:3-20: interleaved pairs (x[2j], x[2j+1]) * (r[2j], r[2j+1]).
+void oracle_complex_mul_f32(const float* a, const float* b, float* out, size_t length) {
+    for (size_t i = 0; i < length; i += 2) {
+        const float x = a[i], y = a[i + 1], c = b[i], d = b[i + 1];
+        const float e = x * c - y * d;
+        const float f = x * d + y * c;
+        out[i] = e;
+        out[i + 1] = f;
+    }
+}
+
+// src/qwen3_moe/rope.rs:7-28: freq_j = 1 / theta^(2j/dim) in f32, angle = t * freq_j, row t =
+// [cos, sin] pairs.  The reference builds each entry with Complex::new(1, angle).to_polar(),
+// which yields (sqrt(1 + angle^2), atan(angle)) rather than a unit phasor; the table is not
+// used anywhere in that snapshot.  This restatement writes (cos angle, sin angle), the phasor
+// the complex multiply needs; faithful_to_polar != 0 reproduces the reference's text.
+void oracle_precompute_freqs_cis(size_t dim, size_t rows, float theta, float* out, int faithful_to_polar) {
+    std::vector<float> freqs;
+    for (size_t x = 0; x < dim; x += 2) {
+        const float p = static_cast<float>(x) / static_cast<float>(dim);
+        freqs.push_back(1.0f / std::pow(theta, p));
+    }
+    for (size_t t = 0; t < rows; ++t)
+        for (size_t j = 0; j < freqs.size(); ++j) {
+            const float angle = static_cast<float>(t) * freqs[j];
+            float* o = out + (t * freqs.size() + j) * 2;
+            if (faithful_to_polar) {
+                o[0] = std::sqrt(1.0f + angle * angle);
+                o[1] = std::atan2(angle, 1.0f);
+            } else {
+                o[0] = std::cos(angle);
+                o[1] = std::sin(angle);
+            }
+        }
+}
+
+// The finalize step of the fused QKV projection (src/kernel/x86_64/f16_512/
+// matmul_rms_complex.rs:76-96: RMSNorm then RoPE on every 128-wide head of Q and K, in place)
+// followed by the write of K and V into the cache at the chunk's positions (output_to_kv,
+// src/compiler/zip_map/complex_zip.rs:92-98).  The rope row of chunk row h is position + h
+// (complex_zip.rs:100,126).  q_weight / k_weight (may be NULL = the reference's weight-free
+// norm) multiply the normalised head before the rotation.  bf16 in, fp32 arithmetic, bf16 out.
+void oracle_qk_norm_rope_append_bf16(const uint16_t* q_in, const uint16_t* k_in, const uint16_t* v_in,
+                                     uint16_t* q_out, uint16_t* k_cache, uint16_t* v_cache,
+                                     const float* q_weight, const float* k_weight, const float* rope,
+                                     const size_t* kv_strides, size_t max_batch, size_t q_heads,
+                                     size_t kv_heads, size_t head_size, size_t position_index,
+                                     const int32_t* positions, size_t position_interval, size_t batch_size,
+                                     float eps) {
+    const size_t D = head_size;
+    std::vector<float> x(D), y(D);
+    auto head = [&](const uint16_t* src, const float* w, const float* rope_row, uint16_t* dst, size_t dst_stride) {
+        for (size_t c = 0; c < D; ++c) x[c] = bf16_to_f32(src[c]);
+        oracle_rms_norm_f32(x.data(), y.data(), D, eps);
+        if (w)
+            for (size_t c = 0; c < D; ++c) y[c] = y[c] * w[c];
+        oracle_complex_mul_f32(y.data(), rope_row, x.data(), D);
+        for (size_t c = 0; c < D; ++c) dst[c * dst_stride] = f32_to_bf16(x[c]);
+    };
+    for (size_t h = 0; h < position_interval; ++h)
+        for (size_t b = 0; b < batch_size; ++b) {
+            const size_t pos = (positions ? static_cast<size_t>(positions[b]) : position_index) + h;
+            const float* rope_row = rope + pos * D;
+            for (size_t qh = 0; qh < q_heads; ++qh) {
+                const size_t off = ((h * max_batch + b) * q_heads + qh) * D;
+                head(q_in + off, q_weight, rope_row, q_out + off, 1);
+            }
+            for (size_t kvh = 0; kvh < kv_heads; ++kvh) {
+                const size_t off = ((h * max_batch + b) * kv_heads + kvh) * D;
+                const size_t dst = b * kv_strides[0] + kvh * kv_strides[1] + pos * kv_strides[2];
+                head(k_in + off, k_weight, rope_row, k_cache + dst, kv_strides[3]);
+                for (size_t c = 0; c < D; ++c) v_cache[dst + c * kv_strides[3]] = v_in[off + c];
+            }
+        }
 }
 
 uint16_t oracle_f32_to_bf16(float f) { return f32_to_bf16(f); }

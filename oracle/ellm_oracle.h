@@ -41,6 +41,16 @@ void oracle_kv_append_bf16(uint16_t* cache, const uint16_t* src, const size_t* k
                            const int32_t* positions);
 void oracle_merge_partials_f32(const float* o_parts, const float* lse_parts, size_t parts,
                                size_t rows, size_t head_size, float* o, float* lse);
+void oracle_rms_norm_f32(const float* input, float* output, size_t length, float eps);
+void oracle_complex_mul_f32(const float* a, const float* b, float* out, size_t length);
+void oracle_precompute_freqs_cis(size_t dim, size_t rows, float theta, float* out, int faithful_to_polar);
+void oracle_qk_norm_rope_append_bf16(const uint16_t* q_in, const uint16_t* k_in, const uint16_t* v_in,
+                                     uint16_t* q_out, uint16_t* k_cache, uint16_t* v_cache,
+                                     const float* q_weight, const float* k_weight, const float* rope,
+                                     const size_t* kv_strides, size_t max_batch, size_t q_heads,
+                                     size_t kv_heads, size_t head_size, size_t position_index,
+                                     const int32_t* positions, size_t position_interval, size_t batch_size,
+                                     float eps);
 uint16_t oracle_f32_to_bf16(float f);
 float oracle_bf16_to_f32(uint16_t h);
 

@@ -1,0 +1,82 @@
+"""The fused RMSNorm + RoPE + cache-write kernel against the CPU oracle (B200 only).
+
+The kernel sums the squares with a warp butterfly, the oracle sequentially, so a normalised
+value may land one bf16 step away; V rows and everything the kernel must not touch are
+bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+import ellm_b200
+import oracle
+from helpers import bits, from_bits
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(seed, S, B, max_batch, Hq, Hkv, max_seq, position_index=0, positions=None, weights=True):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(S, max_batch, Hq, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(S, max_batch, Hkv, 128, generator=g).to(torch.bfloat16)
+    v = torch.randn(S, max_batch, Hkv, 128, generator=g).to(torch.bfloat16)
+    ck = torch.randn(max_batch, Hkv, max_seq, 128, generator=g).to(torch.bfloat16)   # canaries
+    cv = torch.randn(max_batch, Hkv, max_seq, 128, generator=g).to(torch.bfloat16)
+    qw = (1 + 0.02 * torch.randn(128, generator=g)).float() if weights else None
+    kw = (1 + 0.02 * torch.randn(128, generator=g)).float() if weights else None
+    rope = ellm_b200.precompute_freqs_cis(128, max_seq, 1e6)
+    strides = [Hkv * max_seq * 128, max_seq * 128, 128, 1]
+    want_ck, want_cv = bits(ck).copy(), bits(cv).copy()
+    want_q = oracle.qk_norm_rope_append_bf16(bits(q), bits(k), bits(v), want_ck, want_cv, rope, strides, Hq, Hkv,
+                                             position_index, S, B, 1e-6, q_weight=None if qw is None else qw.numpy(),
+                                             k_weight=None if kw is None else kw.numpy(), positions=positions, max_batch=max_batch)
+    dev = torch.device("cuda:0")
+    dq, dck, dcv = q.to(dev), ck.to(dev), cv.to(dev)
+    q_out = torch.zeros_like(dq)
+    pos = None if positions is None else torch.tensor(positions, dtype=torch.int32, device=dev)
+    ellm_b200.qk_norm_rope_append(dq, k.to(dev), v.to(dev), q_out, dck, dcv, torch.from_numpy(rope).to(dev), strides,
+                                  max_batch, Hq, Hkv, 128, max_seq, position_index, S, B, 1e-6,
+                                  q_weight=None if qw is None else qw.to(dev), k_weight=None if kw is None else kw.to(dev),
+                                  positions=pos)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(dcv), want_cv), "V rows / untouched rows differ"
+    for got, want in ((bits(q_out)[:, :B], want_q[:, :B]), (bits(dck), want_ck)):
+        g32, w32 = oracle.bf16_bits_to_f32(got), oracle.bf16_bits_to_f32(want)
+        assert np.isfinite(g32).all()
+        exact = (got == want).mean()
+        assert exact >= 0.98, exact
+        assert (np.abs(g32 - w32) <= np.abs(w32) * 2.0 ** -7 + 1e-30).all()   # at most one bf16 step
+    assert (bits(q_out)[:, B:] == 0).all()   # dead batch slots untouched
+
+
+@pytest.mark.parametrize("weights", [True, False])
+def test_prefill_chunk(weights):
+    _case(1, S=37, B=2, max_batch=3, Hq=8, Hkv=2, max_seq=64, position_index=9, weights=weights)
+
+
+def test_decode_ragged_positions():
+    _case(2, S=1, B=3, max_batch=3, Hq=32, Hkv=4, max_seq=300, positions=[0, 299, 128])
+
+
+def test_feeds_attention_end_to_end():
+    """norm+rope+append then attention == the oracle's two steps chained."""
+    dev = torch.device("cuda:0")
+    S, B, Hq, Hkv, max_seq = 150, 1, 8, 2, 160
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(S, B, Hq, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(S, B, Hkv, 128, generator=g).to(torch.bfloat16)
+    v = torch.randn(S, B, Hkv, 128, generator=g).to(torch.bfloat16)
+    rope = ellm_b200.precompute_freqs_cis(128, max_seq, 1e6)
+    strides = [Hkv * max_seq * 128, max_seq * 128, 128, 1]
+    ck = np.zeros((B, Hkv, max_seq, 128), np.uint16); cv = np.zeros_like(ck)
+    want_q = oracle.qk_norm_rope_append_bf16(bits(q), bits(k), bits(v), ck, cv, rope, strides, Hq, Hkv, 0, S, B, 1e-6)
+    scale = 1 / np.sqrt(128.0)
+    want_o, want_l = oracle.attention_bf16(want_q, ck, cv, strides, Hq, Hkv, scale, 0, S, B)
+    dq = q.to(dev); dck = torch.zeros(B, Hkv, max_seq, 128, dtype=torch.bfloat16, device=dev); dcv = torch.zeros_like(dck)
+    out = torch.zeros_like(dq); lse = torch.zeros(S, B, Hq, dtype=torch.float32, device=dev)
+    ellm_b200.qk_norm_rope_append(dq, k.to(dev), v.to(dev), dq, dck, dcv, torch.from_numpy(rope).to(dev), strides, B, Hq, Hkv,
+                                  128, max_seq, 0, S, B, 1e-6)   # in place on q
+    op = ellm_b200.Attention.new(dq, dck, dcv, out, B, Hq, Hkv, 128, strides, scale, max_seq=max_seq, max_interval=S, lse=lse)
+    op.run(0, S, B, 1, 0)
+    d = np.abs(out.float().cpu().numpy() - oracle.bf16_bits_to_f32(want_o))
+    assert d.max() <= 2e-2 and d.mean() <= 2e-3
+    assert np.abs(lse.cpu().numpy() - want_l).max() <= 2e-2   # one-bf16-step differences in normalised Q/K move the scores

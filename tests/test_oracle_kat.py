@@ -147,3 +147,60 @@ def test_merge_partials_equals_unsplit():
         parts_o.append(o[None]); parts_l.append([l])
     o, l = oracle.merge_partials(np.stack(parts_o), np.array(parts_l))
     assert np.abs(o[0] - full).max() < 1e-5 and abs(l[0] - full_lse) < 1e-5
+
+
+def test_rms_norm_kat(oracle_lib):
+    # src/kernel/generic/rms_norm.rs:52-88: input 1..18, eps 1e-6, within 4 ulps
+    x = np.arange(1, 19, dtype=np.float32)
+    y = np.zeros_like(x)
+    oracle_lib.oracle_rms_norm_f32(x.ctypes.data, y.ctypes.data, 18, 1e-6)
+    want = np.array([0.09238425642251968, 0.18476851284503937, 0.27715277671813965, 0.36953702569007874,
+                     0.4619212746620178, 0.5543055534362793, 0.646689772605896, 0.7390740513801575,
+                     0.831458330154419, 0.9238425493240356, 1.0162267684936523, 1.1086111068725586,
+                     1.2009953260421753, 1.293379545211792, 1.3857638835906982, 1.478148102760315,
+                     1.5705323219299316, 1.662916660308838], dtype=np.float32)
+    ulps = np.abs(y.view(np.int32).astype(np.int64) - want.view(np.int32).astype(np.int64))
+    assert ulps.max() <= 4
+
+
+def test_complex_mul_kat(oracle_lib):
+    # src/kernel/generic/complex_mul.rs:29-48: (k + i(k+1))^2 for 17 pairs
+    a = np.arange(1, 35, dtype=np.float32)
+    out = np.zeros_like(a)
+    oracle_lib.oracle_complex_mul_f32(a.ctypes.data, a.ctypes.data, out.ctypes.data, 34)
+    want = np.array([-3, 4, -7, 24, -11, 60, -15, 112, -19, 180, -23, 264, -27, 364, -31, 480, -35, 612, -39, 760,
+                     -43, 924, -47, 1104, -51, 1300, -55, 1512, -59, 1740, -63, 1984, -67, 2244], dtype=np.float32)
+    assert np.array_equal(out, want)
+
+
+def test_rope_table_is_a_unit_phasor_and_the_reference_text_is_not():
+    t = oracle.rope_table(128, 64, 1e6)
+    assert np.abs(t[:, 0::2] ** 2 + t[:, 1::2] ** 2 - 1).max() < 1e-6
+    assert np.array_equal(t[0], np.tile(np.array([1, 0], np.float32), 64))
+    assert abs(t[5, 0] - np.cos(5.0)) < 1e-6 and abs(t[5, 1] - np.sin(5.0)) < 1e-6   # freq_0 = 1
+    bad = oracle.rope_table(128, 64, 1e6, faithful_to_polar=True)   # rope.rs:22-24 as written: (|1+ia|, arg)
+    assert abs(bad[5, 0] - np.sqrt(26.0)) < 1e-5 and abs(bad[5, 1] - np.arctan(5.0)) < 1e-6
+    import ellm_b200
+    assert np.abs(ellm_b200.precompute_freqs_cis(128, 4096, 1e6) - oracle.rope_table(128, 4096, 1e6)).max() < 1e-3
+
+
+def test_qk_norm_rope_append_matches_float64():
+    rng = np.random.default_rng(3)
+    S, B, Hq, Hkv, D, max_seq, pos0 = 3, 2, 4, 2, 128, 16, 5
+    q = oracle.f32_to_bf16_bits(rng.standard_normal((S, B, Hq, D)).astype(np.float32))
+    k = oracle.f32_to_bf16_bits(rng.standard_normal((S, B, Hkv, D)).astype(np.float32))
+    v = oracle.f32_to_bf16_bits(rng.standard_normal((S, B, Hkv, D)).astype(np.float32))
+    w = (1 + 0.02 * rng.standard_normal(D)).astype(np.float32)
+    rope = oracle.rope_table(D, max_seq, 1e6)
+    ck = np.zeros((B, Hkv, max_seq, D), np.uint16); cv = np.zeros_like(ck)
+    strides = [Hkv * max_seq * D, max_seq * D, D, 1]
+    qo = oracle.qk_norm_rope_append_bf16(q, k, v, ck, cv, rope, strides, Hq, Hkv, pos0, S, B, 1e-6, q_weight=w, k_weight=w)
+    x = oracle.bf16_bits_to_f32(k[1, 1, 0]).astype(np.float64)
+    y = x / (np.sqrt((x ** 2).mean()) + 1e-6) * w
+    c, s_ = rope[pos0 + 1, 0::2].astype(np.float64), rope[pos0 + 1, 1::2].astype(np.float64)
+    want = np.empty(D); want[0::2] = y[0::2] * c - y[1::2] * s_; want[1::2] = y[0::2] * s_ + y[1::2] * c
+    got = oracle.bf16_bits_to_f32(ck[1, 0, pos0 + 1])
+    assert np.abs(got - want).max() <= np.abs(want).max() * 2 ** -8
+    assert np.array_equal(cv[1, 0, pos0 + 1], v[1, 1, 0])
+    assert (ck[:, :, :pos0] == 0).all() and (ck[:, :, pos0 + S:] == 0).all()
+    assert qo.shape == q.shape and (qo != 0).any()
