@@ -319,8 +319,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int t = 0; t < kTcTiles; ++t) {
             mbar_init(bar_q(t), 1);
             mbar_init(bar_s_full(t), 1);
-            mbar_init(bar_p_full(t), kTcTileRows);
-            mbar_init(bar_p_half(t), kTcTileRows);
+            mbar_init(bar_p_full(t), kTcTileRows / 32);   // one arrival per softmax warp
+            mbar_init(bar_p_half(t), kTcTileRows / 32);
             mbar_init(bar_pv_done(t), 1);
         }
         for (int s = 0; s < kTcStages; ++s) {
@@ -356,13 +356,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         float m_used = -INFINITY, l = 0.0f;
         bool ok = true;
         for (int j = 0; j < my_steps && ok; ++j) {
-            ok = mbar_wait(bar_s_full(t), j & 1, abort_word, p.status, kTcWaitSFull);
+            // lane 0 polls the barrier, the warp follows (32 pollers per warp only add shared-memory traffic)
+            ok = lane == 0 ? mbar_wait(bar_s_full(t), j & 1, abort_word, p.status, kTcWaitSFull) : true;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
 #if defined(ELLM_WHATIF_NOSOFTMAX)
             tc_fence_before();
-            mbar_arrive(bar_p_full(t));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_p_full(t));
             continue;
 #endif
             const long long key0 = static_cast<long long>(j) * kTcKeys;
@@ -415,7 +417,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     tmem_st32u(tS + 32, pk + 32);
                     tmem_wait_st();
                     tc_fence_before();
-                    mbar_arrive(bar_p_full(t));
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_p_full(t));
                 }
             }
             if (slow) {
@@ -423,19 +426,19 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 // scores are read again in pass 2 rather than kept: tensor-memory reads are cheap and
                 // 128 live registers per thread are not.
                 float mx = -INFINITY;
-    #pragma unroll
+#pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     float s[64];
                     tmem_ld32(tS + h * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
                     tmem_ld32(tS + h * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
                     tmem_wait_ld();
                     if (edge) {
-    #pragma unroll
+#pragma unroll
                         for (int c = 0; c < 64; ++c) s[c] = (h * 64 + c <= rel) ? s[c] : -INFINITY;
                     }
                     float m0 = max3(s[0], s[1], s[2]), m1 = max3(s[3], s[4], s[5]);
                     float m2 = max3(s[6], s[7], s[8]), m3 = max3(s[9], s[10], s[11]);
-    #pragma unroll
+#pragma unroll
                     for (int c = 12; c < 60; c += 8) {
                         m0 = max3(m0, s[c], s[c + 1]);
                         m1 = max3(m1, s[c + 2], s[c + 3]);
@@ -460,12 +463,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 // S_t(j) complete implies P.V(t, j-1) complete (MMAs of one thread finish in issue
                 // order), so O_t can be rescaled and the columns of S_t can take P_t right away.
                 if (rescale && j > 0) {   // before any P.V of this step may start
-    #pragma unroll
+#pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         float o[32];
                         tmem_ld32(tO + c * 32, o);
                         tmem_wait_ld();
-    #pragma unroll
+#pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] *= corr;
                         tmem_st32(tO + c * 32, o);
                     }
@@ -478,7 +481,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 {
                     const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-msub, -msub);
                     uint64_t sum_a = pack2(0.0f, 0.0f), sum_b = sum_a;
-    #pragma unroll
+#pragma unroll
                     for (int half = 0; half < 2; ++half) {
                         // keys [64*half, 64*half+64) of S sit in columns [64*half, +64); their P goes to
                         // columns [32*half, +32), which never overlap a half of S not yet read
@@ -487,18 +490,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         tmem_ld32(tS + half * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
                         tmem_wait_ld();
                         if (edge) {
-    #pragma unroll
+#pragma unroll
                             for (int c = 0; c < 64; ++c) s[c] = (half * 64 + c <= rel) ? s[c] : -INFINITY;
                         }
                         uint32_t pk[32];
-    #pragma unroll
+#pragma unroll
                         for (int cc = 0; cc < 32; ++cc) {
                             const int c = half * 32 + cc;
                             const uint64_t x2 = fma2(pack2(s[2 * cc], s[2 * cc + 1]), scale2, negm2);
                             uint64_t p2;
-    #if defined(ELLM_WHATIF_NOEXP)
+#if defined(ELLM_WHATIF_NOEXP)
                             if (true) { p2 = x2; } else
-    #endif
+#endif
                             if (kTcPolyEvery > 0 && (c % kTcPolyEvery) == kTcPolyEvery - 1) {
                                 p2 = exp2_poly2(x2);
                             } else {
@@ -514,11 +517,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         tmem_st32u(tS + half * 32, pk);
                         tmem_wait_st();
                         tc_fence_before();
-    #if ELLM_TC_SPLIT_P
-                        mbar_arrive(half == 0 ? bar_p_half(t) : bar_p_full(t));
-    #else
-                        if (half == 1) mbar_arrive(bar_p_full(t));
-    #endif
+                        __syncwarp();
+#if ELLM_TC_SPLIT_P
+                        if (lane == 0) mbar_arrive(half == 0 ? bar_p_half(t) : bar_p_full(t));
+#else
+                        if (half == 1 && lane == 0) mbar_arrive(bar_p_full(t));
+#endif
                     }
                     float sa, sb;
                     unpack2(add2(sum_a, sum_b), sa, sb);
@@ -677,6 +681,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // teardown: every role gets here (all waits are bounded)
     tc_fence_before();
     __syncthreads();
+    if (*abort_word) {
+        // a wait ran out: TMA copies of this CTA may still be in flight towards its shared memory;
+        // give them time to land (they take microseconds) before the CTA and its memory go away
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
     if (warp == kTcTiles * 4 + 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
