@@ -46,7 +46,8 @@ _SIGNATURES = {
     "ellm_device_alloc": (_I, [_I, _SZ, C.POINTER(_VP)]),
     "ellm_device_free": (_I, [_I, _VP]),
     "ellm_kv_append": (_I, [_VP, _VP, C.POINTER(_SZ), _SZ, _SZ, _SZ, _SZ, _SZ, _VP, _SZ, _SZ, _I, _VP]),
-    "ellm_qk_norm_rope_append": (_I, [_VP] * 9 + [_SZ, C.POINTER(_SZ)] + [_SZ] * 6 + [_VP, _SZ, _SZ, C.c_float, _I, _VP]),
+    "ellm_qk_norm_rope_append": (_I, [_VP] * 9 + [_SZ, C.POINTER(_SZ)] + [_SZ] * 6 + [_VP, _SZ, _SZ, C.c_float, _SZ, _SZ, _I, _VP]),
+    "ellm_rms_norm": (_I, [_VP, _VP, _SZ, _SZ, C.c_float, _I, _VP]),
     "ellm_attn_merge_partials": (_I, [_VP, _VP, _SZ, _SZ, _SZ, _VP, _VP, _I, _VP]),
     "ellm_attn_merge_partials_f32": (_I, [_VP, _VP, _SZ, _SZ, _SZ, _VP, _VP, _I, _VP]),
     "ellm_attn_run_window": (_I, [_VP, _SZ, _SZ, _SZ, _SZ, _SZ, _VP, _VP]),

@@ -131,11 +131,18 @@ def decode_noalloc(q, k_cache, v_cache, out, batch_size, q_heads, kv_heads, head
 
 def qk_norm_rope_append(q_in, k_in, v_in, q_out, k_cache, v_cache, rope, kv_strides, max_batch, q_heads,
                         kv_heads, head_size, max_seq, position_index, position_interval, batch_size, eps, *,
-                        q_weight=None, k_weight=None, positions=None, device=0, stream=None):
+                        q_weight=None, k_weight=None, positions=None, q_in_row_stride=0, kv_in_row_stride=0,
+                        device=0, stream=None):
     """Per-head RMSNorm + interleaved RoPE on Q and K, K and V written into the cache
     (ellm_qk_norm_rope_append); rope is the fp32 [rows, 128] table of rope.precompute_freqs_cis."""
     L.check(L.load().ellm_qk_norm_rope_append(
         _ptr(q_in), _ptr(k_in), _ptr(v_in), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(q_weight),
         _ptr(k_weight), _ptr(rope), rope.shape[0], (C.c_size_t * 4)(*[int(s) for s in kv_strides]), max_batch,
         q_heads, kv_heads, head_size, max_seq, position_index, _ptr(positions), position_interval,
-        batch_size, float(eps), device, stream))
+        batch_size, float(eps), q_in_row_stride, kv_in_row_stride, device, stream))
+
+
+def rms_norm(x, y, eps, device=0, stream=None):
+    """y = x / (sqrt(mean x^2) + eps) per row of a [rows, length] bf16 matrix (ellm_rms_norm)."""
+    rows, length = x.shape
+    L.check(L.load().ellm_rms_norm(_ptr(x), _ptr(y), rows, length, float(eps), device, stream))

@@ -21,6 +21,7 @@
 #include "prefill_warp_mma.cuh"
 #include "prefill_tcgen05.cuh"
 #include "qk_norm_rope_append.cuh"
+#include "rms_norm.cuh"
 
 namespace {
 
@@ -547,7 +548,7 @@ int ellm_qk_norm_rope_append(const void* q_in, const void* k_in, const void* v_i
                              size_t rope_rows, const size_t kv_strides[4], size_t max_batch, size_t q_heads,
                              size_t kv_heads, size_t head_size, size_t max_seq, size_t position_index,
                              const int32_t* positions, size_t position_interval, size_t batch_size, float eps,
-                             int device, void* stream) {
+                             size_t q_in_row_stride, size_t kv_in_row_stride, int device, void* stream) {
     if (!q_in || !k_in || !v_in || !q_out || !k_cache || !v_cache || !rope || !kv_strides)
         return fail(ELLM_ERR_INVALID_ARG, "q_in, k_in, v_in, q_out, k_cache, v_cache, rope and kv_strides must be non-NULL");
     if (head_size != static_cast<size_t>(ellm::kHeadDim)) return fail(ELLM_ERR_UNSUPPORTED, "head_size %zu: only 128", head_size);
@@ -574,6 +575,11 @@ int ellm_qk_norm_rope_append(const void* q_in, const void* k_in, const void* v_i
     p.q_out = static_cast<__nv_bfloat16*>(q_out);
     p.k_cache = static_cast<__nv_bfloat16*>(k_cache);
     p.v_cache = static_cast<__nv_bfloat16*>(v_cache);
+    p.q_in_stride = static_cast<long long>(q_in_row_stride ? q_in_row_stride : q_heads * head_size);
+    p.kv_in_stride = static_cast<long long>(kv_in_row_stride ? kv_in_row_stride : kv_heads * head_size);
+    if (p.q_in_stride % 8 != 0 || p.kv_in_stride % 8 != 0 || p.q_in_stride < static_cast<long long>(q_heads * head_size) ||
+        p.kv_in_stride < static_cast<long long>(kv_heads * head_size))
+        return fail(ELLM_ERR_INVALID_ARG, "input row strides must be multiples of 8 elements and cover a row");
     p.q_weight = q_weight; p.k_weight = k_weight; p.rope = rope;
     p.positions = positions;
     p.position_index = static_cast<long long>(position_index);
@@ -590,6 +596,22 @@ int ellm_qk_norm_rope_append(const void* q_in, const void* k_in, const void* v_i
     const long long blocks = (warps + 7) / 8;
     if (blocks > 0x7fffffffll) return fail(ELLM_ERR_UNSUPPORTED, "too many rows for one launch");
     ellm::qk_norm_rope_append_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    ELLM_CUDA(cudaGetLastError());
+    return ELLM_OK;
+}
+
+int ellm_rms_norm(const void* x, void* y, size_t rows, size_t length, float eps, int device, void* stream) {
+    if (!x || !y) return fail(ELLM_ERR_INVALID_ARG, "x and y must be non-NULL");
+    if (length == 0 || length % 8 != 0) return fail(ELLM_ERR_INVALID_ARG, "length %zu must be a non-zero multiple of 8", length);
+    if (!aligned16(x) || !aligned16(y)) return fail(ELLM_ERR_INVALID_ARG, "x and y must be 16-byte aligned");
+    if (!(eps >= 0.0f)) return fail(ELLM_ERR_INVALID_ARG, "eps must be >= 0");
+    if (rows == 0) return ELLM_OK;
+    if (rows > 0x7fffffffull) return fail(ELLM_ERR_UNSUPPORTED, "too many rows for one launch");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    ellm::rms_norm_kernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), static_cast<long long>(rows),
+        static_cast<int>(length), eps);
     ELLM_CUDA(cudaGetLastError());
     return ELLM_OK;
 }

@@ -16,9 +16,10 @@
 namespace ellm {
 
 struct NormRopeParams {
-    const __nv_bfloat16* q_in;   // [interval, max_batch, q_heads, 128]
-    const __nv_bfloat16* k_in;   // [interval, max_batch, kv_heads, 128]
+    const __nv_bfloat16* q_in;   // row (chunk row, sequence) at q_in + row * q_in_stride, [q_heads, 128] inside
+    const __nv_bfloat16* k_in;   // row at k_in + row * kv_in_stride, [kv_heads, 128] inside
     const __nv_bfloat16* v_in;
+    long long q_in_stride, kv_in_stride;   // elements; q_heads*128 and kv_heads*128 when contiguous
     __nv_bfloat16* q_out;        // same layout as q_in (may alias it)
     __nv_bfloat16* k_cache;
     __nv_bfloat16* v_cache;
@@ -48,13 +49,13 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(const NormRope
     if (head >= p.q_heads + p.kv_heads) {  // V: plain row copy into the cache
         const int kvh = head - p.q_heads - p.kv_heads;
         if (pos < 0 || pos >= p.max_seq) return;
-        const uint2 v = *reinterpret_cast<const uint2*>(p.v_in + (row * p.kv_heads + kvh) * kHeadDim + lane * 4);
+        const uint2 v = *reinterpret_cast<const uint2*>(p.v_in + row * p.kv_in_stride + kvh * kHeadDim + lane * 4);
         *reinterpret_cast<uint2*>(p.v_cache + b * p.s0 + kvh * p.s1 + pos * p.s2 + lane * 4) = v;
         return;
     }
     const bool is_q = head < p.q_heads;
     const int kvh = head - p.q_heads;
-    const __nv_bfloat16* src = is_q ? p.q_in + (row * p.q_heads + head) * kHeadDim : p.k_in + (row * p.kv_heads + kvh) * kHeadDim;
+    const __nv_bfloat16* src = is_q ? p.q_in + row * p.q_in_stride + head * kHeadDim : p.k_in + row * p.kv_in_stride + kvh * kHeadDim;
     if (!is_q && (pos < 0 || pos >= p.max_seq)) return;
     if (pos < 0 || pos >= p.rope_rows) return;  // no rotation row for this position: leave the output untouched
     const uint2 raw = *reinterpret_cast<const uint2*>(src + lane * 4);

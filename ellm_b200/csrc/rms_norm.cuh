@@ -1,0 +1,52 @@
+// Row-wise weight-free RMS normalisation, y = x / (sqrt(mean x^2) + eps): the reference's
+// rms_norm (src/kernel/generic/rms_norm.rs:6-26; eps is added to the root, not under it).  It is
+// the input norm of a decoder layer (src/qwen3_moe/decoder_layer.rs:139-143), i.e. what produces
+// the activations the QKV projection reads.  HBM-bound: one read and one write of every row.
+// One CTA per row, 8 bf16 per thread per step, fp32 arithmetic.
+#pragma once
+#include "common.cuh"
+
+namespace ellm {
+
+__global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                                                       long long rows, int length, float eps) {
+    __shared__ float warp_sums[8];
+    __shared__ float s_rrms;
+    const long long row = blockIdx.x;
+    if (row >= rows) return;
+    const uint4* src = reinterpret_cast<const uint4*>(x + row * length);
+    uint4* dst = reinterpret_cast<uint4*>(y + row * length);
+    const int chunks = length / 8;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        const uint4 v = src[c];
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float a = __low2float(p[i]), b = __high2float(p[i]);
+            ss += a * a + b * b;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) t += warp_sums[w];
+        s_rrms = 1.0f / (sqrtf(t / static_cast<float>(length)) + eps);
+    }
+    __syncthreads();
+    const float rrms = s_rrms;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        const uint4 v = src[c];
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+        uint4 o;
+        uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) po[i] = pack_bf16(__low2float(p[i]) * rrms, __high2float(p[i]) * rrms);
+        dst[c] = o;
+    }
+}
+
+}  // namespace ellm

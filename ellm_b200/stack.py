@@ -3,30 +3,23 @@
 Per layer, following the reference's decoder layer and attention block minus the MoE part
 (src/qwen3_moe/decoder_layer.rs:139-165, src/qwen3_moe/attention.rs:126-196):
 
-    h   = rms(x)                                   input norm, weight-free (generic/rms_norm.rs:6-26)
-    q,k,v = h Wq^T, h Wk^T, h Wv^T                 matmul3 (src/compiler/mul/matmul3.rs:289-385)
+    h   = rms(x)                                   input norm, weight-free (generic/rms_norm.rs:6-26): ellm_rms_norm
+    q,k,v = h [Wq;Wk;Wv]^T                         matmul3 (src/compiler/mul/matmul3.rs:289-385), one GEMM
     q,k = rope(qk_norm(q, k)); cache <- k, v       ellm_qk_norm_rope_append
     a   = Attention(q, cache)                      ellm_attn_run
     x   = x + a Wo^T                               matmul_add (src/compiler/mul/matmul_add.rs:186-226)
 
-The projections and the input norm are library calls (torch / cuBLAS): they are the path's
-neighbours, not the path.  The norm+rope+append step and attention are this repository's
-kernels.  Decode steps can be captured once in a CUDA graph and replayed: every kernel takes
+The projections are library calls (torch / cuBLAS): they are the path's neighbours, not the
+path.  The input norm, the norm+rope+append step and attention are this repository's kernels.  Decode steps can be captured once in a CUDA graph and replayed: every kernel takes
 the per-sequence positions from a device array that the graph itself advances.
 """
 import numpy as np
 import torch
 
 from . import _lib as L
-from .attention import Attention, qk_norm_rope_append
+from .attention import Attention, qk_norm_rope_append, rms_norm
 from .kv_cache import StaticKVCache
 from .rope import precompute_freqs_cis
-
-
-def rms(x, eps):
-    """y = x / (sqrt(mean x^2) + eps) over the last dimension, fp32 inside, bf16 out."""
-    xf = x.float()
-    return (xf / (xf.pow(2).mean(-1, keepdim=True).sqrt() + eps)).to(torch.bfloat16)
 
 
 class AttentionStack:
@@ -48,14 +41,16 @@ class AttentionStack:
         self.wk = [w(kd, hidden) for _ in range(layers)]
         self.wv = [w(kd, hidden) for _ in range(layers)]
         self.wo = [w(hidden, qd) for _ in range(layers)]
+        # the three projections as one GEMM: rows of [Wq; Wk; Wv]
+        self.wqkv = [torch.cat([self.wq[i], self.wk[i], self.wv[i]]).contiguous() for i in range(layers)]
+        self.qkv = torch.zeros(max_interval * max_batch, qd + 2 * kd, dtype=torch.bfloat16, device=dev)
+        self.h = torch.zeros(max_interval * max_batch, hidden, dtype=torch.bfloat16, device=dev)
         self.q_norm = [w(head_dim, mean=1.0, dtype=torch.float32) for _ in range(layers)]
         self.k_norm = [w(head_dim, mean=1.0, dtype=torch.float32) for _ in range(layers)]
         self.rope = torch.from_numpy(precompute_freqs_cis(head_dim, max_seq, theta)).to(dev)
         self.cache = StaticKVCache(layers, max_batch, kv_heads, max_seq, head_dim, device=dev)
         rows = max_interval * max_batch
         self.q = torch.zeros(max_interval, max_batch, q_heads, head_dim, dtype=torch.bfloat16, device=dev)
-        self.k = torch.zeros(max_interval, max_batch, kv_heads, head_dim, dtype=torch.bfloat16, device=dev)
-        self.v = torch.zeros_like(self.k)
         self.a = torch.zeros_like(self.q)
         self.positions = torch.zeros(max_batch, dtype=torch.int32, device=dev)
         self.scale = 1.0 / np.sqrt(head_dim)
@@ -70,17 +65,19 @@ class AttentionStack:
     def _layer(self, i, x, n, batch, position_index, ragged):
         """x: [n * max_batch, hidden] bf16 (rows ordered chunk row, then sequence)."""
         rows = n * self.max_batch
-        h = rms(x, self.eps)
-        q, k, v, a = self.q[:n], self.k[:n], self.v[:n], self.a[:n]
-        torch.matmul(h, self.wq[i].t(), out=q.view(rows, -1))
-        torch.matmul(h, self.wk[i].t(), out=k.view(rows, -1))
-        torch.matmul(h, self.wv[i].t(), out=v.view(rows, -1))
+        dev_index = self.dev.index or 0
+        h, qkv = self.h[:rows], self.qkv[:rows]
+        rms_norm(x, h, self.eps, device=dev_index, stream=self.stream.cuda_stream)
+        torch.matmul(h, self.wqkv[i].t(), out=qkv)
+        q, a = self.q[:n], self.a[:n]
+        qd, kd = self.q_heads * self.head_dim, self.kv_heads * self.head_dim
         ck, cv = self.cache.layer(i)
-        qk_norm_rope_append(q, k, v, q, ck, cv, self.rope, self.cache.strides, self.max_batch, self.q_heads,
-                            self.kv_heads, self.head_dim, self.max_seq, position_index, n, batch, self.eps,
-                            q_weight=self.q_norm[i], k_weight=self.k_norm[i],
-                            positions=self.positions if ragged else None, device=self.dev.index or 0,
-                            stream=self.stream.cuda_stream)
+        # q, k, v are column blocks of the fused projection's output rows
+        qk_norm_rope_append(qkv, qkv[:, qd:], qkv[:, qd + kd:], q, ck, cv, self.rope, self.cache.strides,
+                            self.max_batch, self.q_heads, self.kv_heads, self.head_dim, self.max_seq, position_index,
+                            n, batch, self.eps, q_weight=self.q_norm[i], k_weight=self.k_norm[i],
+                            positions=self.positions if ragged else None, q_in_row_stride=qd + 2 * kd,
+                            kv_in_row_stride=qd + 2 * kd, device=dev_index, stream=self.stream.cuda_stream)
         if ragged:
             self.ops[i].run_ragged(self.positions, n, batch, 1, 0)
         else:

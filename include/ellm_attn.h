@@ -135,7 +135,9 @@ int ellm_kv_append(void* cache, const void* src, const size_t kv_strides[4], siz
  * matmul_rms_complex.rs:76-96 - and the write of K and V into the cache at the chunk's
  * positions (output_to_kv, src/compiler/zip_map/complex_zip.rs:92-98).
  * q_in/q_out [rows, max_batch, q_heads, 128] (may alias), k_in/v_in [rows, max_batch, kv_heads,
- * 128], bf16; q_weight/k_weight fp32[128] or NULL (the reference's norm has no weight);
+ * 128], bf16; q_in_row_stride / kv_in_row_stride (elements, 0 = contiguous) let the three inputs be
+ * column blocks of one fused projection output; q_weight/k_weight fp32[128] or NULL (the
+ * reference's norm has no weight);
  * rope fp32 [rope_rows, 128] of interleaved (cos, sin), row = absolute position
  * (src/qwen3_moe/rope.rs:7-28); positions as in ellm_attn_run_ragged or NULL. */
 int ellm_qk_norm_rope_append(const void* q_in, const void* k_in, const void* v_in, void* q_out,
@@ -144,8 +146,16 @@ int ellm_qk_norm_rope_append(const void* q_in, const void* k_in, const void* v_i
                              const size_t kv_strides[4], size_t max_batch, size_t q_heads,
                              size_t kv_heads, size_t head_size, size_t max_seq,
                              size_t position_index, const int32_t* positions,
-                             size_t position_interval, size_t batch_size, float eps, int device,
+                             size_t position_interval, size_t batch_size, float eps,
+                             size_t q_in_row_stride, size_t kv_in_row_stride, int device,
                              void* stream);
+
+/* Row-wise weight-free RMS normalisation y = x / (sqrt(mean x^2) + eps) of a [rows, length] bf16
+ * matrix (length a multiple of 8): the reference's rms_norm, src/kernel/generic/rms_norm.rs:6-26,
+ * the input norm that produces what the QKV projection reads
+ * (src/qwen3_moe/decoder_layer.rs:139-143).  x and y may alias. */
+int ellm_rms_norm(const void* x, void* y, size_t rows, size_t length, float eps, int device,
+                  void* stream);
 
 /* Combine `parts` partial results of the same query rows taken over disjoint key
  * sets: L = log sum_i exp(L_i), O = sum_i O_i exp(L_i - L).  No counterpart in the

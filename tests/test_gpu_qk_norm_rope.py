@@ -80,3 +80,48 @@ def test_feeds_attention_end_to_end():
     d = np.abs(out.float().cpu().numpy() - oracle.bf16_bits_to_f32(want_o))
     assert d.max() <= 2e-2 and d.mean() <= 2e-3
     assert np.abs(lse.cpu().numpy() - want_l).max() <= 2e-2   # one-bf16-step differences in normalised Q/K move the scores
+
+
+def test_rms_norm_rows_against_oracle():
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(9)
+    for rows, length in ((1, 8), (5, 2048), (37, 4096), (3, 264)):
+        x = (torch.randn(rows, length, generator=g) * 3).to(torch.bfloat16)
+        xf = x.float().numpy()
+        want = np.empty_like(xf)
+        for r in range(rows):
+            oracle.load().oracle_rms_norm_f32(xf[r].ctypes.data, want[r].ctypes.data, length, 1e-6)
+        want_bits = oracle.f32_to_bf16_bits(want)
+        y = torch.zeros(rows, length, dtype=torch.bfloat16, device=dev)
+        ellm_b200.rms_norm(x.to(dev), y, 1e-6)
+        torch.cuda.synchronize()
+        got = bits(y)
+        assert (got == want_bits).mean() >= 0.98
+        g32, w32 = oracle.bf16_bits_to_f32(got), oracle.bf16_bits_to_f32(want_bits)
+        assert (np.abs(g32 - w32) <= np.abs(w32) * 2.0 ** -7 + 1e-30).all()
+
+
+def test_inputs_as_column_blocks_of_one_projection_output():
+    """q, k, v given as column blocks of a fused [rows, (Hq + 2 Hkv) * 128] matrix equal the contiguous form."""
+    dev = torch.device("cuda:0")
+    S, B, Hq, Hkv, max_seq = 9, 2, 4, 2, 16
+    g = torch.Generator().manual_seed(10)
+    qkv = torch.randn(S * B, (Hq + 2 * Hkv) * 128, generator=g).to(torch.bfloat16).to(dev)
+    qd, kd = Hq * 128, Hkv * 128
+    rope = torch.from_numpy(ellm_b200.precompute_freqs_cis(128, max_seq, 1e6)).to(dev)
+    strides = [Hkv * max_seq * 128, max_seq * 128, 128, 1]
+    outs = []
+    for fused in (False, True):
+        ck = torch.zeros(B, Hkv, max_seq, 128, dtype=torch.bfloat16, device=dev); cv = torch.zeros_like(ck)
+        q_out = torch.zeros(S, B, Hq, 128, dtype=torch.bfloat16, device=dev)
+        if fused:
+            ellm_b200.qk_norm_rope_append(qkv, qkv[:, qd:], qkv[:, qd + kd:], q_out, ck, cv, rope, strides, B, Hq, Hkv, 128,
+                                          max_seq, 3, S, B, 1e-6, q_in_row_stride=qd + 2 * kd, kv_in_row_stride=qd + 2 * kd)
+        else:
+            ellm_b200.qk_norm_rope_append(qkv[:, :qd].contiguous(), qkv[:, qd:qd + kd].contiguous(), qkv[:, qd + kd:].contiguous(),
+                                          q_out, ck, cv, rope, strides, B, Hq, Hkv, 128, max_seq, 3, S, B, 1e-6)
+        torch.cuda.synchronize()
+        outs.append((q_out, ck, cv))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    assert outs[0][1].abs().sum() > 0
