@@ -64,6 +64,12 @@ class ClockSampler:
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
+        # address the GPU by UUID: nvidia-smi's indices need not match CUDA's
+        try:
+            uuid = str(torch.cuda.get_device_properties(index).uuid)
+            index = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:
+            pass
         self.index, self.rows, self.proc = index, [], None
 
     def start(self):

@@ -197,7 +197,7 @@ int launch_decode(ellm_attn* h, const int32_t* positions, size_t position_index,
         ellm::decode_splitkv_kernel<<<h->dec_ctas, ellm::kDecThreads, ellm::kDecSmemBytes, h->stream>>>(p);
     }
     ELLM_CUDA(cudaGetLastError());
-    const unsigned blocks = static_cast<unsigned>((batch * h->d.q_heads + 3) / 4);
+    const unsigned blocks = static_cast<unsigned>(batch * h->d.q_heads);
     {
         // programmatic dependent launch: the merge grid is set up while the decode grid drains;
         // its first instruction waits for the decode grid's memory to be visible
@@ -267,8 +267,8 @@ cudaError_t copy_rows(void* dst, const void* src, size_t pitch, size_t width, si
     return cudaMemcpy2DAsync(dst, pitch, src, pitch, width, rows, kind, stream);
 }
 
-int finish(ellm_attn* h) {
-    if (h->d.async) return ELLM_OK;
+int finish(ellm_attn* h, bool enqueue_only) {
+    if (enqueue_only) return ELLM_OK;
     ELLM_CUDA(cudaStreamSynchronize(h->stream));
     if (h->status_host && *h->status_host != 0) {
         const int code = *h->status_host;
@@ -282,7 +282,7 @@ int finish(ellm_attn* h) {
 // Common body of run / run_ragged / run_window.
 int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size_t interval,
              size_t batch, long long key_begin, long long key_end, float* out_f32, float* lse_out,
-             bool append) {
+             bool append, int enqueue_only = -1) {
     if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL");
     if (interval == 0 || batch == 0) return ELLM_OK;  // nothing to do, as an empty assign() range
     if (batch > h->d.max_batch) return fail(ELLM_ERR_INVALID_ARG, "batch_size %zu > max_batch %zu", batch, h->d.max_batch);
@@ -296,6 +296,7 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
     DeviceGuard guard(h->d.device);
     if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", h->d.device);
     std::lock_guard<std::mutex> lock(h->mu);
+    const bool no_sync = enqueue_only < 0 ? h->d.async != 0 : enqueue_only != 0;
     int rc;
     const bool do_append = append && h->d.k_new;
     if (do_append && interval > 1) {   // a decode step appends inside its own kernel
@@ -326,9 +327,9 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
         }
     }
     if (rc) return rc;
-    if (h->status_dev && !h->d.async && interval > 1)
+    if (h->status_dev && !no_sync && interval > 1)
         cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream);
-    return finish(h);
+    return finish(h, no_sync);
 }
 
 }  // namespace
@@ -475,10 +476,8 @@ int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
         positions = h->positions_dev;
     }
     const uint64_t tc_before = h->launches[ELLM_KERNEL_PREFILL_TCGEN05];
-    const int was_async = h->d.async;
-    h->d.async = 1;
-    int rc = run_impl(h, positions, position_index, position_interval, batch_size, 0, INT64_MAX, nullptr, h->d.lse, k_new_host != nullptr);
-    h->d.async = was_async;
+    int rc = run_impl(h, positions, position_index, position_interval, batch_size, 0, INT64_MAX, nullptr, h->d.lse,
+                      k_new_host != nullptr, /*enqueue_only=*/1);
     if (rc) return rc;
     ELLM_CUDA(copy_rows(out_host, h->d.out, q_pitch, q_width, position_interval, cudaMemcpyDeviceToHost, h->stream));
     if (lse_host)
@@ -793,7 +792,7 @@ extern "C" int ellm_attn_decode_noalloc(const void* q, const void* k_cache, cons
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     ellm::decode_splitkv_kernel<<<num_ctas, ellm::kDecThreads, ellm::kDecSmemBytes, s>>>(p);
     ELLM_CUDA(cudaGetLastError());
-    const unsigned blocks = static_cast<unsigned>((batch_size * q_heads + 3) / 4);
+    const unsigned blocks = static_cast<unsigned>(batch_size * q_heads);
     ellm::decode_merge_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(p, static_cast<__nv_bfloat16*>(out), lse);
     ELLM_CUDA(cudaGetLastError());
     return ELLM_OK;
