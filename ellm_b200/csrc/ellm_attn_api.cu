@@ -310,7 +310,7 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
         bool use_tc = false;
         if (key_begin == 0) {
             if (h->d.prefill_kernel == ELLM_PREFILL_TCGEN05) use_tc = true;
-            else if (h->d.prefill_kernel == ELLM_PREFILL_AUTO) use_tc = !positions && ellm::tcgen05_prefers(h->tc, interval, h->group);
+            else if (h->d.prefill_kernel == ELLM_PREFILL_AUTO) use_tc = ellm::tcgen05_prefers(h->tc, interval, h->group);
         }
         if (use_tc) {
             if (!h->tc.ready)

@@ -66,8 +66,10 @@ struct TcParams {
 
     float* lse;
     int* status;            // device word: non-zero = a bounded wait ran out
+    const int32_t* positions;  // per-sequence position of chunk row 0, or nullptr (then `base` for all)
     long long base;         // position of chunk row 0
-    long long key_end;      // rows attend keys [0, min(position + 1, key_end))
+    long long key_end;      // rows attend keys [0, min(position + 1, key_end)); uniform chunk start only
+    long long max_seq;      // rows per (sequence, kv head) in the cache
     int interval, batch, max_batch;
     int q_heads, kv_heads, group;
     int pair_tiles;         // 256-row CTA tiles per (sequence, kv head) = ceil(interval * group / 256)
@@ -262,11 +264,11 @@ __device__ __forceinline__ uint64_t exp2_poly2(uint64_t x2) {
 enum { kTcWaitQ = 1, kTcWaitKvFull = 2, kTcWaitKvEmpty = 3, kTcWaitSFull = 4, kTcWaitPFull = 5, kTcWaitPvDone = 6 };
 
 // Key tiles row tile t of this CTA needs (0 when the tile has no valid row).
-__device__ __forceinline__ int tc_tile_steps(const TcParams& p, int rho0, int total_rows) {
+__device__ __forceinline__ int tc_tile_steps(const TcParams& p, int rho0, int total_rows, long long base, long long key_end) {
     if (rho0 >= total_rows) return 0;
     const int rho_last = min(rho0 + kTcTileRows, total_rows) - 1;
-    long long kend = p.base + rho_last / p.group + 1;
-    if (kend > p.key_end) kend = p.key_end;
+    long long kend = base + rho_last / p.group + 1;
+    if (kend > key_end) kend = key_end;
     return static_cast<int>((kend + kTcKeys - 1) / kTcKeys);
 }
 
@@ -288,7 +290,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     auto bar_p_full = [&](int t) { return bar0 + 8u * (4 + 2 * kTcStages + t); };
     auto bar_pv_done = [&](int t) { return bar0 + 8u * (6 + 2 * kTcStages + t); };
     auto bar_p_half = [&](int t) { return bar0 + 8u * (8 + 2 * kTcStages + t); };
-    constexpr int kNumBars = 10 + 2 * kTcStages;
+    const uint32_t bar_tail = bar0 + 8u * (10 + 2 * kTcStages);
+    constexpr int kNumBars = 11 + 2 * kTcStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kTcSmemBar + 8 * kNumBars);
     volatile int* abort_word = reinterpret_cast<volatile int*>(smem + kTcSmemBar + 8 * kNumBars + 8);
 
@@ -312,8 +315,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int total_rows = p.interval * p.group;
     int steps[kTcTiles];
 #pragma unroll
-    for (int t = 0; t < kTcTiles; ++t) steps[t] = tc_tile_steps(p, (pair * kTcTiles + t) * kTcTileRows, total_rows);
+    // where this sequence's chunk starts and where its keys end
+    const long long base = p.positions ? static_cast<long long>(p.positions[b]) : p.base;
+    const long long key_end = p.positions ? min(base + p.interval, p.max_seq) : p.key_end;
+    for (int t = 0; t < kTcTiles; ++t) steps[t] = tc_tile_steps(p, (pair * kTcTiles + t) * kTcTileRows, total_rows, base, key_end);
     const int nsteps = max(steps[0], steps[1]);
+    // With per-sequence chunk starts the K/V tensor maps are bounded by the cache, not by this
+    // sequence's end, so the last V tile may carry rows past key_end that hold anything; their P
+    // is 0 but 0 * NaN is NaN, so the producer zeroes them before the MMA may read the tile.
+    const bool zero_tail = p.positions != nullptr && static_cast<long long>(nsteps) * kTcKeys > key_end;
 
     if (threadIdx.x == 0) {
         for (int t = 0; t < kTcTiles; ++t) {
@@ -327,6 +337,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(bar_kv_full(s), 1);
             mbar_init(bar_kv_empty(s), 1);
         }
+        mbar_init(bar_tail, 1);
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -350,8 +361,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int rho = (pair * kTcTiles + t) * kTcTileRows + row;
         const bool valid = rho < total_rows;
         const int pos = valid ? rho / p.group : 0, g = valid ? rho % p.group : 0;
-        const long long lim = valid ? min(p.base + pos, p.key_end - 1) : -1;   // last key this row may see
-        const long long tile_min_lim = min(p.base + ((pair * kTcTiles + t) * kTcTileRows) / p.group, p.key_end - 1);
+        const long long lim = valid ? min(base + pos, key_end - 1) : -1;   // last key this row may see
+        const long long tile_min_lim = min(base + ((pair * kTcTiles + t) * kTcTileRows) / p.group, key_end - 1);
         const int my_steps = steps[t];
         float m_used = -INFINITY, l = 0.0f;
         bool ok = true;
@@ -589,6 +600,23 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     tma_load_4d(smem_base + kTcSmemRing + slot * kTcTileBytes + h * kTcHalfBytes, map, bar_kv_full(slot),
                                 h * 64, key0, kvh, b);
             }
+            if (ok && zero_tail) {
+                const int item = 2 * nsteps - 1, slot = item % kTcStages;   // the last V tile
+                ok = mbar_wait(bar_kv_full(slot), (item / kTcStages) & 1, abort_word, p.status, kTcWaitKvFull);
+                if (ok) {
+                    // a 128-byte row of either half holds one key; the swizzle only permutes inside a row
+                    const int first = static_cast<int>(key_end - static_cast<long long>(nsteps - 1) * kTcKeys);
+                    unsigned char* tile = smem + kTcSmemRing + slot * kTcTileBytes;
+                    for (int r = first; r < kTcKeys; ++r)
+                        for (int h = 0; h < 2; ++h) {
+                            uint4* row = reinterpret_cast<uint4*>(tile + h * kTcHalfBytes + r * 128);
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) row[c] = make_uint4(0u, 0u, 0u, 0u);
+                        }
+                    fence_async_smem();
+                    mbar_arrive(bar_tail);
+                }
+            }
         }
     } else {
         // =============================== MMA issuer ===============================
@@ -622,6 +650,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             };
             // item i of the ring: K_(i/2) for even i, V_(i/2) for odd i
             auto wait_item = [&](int item) {
+                if (zero_tail && item == 2 * nsteps - 1)   // the last V tile is released by the producer's clean-up
+                    return mbar_wait(bar_tail, 0, abort_word, p.status, kTcWaitKvFull);
                 return mbar_wait(bar_kv_full(item % kTcStages), (item / kTcStages) & 1, abort_word, p.status, kTcWaitKvFull);
             };
             for (int t = 0; t < kTcTiles && ok; ++t)
@@ -729,19 +759,17 @@ inline bool tcgen05_prefers(const Tcgen05Plan& plan, size_t interval, int group)
     return plan.ready && interval * static_cast<size_t>(group) >= 256;
 }
 
-// Uniform chunk start only (positions == nullptr): the K/V tensor maps are bounded at
-// min(position_index + interval, key_end) so that TMA zero-fills rows the chunk must not read.
+// With a uniform chunk start the K/V tensor maps are bounded at min(position_index + interval,
+// key_end) so that TMA zero-fills rows the chunk must not read; with per-sequence starts
+// (positions != nullptr) they are bounded by the cache and the kernel zeroes the tail itself.
 // out_f32 != nullptr writes an fp32 partial result there instead of bf16 to d.out.
 inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, const int32_t* positions,
                                   size_t position_index, size_t interval, size_t batch, long long key_end,
                                   float* out_f32, float* lse, int* status, cudaStream_t stream) {
     if (!plan.ready) return ELLM_ERR_UNSUPPORTED;
-    if (positions) {
-        snprintf(plan.why, sizeof(plan.why), "ragged positions are served by the warp-MMA kernel");
-        return ELLM_ERR_UNSUPPORTED;
-    }
     const int group = static_cast<int>(d.q_heads / d.kv_heads);
-    long long kv_rows = static_cast<long long>(position_index + interval);
+    // per-sequence chunk starts: the maps can only be bounded by the cache itself
+    long long kv_rows = positions ? static_cast<long long>(d.max_seq) : static_cast<long long>(position_index + interval);
     if (kv_rows > key_end) kv_rows = key_end;
     if (kv_rows > static_cast<long long>(d.max_seq)) kv_rows = static_cast<long long>(d.max_seq);
     if (kv_rows <= 0) {
@@ -781,6 +809,8 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
     p.lse = lse;
     p.status = status;
     p.base = static_cast<long long>(position_index);
+    p.positions = positions;
+    p.max_seq = static_cast<long long>(d.max_seq);
     p.interval = static_cast<int>(interval);
     p.batch = static_cast<int>(batch);
     p.max_batch = static_cast<int>(d.max_batch);

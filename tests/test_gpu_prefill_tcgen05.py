@@ -59,8 +59,8 @@ def test_auto_picks_tcgen05_for_large_chunks_and_warp_mma_for_small():
     small.gpu()
     assert small.last_stats["prefill_warp_mma"][0] == 1
     ragged = Case(seed=1, interval=256, batch=2, q_heads=2, kv_heads=2, max_seq=600, positions=[0, 300])
-    ragged.gpu()   # ragged chunk starts are served by the warp-MMA kernel
-    assert ragged.last_stats["prefill_warp_mma"][0] == 1
+    ragged.gpu()   # per-sequence chunk starts stay on the tcgen05 kernel
+    assert ragged.last_stats["prefill_tcgen05"][0] == 1
 
 
 def test_tcgen05_unsupported_group_is_reported():
@@ -109,3 +109,13 @@ def test_sequence_chunks_as_key_windows_merge_to_the_full_result(kernel):
         got_o[i * chunk:(i + 1) * chunk] = bits(out).reshape(chunk, 1, Hq, 128)
         got_l[i * chunk:(i + 1) * chunk] = lse.cpu().numpy().reshape(chunk, 1, Hq)
     assert_attention_close(full, got_o, got_l, want_o, want_l)
+
+
+@pytest.mark.parametrize("positions,interval", [([0, 300, 37], 200), ([5, 0], 128), ([1000, 1, 511, 512], 129), ([0], 256)])
+@pytest.mark.parametrize("q_heads,kv_heads", [(8, 2), (4, 4)])
+def test_tcgen05_prefill_per_sequence_chunk_starts(positions, interval, q_heads, kv_heads):
+    """Sequences of a batch at different positions; the cache past every sequence's end is NaN, so a
+    V row read past the end without being cleared would poison the output."""
+    case = Case(seed=900 + interval, interval=interval, batch=len(positions), q_heads=q_heads, kv_heads=kv_heads,
+                max_seq=max(positions) + interval + 70, positions=positions, max_batch=len(positions) + 1)
+    _check(case)
