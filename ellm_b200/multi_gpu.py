@@ -7,7 +7,8 @@ the path has an exchange step.
 `heads`: every rank owns a contiguous range of KV heads with their query heads and runs the
 whole causal prefill for them; no collective.  `seq`: one sequence cut into chunks
 (sharding.SequenceChunkPlan); partial (O, LSE) per key chunk, exchanged with NCCL
-send/recv and combined by the merge kernel.  Rank 0 prints one JSON line; times are CUDA
+send/recv - or stored by the producing kernels straight into the owner's memory
+(--exchange p2p) - and combined by the merge kernel.  Rank 0 prints one JSON line; times are CUDA
 events, maximum over ranks.  `--dump DIR` saves inputs and results for an external check.
 """
 import argparse
@@ -124,11 +125,54 @@ def run_seq(args, rank, world, dev):
         merge_partials(o, l, mo, ml, device=dev.index, stream=stream, out_f32=True)
         return mo, ml
 
+    use_p2p = args.exchange == "p2p" and world > 1
+    if use_p2p:
+        # inbox in symmetric memory: [owned chunk slot, source rank, rows, D] fp32 and the LSEs behind it
+        import torch.distributed._symmetric_memory as symm_mem
+        n_own = len(mine)
+        o_elems, l_elems = n_own * world * rows * D, n_own * world * rows
+        inbox = symm_mem.empty(o_elems + l_elems, dtype=torch.float32, device=dev)
+        hdl = symm_mem.rendezvous(inbox, dist.group.WORLD.group_name)
+        views = {}
+        for r in range(world):
+            buf = hdl.get_buffer(r, (o_elems + l_elems,), torch.float32)
+            views[r] = (buf[:o_elems].view(n_own, world, Lc, 1, Hq, D), buf[o_elems:].view(n_own, world, Lc, 1, Hq))
+
+        def inbox_of(dst, i, src):
+            j = plan.chunks_of(dst).index(i)
+            return views[dst][0][j, src], views[dst][1][j, src]
+
+        def compute_partial_into(i, k, o, lse):
+            r, j = slot[i]
+            q_buf.copy_(q_all[r, j])
+            if o is None:
+                o = torch.empty(Lc, 1, Hq, D, dtype=torch.float32, device=dev)
+                lse = torch.empty(Lc, 1, Hq, dtype=torch.float32, device=dev)
+            ops[k].run_window((i - k) * Lc, Lc, 1, 0, Lc, o, lse)   # the kernel's stores go straight to o, local or peer
+            return o, lse
+
+        def merge_into(parts, o, lse):
+            po = torch.stack([p[0].view(rows, D) for p in parts])
+            pl = torch.stack([p[1].view(rows) for p in parts])
+            merge_partials(po, pl, o, lse, device=dev.index, stream=stream, out_f32=True)
+
+        def finish(i, n_sources):
+            j = mine.index(i)
+            mo = torch.empty(Lc, 1, Hq, D, dtype=torch.float32, device=dev)
+            ml = torch.empty(Lc, 1, Hq, dtype=torch.float32, device=dev)
+            merge_partials(views[rank][0][j, :n_sources].reshape(n_sources, rows, D),
+                           views[rank][1][j, :n_sources].reshape(n_sources, rows), mo, ml, device=dev.index,
+                           stream=stream, out_f32=True)
+            return mo, ml
+
     def step():
         if world > 1:
             dist.all_gather_into_tensor(q_all.view(world, -1), q_own.view(-1))
         else:
             q_all[0].copy_(q_own)
+        if use_p2p:
+            return sharding.sequence_chunk_attention_p2p(plan, rank, compute_partial_into, merge_into, inbox_of,
+                                                         lambda: hdl.barrier(channel=0), finish)
         return sharding.sequence_chunk_attention(plan, rank, None, compute_partial, merge, dist=dist,
                                                  empty_like=torch.empty_like)
 
@@ -152,7 +196,7 @@ def run_seq(args, rank, world, dev):
     part_bytes = rows * D * 4 + rows * 4
     sent = sum(1 for i in range(plan.n_chunks) for src in plan.sources_of(i) if src != plan.owner(i))
     return {"mode": "seq", "ms": ms, "tflops": flops / ms / 1e9, "chunks": plan.n_chunks, "chunk_len": Lc,
-            "zigzag": plan.zigzag, "pairs_per_rank": pairs, "nvlink_bytes_partials": sent * part_bytes,
+            "zigzag": plan.zigzag, "pairs_per_rank": pairs, "exchange": "p2p" if use_p2p else "nccl", "nvlink_bytes_partials": sent * part_bytes,
             "nvlink_bytes_q_allgather": (world - 1) * world * q_own.numel() * 2}
 
 
@@ -168,6 +212,9 @@ def main():
     ap.add_argument("--dump", default="", help="directory: save inputs and results for an external check")
     ap.add_argument("--dump-rows", type=int, default=256, help="heads mode: rows per head to save")
     ap.add_argument("--contiguous", action="store_true", help="seq mode: rank r owns chunk r (no zig-zag)")
+    ap.add_argument("--exchange", choices=["nccl", "p2p"], default="nccl",
+                    help="seq mode: move the partials with NCCL send/recv, or let the producing kernels store them "
+                         "directly into the owner's symmetric-memory inbox over NVLink")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -19,6 +19,12 @@ Two ways to shard:
   triangle (every rank computes 2N+1 chunk pairs); contiguous ownership gives rank
   0 N pairs and rank N-1 one.
 
+`sequence_chunk_attention` moves the partials with grouped send/recv (NCCL, or gloo in the CPU
+tests).  `sequence_chunk_attention_p2p` needs no collective for them at all: every rank exposes
+an inbox in symmetric memory and the kernel that produces a partial writes it straight into the
+owner's inbox over NVLink (ordinary stores to a peer pointer), so the transfer rides in the
+producing kernel's epilogue; one device-side barrier separates the writes from the merge.
+
 The compute and merge steps are passed in as callables so that the same exchange
 logic runs over NCCL with the CUDA kernels and, in the CPU tests, over gloo with a
 stand-in.
@@ -127,4 +133,37 @@ def sequence_chunk_attention(plan, rank, q_chunks, compute_partial, merge, dist=
     for i in mine:
         parts = ([local[i]] if i in local else []) + received[i]
         result[i] = parts[0] if len(parts) == 1 else merge(parts)
+    return result
+
+
+def sequence_chunk_attention_p2p(plan, rank, compute_partial_into, merge_into, inbox_of, barrier, finish):
+    """Sequence-chunk sharded prefill with the partials written directly into peer memory.
+
+    inbox_of(dst_rank, q_chunk, src_rank) -> (o, lse): views of the fp32 inbox slot of `dst_rank`
+      (its own memory when dst_rank == rank, a peer mapping otherwise) for the partial that
+      `src_rank` contributes to query chunk `q_chunk`.
+    compute_partial_into(i, k, o, lse): attention of query chunk i against key chunk k, result
+      written to (o, lse) - which may be peer memory.
+    merge_into(parts, o, lse): log-sum-exp combine of local partials into (o, lse).
+    barrier(): device-side barrier over all ranks on the compute stream.
+    finish(i, n_sources) -> result for owned chunk i from the first n_sources inbox slots.
+    With zig-zag or contiguous ownership the ranks holding a partial for chunk i are always
+    0 .. n_sources-1, so an owner's inbox slots for a chunk are contiguous.
+    """
+    barrier()   # nobody overwrites an inbox its owner may still be merging from the last step
+    for i in range(plan.n_chunks):
+        ks = [k for k in plan.chunks_of(rank) if k <= i]
+        if not ks:
+            continue
+        o, lse = inbox_of(plan.owner(i), i, rank)
+        if len(ks) == 1:
+            compute_partial_into(i, ks[0], o, lse)
+        else:
+            merge_into([compute_partial_into(i, k, None, None) for k in ks], o, lse)
+    barrier()   # every partial has landed in its owner's inbox
+    result = {}
+    for i in plan.chunks_of(rank):
+        srcs = plan.sources_of(i)
+        assert srcs == list(range(len(srcs)))
+        result[i] = finish(i, len(srcs))
     return result

@@ -53,14 +53,15 @@ def test_head_group_sharding_two_gpus():
             _oracle_check(t["q"], t["k"].contiguous(), t["v"].contiguous(), t["out"], t["lse"])
 
 
-@pytest.mark.parametrize("layout", ["zigzag", "contiguous"])
-def test_sequence_chunk_sharding_two_gpus(layout):
+@pytest.mark.parametrize("layout,exchange", [("zigzag", "nccl"), ("contiguous", "nccl"), ("zigzag", "p2p"), ("contiguous", "p2p")])
+def test_sequence_chunk_sharding_two_gpus(layout, exchange):
     _need(2)
     S, Hq, Hkv = 2048, 8, 2
     with tempfile.TemporaryDirectory() as d:
-        extra = ["--contiguous"] if layout == "contiguous" else []
+        extra = (["--contiguous"] if layout == "contiguous" else []) + ["--exchange", exchange]
         res = _torchrun(2, "--mode", "seq", "--seq", str(S), "--q-heads", str(Hq), "--kv-heads", str(Hkv), "--dump", d,
-                        "--steps", "1", *extra)
+                        "--steps", "2", *extra)
+        assert res["exchange"] == exchange
         chunks = {}
         for r in range(2):
             chunks.update(torch.load(os.path.join(d, f"rank{r}.pt")))
