@@ -36,7 +36,7 @@ constexpr int kDecTileKeys = 64;                  // keys per tile (16 per warp)
 constexpr int kDecStages = 3;                     // cp.async ring depth per warp
 constexpr int kDecWarpStageBytes = 16 * kRowBytes * 2;  // 16 K rows + 16 V rows = 8 KB
 constexpr int kDecMaxBatch = 1024;                // prefix table held in shared memory
-constexpr int kDecSmemBytes = kDecWarps * kDecStages * kDecWarpStageBytes + (kDecMaxBatch + 1) * 4;
+constexpr int kDecSmemBytes = kDecWarps * kDecStages * kDecWarpStageBytes + (2 * kDecMaxBatch + 1) * 4;
 
 struct DecodeParams {
     const __nv_bfloat16* q;        // [max_batch, q_heads, 128] (chunk row 0)
@@ -84,15 +84,24 @@ __device__ __forceinline__ int dec_seq_tiles(const DecodeParams& p, int b) {
     return static_cast<int>((n + kDecTileKeys - 1) / kDecTileKeys);
 }
 
-// prefix[b] = sum of tiles of sequences < b, for b in [0, batch]; all threads call.
-__device__ inline void dec_build_prefix(const DecodeParams& p, int* prefix) {
+// prefix[b] = sum of tiles of sequences < b, for b in [0, batch]; lens[b] = keys sequence b
+// attends.  All threads call.  The positions are fetched by as many threads as there are
+// sequences (one global-memory latency, not one per sequence); the running sum over the
+// per-sequence tile counts is then a short loop over shared memory.
+__device__ inline void dec_build_prefix(const DecodeParams& p, int* prefix, int* lens) {
+    for (int b = threadIdx.x; b < p.batch; b += blockDim.x) {
+        const long long len = dec_seq_len(p, b);
+        lens[b] = static_cast<int>(len < 0 ? 0 : len);
+        prefix[b + 1] = dec_seq_tiles(p, b);
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
         int acc = 0;
+        prefix[0] = 0;
         for (int b = 0; b < p.batch; ++b) {
-            prefix[b] = acc;
-            acc += dec_seq_tiles(p, b);
+            acc += prefix[b + 1];
+            prefix[b + 1] = acc;
         }
-        prefix[p.batch] = acc;
     }
     __syncthreads();
 }
@@ -111,13 +120,14 @@ __device__ __forceinline__ int dec_find_seq(const int* prefix, int batch, long l
 
 __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    int* prefix = reinterpret_cast<int*>(smem + kDecWarps * kDecStages * kDecWarpStageBytes);
+    int* prefix = reinterpret_cast<int*>(smem + kDecWarps * kDecStages * kDecWarpStageBytes);   // [kDecMaxBatch + 1]
+    int* lens = prefix + kDecMaxBatch + 1;                                                        // [kDecMaxBatch]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t warp_smem = smem_u32(smem) + warp * kDecStages * kDecWarpStageBytes;
 
     // let a dependent grid (the merge) be set up while this one runs
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    dec_build_prefix(p, prefix);
+    dec_build_prefix(p, prefix, lens);
     if (blockIdx.x == 0)
         for (int i = threadIdx.x; i <= p.batch; i += kDecThreads) p.prefix_out[i] = prefix[i];
     const long long segs_per_seq = static_cast<long long>(p.kv_heads) * p.gtiles;
@@ -139,14 +149,19 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
         const int ntiles = static_cast<int>(piece_end - t);
         const int kvh = seg_in_seq / p.gtiles, gt = seg_in_seq % p.gtiles;
         const long long segment = static_cast<long long>(b) * segs_per_seq + seg_in_seq;
-        const long long len = dec_seq_len(p, b);
+        const long long len = lens[b];
         const int rows_valid = min(16, p.group - gt * 16);
         const long long key0 = p.key_begin + static_cast<long long>(tile0) * kDecTileKeys + warp * 16;
         const __nv_bfloat16* kbase = p.k_cache + b * p.s0 + kvh * p.s1;
         const __nv_bfloat16* vbase = p.v_cache + b * p.s0 + kvh * p.s1;
         // fused append: position of the new token's row and where its K/V come from
-        long long new_pos = p.k_new ? (p.positions ? static_cast<long long>(p.positions[b]) : p.uniform_len - 1) : -1;
-        if (new_pos >= len) new_pos = -1;   // past the cache: nothing is read or written there
+        // the row being appended is the sequence's last key, unless its position lies past the
+        // cache (then len was capped and nothing is read or written there)
+        long long new_pos = -1;
+        if (p.k_new) {
+            const long long uncapped = p.positions ? static_cast<long long>(p.positions[b]) + 1 : p.uniform_len;
+            if (uncapped == len) new_pos = len - 1;
+        }
         const __nv_bfloat16* knew = p.k_new ? p.k_new + (static_cast<long long>(b) * p.kv_heads + kvh) * kHeadDim : nullptr;
         const __nv_bfloat16* vnew = p.k_new ? p.v_new + (static_cast<long long>(b) * p.kv_heads + kvh) * kHeadDim : nullptr;
 
