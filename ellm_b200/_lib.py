@@ -52,6 +52,7 @@ _SIGNATURES = {
     "ellm_attn_merge_partials_f32": (_I, [_VP, _VP, _SZ, _SZ, _SZ, _VP, _VP, _I, _VP]),
     "ellm_attn_run_window": (_I, [_VP, _SZ, _SZ, _SZ, _SZ, _SZ, _VP, _VP]),
     "ellm_attn_decode_noalloc": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _SZ, _SZ, _SZ, _SZ, _SZ, C.POINTER(_SZ), _SZ, C.c_float, _I, _VP]),
+    "ellm_attn_set_option": (_I, [_VP, C.c_char_p, C.c_longlong]),
     "ellm_attn_set_profiling": (_I, [_VP, _I]),
     "ellm_attn_kernel_stats": (_I, [_VP, _I, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
     "ellm_last_error": (C.c_char_p, []),

@@ -71,6 +71,9 @@ class Attention:
                                              _ptr(positions_host), position_index,
                                              position_interval, batch_size))
 
+    def set_option(self, name, value):
+        L.check(self._lib.ellm_attn_set_option(self._h, name.encode(), int(value)))
+
     def set_profiling(self, on):
         L.check(self._lib.ellm_attn_set_profiling(self._h, 1 if on else 0))
 

@@ -645,6 +645,21 @@ int ellm_attn_merge_partials_f32(const float* o_parts, const float* lse_parts, s
     return merge_partials_impl(o_parts, lse_parts, parts, rows, head_size, out, true, lse_out, device, stream);
 }
 
+int ellm_attn_set_option(ellm_attn* h, const char* name, long long value) {
+    if (!h || !name) return fail(ELLM_ERR_INVALID_ARG, "handle and name must be non-NULL");
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (std::strcmp(name, "tc_wait_timeout_ns") == 0) {
+        if (value <= 0) return fail(ELLM_ERR_INVALID_ARG, "tc_wait_timeout_ns must be > 0");
+        h->tc.wait_timeout_ns = static_cast<unsigned long long>(value);
+        return ELLM_OK;
+    }
+    if (std::strcmp(name, "tc_debug_skip_kv_item") == 0) {
+        h->tc.debug_skip_item = value < 0 ? -1 : static_cast<int>(value);
+        return ELLM_OK;
+    }
+    return fail(ELLM_ERR_INVALID_ARG, "unknown option '%s'", name);
+}
+
 int ellm_attn_set_profiling(ellm_attn* h, int on) {
     if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL");
     std::lock_guard<std::mutex> lock(h->mu);

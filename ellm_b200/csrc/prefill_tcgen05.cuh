@@ -59,6 +59,8 @@ struct Tcgen05Plan {
     char why[160] = "";
     void* encode = nullptr;  // cuTensorMapEncodeTiled, fetched from the driver at run time
     int sm_count = 0;
+    unsigned long long wait_timeout_ns = 2000000000ull;   // ellm_attn_set_option("tc_wait_timeout_ns")
+    int debug_skip_item = -1;                              // ellm_attn_set_option("tc_debug_skip_kv_item")
 };
 
 struct TcParams {
@@ -74,6 +76,8 @@ struct TcParams {
     int q_heads, kv_heads, group;
     int pair_tiles;         // 256-row CTA tiles per (sequence, kv head) = ceil(interval * group / 256)
     int pair_major;         // CTA order: 1 = all heads of the heaviest tile first, 0 = head by head
+    unsigned long long wait_timeout_ns;   // bound of every device-side wait
+    int debug_skip_item;    // test hook: ring item (K_0, V_0, K_1, ...) the producer never loads; -1 = none
     float scale_log2;
 };
 
@@ -107,13 +111,13 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 // Bounded wait.  Returns false when the CTA has been told to give up (abort word set by
 // any thread) or when this wait itself ran out, in which case it sets both words.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_word, int* status,
-                                            int code) {
+                                            int code, unsigned long long timeout_ns) {
     const unsigned long long t0 = global_timer_ns();
     for (;;) {
         for (int i = 0; i < 256; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_word) return false;
-        if (global_timer_ns() - t0 > 2000000000ull) {
+        if (global_timer_ns() - t0 > timeout_ns) {
             *abort_word = code;
             atomicCAS(status, 0, code);
             return false;
@@ -121,10 +125,10 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
     }
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_word, int* status,
-                                          int code) {
+                                          int code, unsigned long long timeout_ns) {
     for (int i = 0; i < 64; ++i)
         if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_word, status, code);
+    return mbar_wait_slow(bar, parity, abort_word, status, code, timeout_ns);
 }
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
@@ -368,7 +372,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         bool ok = true;
         for (int j = 0; j < my_steps && ok; ++j) {
             // lane 0 polls the barrier, the warp follows (32 pollers per warp only add shared-memory traffic)
-            ok = lane == 0 ? mbar_wait(bar_s_full(t), j & 1, abort_word, p.status, kTcWaitSFull) : true;
+            ok = lane == 0 ? mbar_wait(bar_s_full(t), j & 1, abort_word, p.status, kTcWaitSFull, p.wait_timeout_ns) : true;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -542,7 +546,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
         }
         if (ok && my_steps > 0) {
-            ok = mbar_wait(bar_pv_done(t), (my_steps - 1) & 1, abort_word, p.status, kTcWaitPvDone);
+            ok = mbar_wait(bar_pv_done(t), (my_steps - 1) & 1, abort_word, p.status, kTcWaitPvDone, p.wait_timeout_ns);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok && my_steps > 0) {
@@ -591,8 +595,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             for (int item = 0; item < 2 * nsteps && ok; ++item) {  // K_0, V_0, K_1, V_1, ...
                 const int slot = item % kTcStages, round = item / kTcStages;
-                ok = mbar_wait(bar_kv_empty(slot), (round & 1) ^ 1, abort_word, p.status, kTcWaitKvEmpty);
+                ok = mbar_wait(bar_kv_empty(slot), (round & 1) ^ 1, abort_word, p.status, kTcWaitKvEmpty, p.wait_timeout_ns);
                 if (!ok) break;
+                if (item == p.debug_skip_item) continue;   // test hook: this item's barrier is never signalled
                 const CUtensorMap* map = (item & 1) ? &map_v : &map_k;
                 const int key0 = (item >> 1) * kTcKeys;
                 mbar_arrive_expect_tx(bar_kv_full(slot), kTcTileBytes);
@@ -602,7 +607,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             if (ok && zero_tail) {
                 const int item = 2 * nsteps - 1, slot = item % kTcStages;   // the last V tile
-                ok = mbar_wait(bar_kv_full(slot), (item / kTcStages) & 1, abort_word, p.status, kTcWaitKvFull);
+                ok = mbar_wait(bar_kv_full(slot), (item / kTcStages) & 1, abort_word, p.status, kTcWaitKvFull, p.wait_timeout_ns);
                 if (ok) {
                     // a 128-byte row of either half holds one key; the swizzle only permutes inside a row
                     const int first = static_cast<int>(key_end - static_cast<long long>(nsteps - 1) * kTcKeys);
@@ -651,11 +656,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // item i of the ring: K_(i/2) for even i, V_(i/2) for odd i
             auto wait_item = [&](int item) {
                 if (zero_tail && item == 2 * nsteps - 1)   // the last V tile is released by the producer's clean-up
-                    return mbar_wait(bar_tail, 0, abort_word, p.status, kTcWaitKvFull);
-                return mbar_wait(bar_kv_full(item % kTcStages), (item / kTcStages) & 1, abort_word, p.status, kTcWaitKvFull);
+                    return mbar_wait(bar_tail, 0, abort_word, p.status, kTcWaitKvFull, p.wait_timeout_ns);
+                return mbar_wait(bar_kv_full(item % kTcStages), (item / kTcStages) & 1, abort_word, p.status, kTcWaitKvFull, p.wait_timeout_ns);
             };
             for (int t = 0; t < kTcTiles && ok; ++t)
-                if (steps[t] > 0) ok = mbar_wait(bar_q(t), 0, abort_word, p.status, kTcWaitQ);
+                if (steps[t] > 0) ok = mbar_wait(bar_q(t), 0, abort_word, p.status, kTcWaitQ, p.wait_timeout_ns);
             if (ok && nsteps > 0) {
                 ok = wait_item(0);
                 if (ok) {
@@ -672,9 +677,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int t = 0; t < kTcTiles && ok; ++t) {
                     if (j >= steps[t]) continue;
 #if ELLM_TC_SPLIT_P
-                    ok = mbar_wait(bar_p_half(t), j & 1, abort_word, p.status, kTcWaitPFull);
+                    ok = mbar_wait(bar_p_half(t), j & 1, abort_word, p.status, kTcWaitPFull, p.wait_timeout_ns);
 #else
-                    ok = mbar_wait(bar_p_full(t), j & 1, abort_word, p.status, kTcWaitPFull);
+                    ok = mbar_wait(bar_p_full(t), j & 1, abort_word, p.status, kTcWaitPFull, p.wait_timeout_ns);
 #endif
                     if (!ok) break;
                     if (!have_v) {
@@ -685,7 +690,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     tc_fence_after();
                     issue_pv_half(t, slot_v, j == 0, 0);
 #if ELLM_TC_SPLIT_P
-                    ok = mbar_wait(bar_p_full(t), j & 1, abort_word, p.status, kTcWaitPFull);
+                    ok = mbar_wait(bar_p_full(t), j & 1, abort_word, p.status, kTcWaitPFull, p.wait_timeout_ns);
                     if (!ok) break;
                     tc_fence_after();
 #endif
@@ -811,6 +816,8 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
     p.base = static_cast<long long>(position_index);
     p.positions = positions;
     p.max_seq = static_cast<long long>(d.max_seq);
+    p.wait_timeout_ns = plan.wait_timeout_ns;
+    p.debug_skip_item = plan.debug_skip_item;
     p.interval = static_cast<int>(interval);
     p.batch = static_cast<int>(batch);
     p.max_batch = static_cast<int>(d.max_batch);

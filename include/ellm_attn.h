@@ -238,6 +238,17 @@ int ellm_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_c
                              const size_t kv_strides[4], size_t max_seq, float scale, int device,
                              void* stream);
 
+/* Named options of a handle.
+ *   "tc_wait_timeout_ns"    bound of every device-side wait of the tcgen05 prefill kernel
+ *                           (default 2 000 000 000); when one runs out the kernel sets a status
+ *                           word, releases its resources and returns, and the call that launched
+ *                           it (or the next synchronising call) returns ELLM_ERR_DEVICE_TIMEOUT.
+ *   "tc_debug_skip_kv_item" test hook for that path: the kernel's loader never fetches ring item
+ *                           N (0 = first K tile, 1 = first V tile, ...) so the wait on it runs
+ *                           out; -1 (default) = off.  The context stays usable afterwards.
+ * Unknown names return ELLM_ERR_INVALID_ARG.  The reference has no counterpart (it aborts). */
+int ellm_attn_set_option(ellm_attn* h, const char* name, long long value);
+
 const char* ellm_last_error(void);   /* thread-local text of the last failure */
 const char* ellm_status_string(int status);
 int ellm_attn_abi_version(void);

@@ -119,3 +119,28 @@ def test_tcgen05_prefill_per_sequence_chunk_starts(positions, interval, q_heads,
     case = Case(seed=900 + interval, interval=interval, batch=len(positions), q_heads=q_heads, kv_heads=kv_heads,
                 max_seq=max(positions) + interval + 70, positions=positions, max_batch=len(positions) + 1)
     _check(case)
+
+
+def test_device_wait_timeout_is_reported_and_the_context_stays_usable():
+    """Failure detection without a fault: the kernel's loader is told to leave one K/V tile's
+    barrier unsignalled (a flag that nothing sets), the wait on it runs out after the configured
+    bound, the kernel releases tensor memory and returns, and the host call reports
+    ELLM_ERR_DEVICE_TIMEOUT.  The same handle then runs normally and matches the oracle."""
+    dev = torch.device("cuda:0")
+    case = Case(seed=77, interval=256, batch=1, q_heads=1, kv_heads=1, max_seq=256, position_index=0)   # one CTA
+    want_k, want_v, want_o, want_l = case.oracle()
+    q, ck, cv = case.q.to(dev), case.cache_k.to(dev), case.cache_v.to(dev)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(256, 1, 1, dtype=torch.float32, device=dev)
+    op = ellm_b200.Attention.new(q, ck, cv, out, 1, 1, 1, 128, case.strides, case.scale, max_seq=256, max_interval=256,
+                                 lse=lse, k_new=case.k_new.to(dev), v_new=case.v_new.to(dev), prefill_kernel=L.PREFILL_TCGEN05)
+    op.set_option("tc_wait_timeout_ns", 200_000_000)     # 0.2 s
+    op.set_option("tc_debug_skip_kv_item", 1)            # the first V tile never arrives
+    with pytest.raises(ellm_b200.EllmError) as e:
+        op.run(0, 256, 1, 1, 0)
+    assert e.value.status == L.ERR_DEVICE_TIMEOUT
+    op.set_option("tc_debug_skip_kv_item", -1)
+    op.run(0, 256, 1, 1, 0)                              # same handle, same context
+    assert_attention_close(case, bits(out), lse.cpu().numpy(), want_o, want_l)
+    with pytest.raises(ellm_b200.EllmError):
+        op.set_option("no_such_option", 1)
