@@ -80,6 +80,21 @@ struct ellm_attn {
     double total_ms[ELLM_KERNEL_COUNT] = {};
     bool profiling = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending[ELLM_KERNEL_COUNT];
+    // ellm_attn_run_host, decode with per-sequence positions: the copies and kernels of a step are
+    // captured once into a CUDA graph and replayed while the caller's buffers stay the same
+    struct HostStepKey {
+        const void *q = nullptr, *k = nullptr, *v = nullptr, *out = nullptr, *lse = nullptr, *pos = nullptr;
+        size_t batch = 0;
+        bool operator==(const HostStepKey& o) const {
+            return q == o.q && k == o.k && v == o.v && out == o.out && lse == o.lse && pos == o.pos && batch == o.batch;
+        }
+    } graph_key;
+    cudaGraphExec_t graph_exec = nullptr;
+    cudaStream_t graph_stream = nullptr;    // own stream: the caller's may be the legacy default stream, which cannot be captured
+    cudaEvent_t graph_event = nullptr;
+    uint64_t graph_launches[ELLM_KERNEL_COUNT] = {};
+    bool graph_disabled = false;
+    bool graph_key_rejected = false;        // graph_key names buffers that are not page-locked
 };
 
 namespace {
@@ -412,6 +427,9 @@ int ellm_attn_destroy(ellm_attn* h) {
             cudaEventDestroy(pr.first);
             cudaEventDestroy(pr.second);
         }
+    if (h->graph_exec) cudaGraphExecDestroy(h->graph_exec);
+    if (h->graph_event) cudaEventDestroy(h->graph_event);
+    if (h->graph_stream) cudaStreamDestroy(h->graph_stream);
     cudaFree(h->part_o);
     cudaFree(h->part_lse);
     cudaFree(h->prefix);
@@ -465,23 +483,97 @@ int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
     const size_t q_pitch = h->d.max_batch * h->d.q_heads * D * 2, q_width = batch_size * h->d.q_heads * D * 2;
     const size_t kv_pitch = h->d.max_batch * h->d.kv_heads * D * 2, kv_width = batch_size * h->d.kv_heads * D * 2;
     const size_t l_pitch = h->d.max_batch * h->d.q_heads * 4, l_width = batch_size * h->d.q_heads * 4;
-    ELLM_CUDA(copy_rows(const_cast<void*>(h->d.q), q_host, q_pitch, q_width, position_interval, cudaMemcpyHostToDevice, h->stream));
-    if (k_new_host) {
-        ELLM_CUDA(copy_rows(const_cast<void*>(h->d.k_new), k_new_host, kv_pitch, kv_width, position_interval, cudaMemcpyHostToDevice, h->stream));
-        ELLM_CUDA(copy_rows(const_cast<void*>(h->d.v_new), v_new_host, kv_pitch, kv_width, position_interval, cudaMemcpyHostToDevice, h->stream));
-    }
-    const int32_t* positions = nullptr;
-    if (positions_host) {
-        ELLM_CUDA(cudaMemcpyAsync(h->positions_dev, positions_host, batch_size * sizeof(int32_t), cudaMemcpyHostToDevice, h->stream));
-        positions = h->positions_dev;
-    }
     const uint64_t tc_before = h->launches[ELLM_KERNEL_PREFILL_TCGEN05];
-    int rc = run_impl(h, positions, position_index, position_interval, batch_size, 0, INT64_MAX, nullptr, h->d.lse,
-                      k_new_host != nullptr, /*enqueue_only=*/1);
+    // everything a step enqueues on `stream`: inputs in, kernels, results out
+    auto enqueue = [&](cudaStream_t stream) -> int {
+        ELLM_CUDA(copy_rows(const_cast<void*>(h->d.q), q_host, q_pitch, q_width, position_interval, cudaMemcpyHostToDevice, stream));
+        if (k_new_host) {
+            ELLM_CUDA(copy_rows(const_cast<void*>(h->d.k_new), k_new_host, kv_pitch, kv_width, position_interval, cudaMemcpyHostToDevice, stream));
+            ELLM_CUDA(copy_rows(const_cast<void*>(h->d.v_new), v_new_host, kv_pitch, kv_width, position_interval, cudaMemcpyHostToDevice, stream));
+        }
+        const int32_t* positions = nullptr;
+        if (positions_host) {
+            ELLM_CUDA(cudaMemcpyAsync(h->positions_dev, positions_host, batch_size * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+            positions = h->positions_dev;
+        }
+        cudaStream_t saved = h->stream;
+        h->stream = stream;
+        int rc = run_impl(h, positions, position_index, position_interval, batch_size, 0, INT64_MAX, nullptr, h->d.lse,
+                          k_new_host != nullptr, /*enqueue_only=*/1);
+        h->stream = saved;
+        if (rc) return rc;
+        ELLM_CUDA(copy_rows(out_host, h->d.out, q_pitch, q_width, position_interval, cudaMemcpyDeviceToHost, stream));
+        if (lse_host)
+            ELLM_CUDA(copy_rows(lse_host, h->d.lse, l_pitch, l_width, position_interval, cudaMemcpyDeviceToHost, stream));
+        return ELLM_OK;
+    };
+
+    // Decode steps with per-sequence positions and pinned buffers repeat identically (only the
+    // buffers' contents change), so the whole step is captured once and replayed.
+    auto pinned = [](const void* ptr) {
+        if (!ptr) return true;
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, ptr) != cudaSuccess) { cudaGetLastError(); return false; }
+        return at.type == cudaMemoryTypeHost;
+    };
+    ellm_attn::HostStepKey key;
+    key.q = q_host; key.k = k_new_host; key.v = v_new_host; key.out = out_host; key.lse = lse_host; key.pos = positions_host;
+    key.batch = batch_size;
+    bool use_graph = position_interval == 1 && positions_host && !h->profiling && !h->graph_disabled;
+    if (use_graph && h->graph_key_rejected && h->graph_key == key) use_graph = false;
+    if (use_graph && !(h->graph_exec && h->graph_key == key)) {
+        // (re)build: the buffers must be page-locked for the copies to be captured
+        if (h->graph_exec) { cudaGraphExecDestroy(h->graph_exec); h->graph_exec = nullptr; }
+        use_graph = pinned(q_host) && pinned(k_new_host) && pinned(v_new_host) && pinned(out_host) && pinned(lse_host) &&
+                    pinned(positions_host);
+        h->graph_key = key;
+        h->graph_key_rejected = !use_graph;
+        if (use_graph && !h->graph_stream) {
+            if (cudaStreamCreateWithFlags(&h->graph_stream, cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&h->graph_event, cudaEventDisableTiming) != cudaSuccess) {
+                cudaGetLastError();
+                h->graph_disabled = true;
+                use_graph = false;
+            }
+        }
+        if (use_graph) {
+            uint64_t before[ELLM_KERNEL_COUNT];
+            for (int i = 0; i < ELLM_KERNEL_COUNT; ++i) before[i] = h->launches[i];
+            cudaGraph_t graph = nullptr;
+            bool ok = cudaStreamBeginCapture(h->graph_stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+            if (ok) {
+                const int rc = enqueue(h->graph_stream);
+                const cudaError_t e = cudaStreamEndCapture(h->graph_stream, &graph);
+                ok = rc == ELLM_OK && e == cudaSuccess && graph != nullptr;
+            }
+            if (ok) ok = cudaGraphInstantiate(&h->graph_exec, graph, 0) == cudaSuccess;
+            if (graph) cudaGraphDestroy(graph);
+            for (int i = 0; i < ELLM_KERNEL_COUNT; ++i) {   // the capture launched nothing yet
+                h->graph_launches[i] = h->launches[i] - before[i];
+                h->launches[i] = before[i];
+            }
+            if (!ok) {
+                cudaGetLastError();
+                h->graph_exec = nullptr;
+                h->graph_disabled = true;   // fall back to plain enqueues for this handle
+                use_graph = false;
+            } else {
+                h->graph_key = key;
+            }
+        }
+    }
+    if (use_graph) {
+        // order after whatever the caller queued on the handle's stream, then replay
+        ELLM_CUDA(cudaEventRecord(h->graph_event, h->stream));
+        ELLM_CUDA(cudaStreamWaitEvent(h->graph_stream, h->graph_event, 0));
+        ELLM_CUDA(cudaGraphLaunch(h->graph_exec, h->graph_stream));
+        for (int i = 0; i < ELLM_KERNEL_COUNT; ++i) h->launches[i] += h->graph_launches[i];
+        ELLM_CUDA(cudaStreamSynchronize(h->graph_stream));
+        return ELLM_OK;
+    }
+
+    int rc = enqueue(h->stream);
     if (rc) return rc;
-    ELLM_CUDA(copy_rows(out_host, h->d.out, q_pitch, q_width, position_interval, cudaMemcpyDeviceToHost, h->stream));
-    if (lse_host)
-        ELLM_CUDA(copy_rows(lse_host, h->d.lse, l_pitch, l_width, position_interval, cudaMemcpyDeviceToHost, h->stream));
     // only the tcgen05 kernel has device-side waits that can run out
     const bool read_status = h->launches[ELLM_KERNEL_PREFILL_TCGEN05] != tc_before;
     if (read_status) ELLM_CUDA(cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream));

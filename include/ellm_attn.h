@@ -109,7 +109,9 @@ int ellm_attn_run_ragged(ellm_attn* h, const int32_t* positions, size_t position
  * buffers are host allocations, src/memory/allocator.rs:4-27): copies q (and
  * k_new/v_new, positions when non-NULL) to the handle's bound device buffers,
  * runs, copies out (and lse) back, and returns when the results are in host
- * memory.  The KV cache stays resident on the device. */
+ * memory.  The KV cache stays resident on the device.  Decode steps with positions_host and
+ * page-locked buffers are captured once into a CUDA graph and replayed for as long as the same
+ * buffers are passed.  Calls on one handle must not overlap. */
 int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
                        const void* v_new_host, void* out_host, float* lse_host,
                        const int32_t* positions_host, size_t position_index,

@@ -192,3 +192,44 @@ def test_error_paths_on_a_live_handle():
     assert op.kernel_stats()["decode_splitkv"][0] == 0
     op.run(3, 1, 2, 8, 0)
     assert op.kernel_stats()["decode_splitkv"][0] == 1
+
+
+def test_run_host_replays_its_graph_with_new_contents():
+    """Decode through host buffers, three steps with the same page-locked buffers and different
+    contents (and advancing positions): every step matches the oracle."""
+    import oracle
+    from helpers import O_MAX_ABS, LSE_MAX_ABS
+    dev = torch.device("cuda:0")
+    B, Hq, Hkv, max_seq = 3, 8, 2, 400
+    g = torch.Generator().manual_seed(123)
+    ck = torch.randn(B, Hkv, max_seq, 128, generator=g).to(torch.bfloat16)
+    cv = torch.randn(B, Hkv, max_seq, 128, generator=g).to(torch.bfloat16)
+    strides = [Hkv * max_seq * 128, max_seq * 128, 128, 1]
+    dq = torch.zeros(1, B, Hq, 128, dtype=torch.bfloat16, device=dev)
+    dkn = torch.zeros(1, B, Hkv, 128, dtype=torch.bfloat16, device=dev)
+    dvn = torch.zeros_like(dkn)
+    dout = torch.zeros_like(dq)
+    dlse = torch.zeros(1, B, Hq, dtype=torch.float32, device=dev)
+    dck, dcv = ck.to(dev), cv.to(dev)
+    op = ellm_b200.Attention.new(dq, dck, dcv, dout, B, Hq, Hkv, 128, strides, 0.0884, max_seq=max_seq, lse=dlse, k_new=dkn, v_new=dvn)
+    qh = torch.zeros(1, B, Hq, 128, dtype=torch.bfloat16).pin_memory()
+    knh = torch.zeros(1, B, Hkv, 128, dtype=torch.bfloat16).pin_memory()
+    vnh = torch.zeros_like(knh).pin_memory()
+    oh = torch.zeros_like(qh).pin_memory()
+    lh = torch.zeros(1, B, Hq, dtype=torch.float32).pin_memory()
+    ph = torch.tensor([10, 200, 57], dtype=torch.int32).pin_memory()
+    ref_k, ref_v = bits(ck).copy(), bits(cv).copy()
+    for step in range(3):
+        qh.copy_(torch.randn(1, B, Hq, 128, generator=g).to(torch.bfloat16))
+        knh.copy_(torch.randn(1, B, Hkv, 128, generator=g).to(torch.bfloat16))
+        vnh.copy_(torch.randn(1, B, Hkv, 128, generator=g).to(torch.bfloat16))
+        op.run_host(qh, oh, 0, 1, B, k_new_host=knh, v_new_host=vnh, lse_host=lh, positions_host=ph)
+        pos = ph.numpy().copy()
+        for cache, new in ((ref_k, knh), (ref_v, vnh)):
+            oracle.kv_append_bf16(cache, bits(new), strides, B, Hkv, 128, 0, 1, B, positions=pos)
+        want_o, want_l = oracle.attention_bf16(bits(qh), ref_k, ref_v, strides, Hq, Hkv, 0.0884, 0, 1, B, positions=pos)
+        assert np.abs(oh.float().numpy() - oracle.bf16_bits_to_f32(want_o)).max() <= O_MAX_ABS
+        assert np.abs(lh.numpy() - want_l).max() <= LSE_MAX_ABS
+        ph += 1
+    assert np.array_equal(bits(dck), ref_k) and np.array_equal(bits(dcv), ref_v)
+    assert op.kernel_stats()["decode_splitkv"][0] == 3
