@@ -376,12 +376,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-#if defined(ELLM_WHATIF_NOSOFTMAX)
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_p_full(t));
-            continue;
-#endif
             const long long key0 = static_cast<long long>(j) * kTcKeys;
             const bool edge = key0 + kTcKeys - 1 > tile_min_lim;   // the causal edge crosses this tile
             const long long dlim = lim - key0;                     // last column this row may see
@@ -514,9 +508,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                             const int c = half * 32 + cc;
                             const uint64_t x2 = fma2(pack2(s[2 * cc], s[2 * cc + 1]), scale2, negm2);
                             uint64_t p2;
-#if defined(ELLM_WHATIF_NOEXP)
-                            if (true) { p2 = x2; } else
-#endif
                             if (kTcPolyEvery > 0 && (c % kTcPolyEvery) == kTcPolyEvery - 1) {
                                 p2 = exp2_poly2(x2);
                             } else {
