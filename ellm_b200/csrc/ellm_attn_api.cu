@@ -297,7 +297,7 @@ int finish(ellm_attn* h, bool enqueue_only) {
 // Common body of run / run_ragged / run_window.
 int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size_t interval,
              size_t batch, long long key_begin, long long key_end, float* out_f32, float* lse_out,
-             bool append, int enqueue_only = -1) {
+             bool append, int enqueue_only = -1, const cudaStream_t* stream_override = nullptr) {
     if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL");
     if (interval == 0 || batch == 0) return ELLM_OK;  // nothing to do, as an empty assign() range
     if (batch > h->d.max_batch) return fail(ELLM_ERR_INVALID_ARG, "batch_size %zu > max_batch %zu", batch, h->d.max_batch);
@@ -311,6 +311,14 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
     DeviceGuard guard(h->d.device);
     if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", h->d.device);
     std::lock_guard<std::mutex> lock(h->mu);
+    // a caller may direct this one step to another stream (the host-buffer entry point's graph
+    // stream); the handle's stream is put back before the lock is released
+    struct StreamSwap {
+        ellm_attn* h;
+        cudaStream_t saved;
+        StreamSwap(ellm_attn* h_, const cudaStream_t* o) : h(h_), saved(h_->stream) { if (o) h->stream = *o; }
+        ~StreamSwap() { h->stream = saved; }
+    } swap(h, stream_override);
     const bool no_sync = enqueue_only < 0 ? h->d.async != 0 : enqueue_only != 0;
     int rc;
     const bool do_append = append && h->d.k_new;
@@ -496,11 +504,8 @@ int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
             ELLM_CUDA(cudaMemcpyAsync(h->positions_dev, positions_host, batch_size * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
             positions = h->positions_dev;
         }
-        cudaStream_t saved = h->stream;
-        h->stream = stream;
         int rc = run_impl(h, positions, position_index, position_interval, batch_size, 0, INT64_MAX, nullptr, h->d.lse,
-                          k_new_host != nullptr, /*enqueue_only=*/1);
-        h->stream = saved;
+                          k_new_host != nullptr, /*enqueue_only=*/1, &stream);
         if (rc) return rc;
         ELLM_CUDA(copy_rows(out_host, h->d.out, q_pitch, q_width, position_interval, cudaMemcpyDeviceToHost, stream));
         if (lse_host)

@@ -59,6 +59,10 @@ struct Tcgen05Plan {
     char why[160] = "";
     void* encode = nullptr;  // cuTensorMapEncodeTiled, fetched from the driver at run time
     int sm_count = 0;
+    // the tensor maps of the last launch, reused when the next one has the same geometry
+    CUtensorMap map_q, map_k, map_v;
+    size_t cached_interval = 0, cached_batch = 0;
+    long long cached_kv_rows = -1;
     unsigned long long wait_timeout_ns = 2000000000ull;   // ellm_attn_set_option("tc_wait_timeout_ns")
     int debug_skip_item = -1;                              // ellm_attn_set_option("tc_debug_skip_kv_item")
 };
@@ -773,8 +777,13 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
         return ELLM_ERR_UNSUPPORTED;
     }
     EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(plan.encode);
-    CUtensorMap map_q, map_k, map_v;
-    {
+    CUtensorMap& map_q = plan.map_q;
+    CUtensorMap& map_k = plan.map_k;
+    CUtensorMap& map_v = plan.map_v;
+    // the buffers, head counts and strides are fixed for the handle: the maps depend only on these
+    const bool reuse = plan.cached_kv_rows == kv_rows && plan.cached_interval == interval && plan.cached_batch == batch;
+    plan.cached_kv_rows = -1;
+    if (!reuse) {
         // q viewed as [head_dim, g, chunk row, kv head, sequence]; a box is 64 x G x (128/G) packed rows
         cuuint64_t dims[5] = {128, static_cast<cuuint64_t>(group), interval, d.kv_heads, d.max_batch};
         cuuint64_t strides[4] = {256, d.max_batch * d.q_heads * 256, static_cast<cuuint64_t>(group) * 256, d.q_heads * 256};
@@ -787,7 +796,7 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
             return ELLM_ERR_UNSUPPORTED;
         }
     }
-    for (int which = 0; which < 2; ++which) {
+    for (int which = 0; which < 2 && !reuse; ++which) {
         cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(kv_rows), d.kv_heads, batch};
         cuuint64_t strides[3] = {d.kv_strides[2] * 2, d.kv_strides[1] * 2, d.kv_strides[0] * 2};
         cuuint32_t box[4] = {64, 128, 1, 1};
@@ -799,6 +808,9 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
             return ELLM_ERR_UNSUPPORTED;
         }
     }
+    plan.cached_kv_rows = kv_rows;
+    plan.cached_interval = interval;
+    plan.cached_batch = batch;
     TcParams p;
     p.out = out_f32 ? static_cast<void*>(out_f32) : d.out;
     p.key_end = kv_rows;
