@@ -10,4 +10,5 @@ from ._lib import (  # noqa: F401
 )
 from .attention import Attention, decode_noalloc, kv_append, merge_partials, qk_norm_rope_append, rms_norm  # noqa: F401
 from .kv_cache import StaticKVCache  # noqa: F401
+from .projection import MatMul3, MatMulAdd  # noqa: F401
 from .rope import precompute_freqs_cis  # noqa: F401

@@ -34,6 +34,27 @@ class AttnDesc(C.Structure):
     ]
 
 
+class MatMul3Desc(C.Structure):
+    _fields_ = [
+        ("hidden", C.c_void_p), ("hidden_row_stride", C.c_size_t), ("wq_nt", C.c_void_p), ("wk_nt", C.c_void_p),
+        ("wv_nt", C.c_void_p), ("q_state", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+        ("kv_strides", C.c_size_t * 4), ("rope", C.c_void_p), ("rope_rows", C.c_size_t),
+        ("q_norm_weight", C.c_void_p), ("k_norm_weight", C.c_void_p), ("head_dim", C.c_size_t),
+        ("m_row", C.c_size_t), ("col", C.c_size_t), ("b_q_row", C.c_size_t), ("b_kv_row", C.c_size_t),
+        ("max_batch", C.c_size_t), ("max_seq", C.c_size_t), ("eps", C.c_float), ("device", C.c_int),
+        ("stream", C.c_void_p), ("async_", C.c_int),
+    ]
+
+
+class MatMulAddDesc(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("a_row_stride", C.c_size_t), ("w_nt", C.c_void_p), ("residual", C.c_void_p),
+        ("residual_row_stride", C.c_size_t), ("output", C.c_void_p), ("output_row_stride", C.c_size_t),
+        ("m_max", C.c_size_t), ("n_max", C.c_size_t), ("k_max", C.c_size_t), ("max_batch", C.c_size_t),
+        ("device", C.c_int), ("stream", C.c_void_p), ("async_", C.c_int),
+    ]
+
+
 _lib = None
 
 _SZ, _VP, _I = C.c_size_t, C.c_void_p, C.c_int
@@ -55,6 +76,16 @@ _SIGNATURES = {
     "ellm_attn_set_option": (_I, [_VP, C.c_char_p, C.c_longlong]),
     "ellm_attn_set_profiling": (_I, [_VP, _I]),
     "ellm_attn_kernel_stats": (_I, [_VP, _I, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
+    "ellm_matmul3_create": (_I, [C.POINTER(MatMul3Desc), C.POINTER(_VP)]),
+    "ellm_matmul3_destroy": (_I, [_VP]),
+    "ellm_matmul3_run": (_I, [_VP, _SZ, _SZ, _SZ, _SZ, _SZ]),
+    "ellm_matmul3_run_ragged": (_I, [_VP, _VP, _SZ, _SZ, _SZ, _SZ]),
+    "ellm_matmul_add_create": (_I, [C.POINTER(MatMulAddDesc), C.POINTER(_VP)]),
+    "ellm_matmul_add_destroy": (_I, [_VP]),
+    "ellm_matmul_add_run": (_I, [_VP, _SZ, _SZ, _SZ, _SZ, _SZ]),
+    "ellm_matmul_set_profiling": (_I, [_VP, _I, _I]),
+    "ellm_matmul_kernel_stats": (_I, [_VP, _I, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
+    "ellm_matmul_set_wait_timeout": (_I, [_VP, _I, C.c_ulonglong]),
     "ellm_last_error": (C.c_char_p, []),
     "ellm_status_string": (C.c_char_p, [_I]),
     "ellm_attn_abi_version": (_I, []),
@@ -62,10 +93,13 @@ _SIGNATURES = {
 
 
 def header_symbols():
-    """Names of the functions include/ellm_attn.h declares (parsed from the header)."""
-    with open(os.path.join(_build.INCLUDE, "ellm_attn.h")) as f:
-        text = re.sub(r"/\*.*?\*/", "", f.read(), flags=re.S)
-    return sorted(set(re.findall(r"\b(ellm_[a-z0-9_]+)\s*\(", text)))
+    """Names of the functions the C headers under include/ declare (parsed from the headers)."""
+    names = set()
+    for header in ("ellm_attn.h", "ellm_proj.h"):
+        with open(os.path.join(_build.INCLUDE, header)) as f:
+            text = re.sub(r"/\*.*?\*/", "", f.read(), flags=re.S)
+        names.update(re.findall(r"\b(ellm_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def load():

@@ -19,7 +19,7 @@ NVCC_FLAGS = [
 
 
 def sources():
-    out = [os.path.join(INCLUDE, "ellm_attn.h")]
+    out = [os.path.join(INCLUDE, "ellm_attn.h"), os.path.join(INCLUDE, "ellm_proj.h")]
     for name in sorted(os.listdir(CSRC)):
         if name.endswith((".cu", ".cuh", ".h")):
             out.append(os.path.join(CSRC, name))

@@ -910,3 +910,5 @@ extern "C" int ellm_attn_decode_noalloc(const void* q, const void* k_cache, cons
     return ELLM_OK;
 }
 
+
+#include "ellm_proj_api.cuh"

@@ -9,9 +9,14 @@ Per layer, following the reference's decoder layer and attention block minus the
     a   = Attention(q, cache)                      ellm_attn_run
     x   = x + a Wo^T                               matmul_add (src/compiler/mul/matmul_add.rs:186-226)
 
-The projections are library calls (torch / cuBLAS): they are the path's neighbours, not the
-path.  The input norm, the norm+rope+append step and attention are this repository's kernels.  Decode steps can be captured once in a CUDA graph and replayed: every kernel takes
-the per-sequence positions from a device array that the graph itself advances.
+Chunks of at least `tensor_core_rows` rows run the projections on this repository's tcgen05
+kernel: MatMul3 with the norm + rope + cache write in its epilogue, and MatMulAdd with the
+residual in its epilogue (ellm_b200/projection.py).  Shorter chunks (decode steps) use library
+GEMMs (torch / cuBLAS) followed by the separate norm + rope + append kernel: a 128-row tile would
+be nearly empty there and the step is bound by streaming the weights, not by the tensor cores.
+The input norm and attention are this repository's kernels on both paths.  Decode steps can be
+captured once in a CUDA graph and replayed: every kernel takes the per-sequence positions from a
+device array that the graph itself advances.
 """
 import numpy as np
 import torch
@@ -19,12 +24,14 @@ import torch
 from . import _lib as L
 from .attention import Attention, qk_norm_rope_append, rms_norm
 from .kv_cache import StaticKVCache
+from .projection import MatMul3, MatMulAdd
 from .rope import precompute_freqs_cis
 
 
 class AttentionStack:
     def __init__(self, layers, hidden, q_heads, kv_heads, max_seq, max_interval, *, head_dim=128, theta=1e6,
-                 eps=1e-6, seed=3, device="cuda:0", stream=None, max_batch=1):
+                 eps=1e-6, seed=3, device="cuda:0", stream=None, max_batch=1, projections="tcgen05",
+                 tensor_core_rows=128):
         dev = torch.device(device)
         self.dev, self.layers, self.hidden = dev, layers, hidden
         self.q_heads, self.kv_heads, self.head_dim = q_heads, kv_heads, head_dim
@@ -54,13 +61,38 @@ class AttentionStack:
         self.a = torch.zeros_like(self.q)
         self.positions = torch.zeros(max_batch, dtype=torch.int32, device=dev)
         self.scale = 1.0 / np.sqrt(head_dim)
-        self.ops = []
+        self.ops, self.qkv_ops, self.out_ops = [], [], []
+        if projections not in ("tcgen05", "library"):
+            raise ValueError("projections must be 'tcgen05' or 'library'")
+        self.tensor_core_rows = tensor_core_rows if projections == "tcgen05" else None
+        self.x = torch.zeros(rows, hidden, dtype=torch.bfloat16, device=dev)   # the residual stream, updated in place
+        dev_index, raw_stream = dev.index or 0, self.stream.cuda_stream
         for i in range(layers):
             ck, cv = self.cache.layer(i)
             self.ops.append(Attention.new(self.q, ck, cv, self.a, max_batch, q_heads, kv_heads, head_dim,
                                           self.cache.strides, self.scale, max_seq=max_seq, max_interval=max_interval,
-                                          device=dev.index or 0, stream=self.stream.cuda_stream, async_=True))
+                                          device=dev_index, stream=raw_stream, async_=True))
+            if self.tensor_core_rows is not None:
+                self.qkv_ops.append(MatMul3.new(self.h, self.wq[i], self.q, self.wk[i], ck, self.wv[i], cv, self.rope,
+                                                head_dim, rows, hidden, qd, kd, kv_strides=self.cache.strides,
+                                                max_batch=max_batch, max_seq=max_seq, rope_rows=max_seq, eps=eps,
+                                                q_norm_weight=self.q_norm[i], k_norm_weight=self.k_norm[i],
+                                                device=dev_index, stream=raw_stream, async_=True))
+                self.out_ops.append(MatMulAdd.new(self.a, self.wo[i], self.x, self.x, rows, hidden, qd,
+                                                  max_batch=max_batch, device=dev_index, stream=raw_stream, async_=True))
         self._rows = rows
+
+    def _layer_tensor_core(self, i, n, batch, position_index, ragged):
+        """One layer on self.x[:n * max_batch] in place, projections on the tcgen05 kernel."""
+        rows = n * self.max_batch
+        rms_norm(self.x[:rows], self.h[:rows], self.eps, device=self.dev.index or 0, stream=self.stream.cuda_stream)
+        if ragged:
+            self.qkv_ops[i].run_ragged(self.positions, n, batch)
+            self.ops[i].run_ragged(self.positions, n, batch, 1, 0)
+        else:
+            self.qkv_ops[i].run(position_index, n, batch)
+            self.ops[i].run(position_index, n, batch, 1, 0)
+        self.out_ops[i].run(position_index, n, batch)
 
     def _layer(self, i, x, n, batch, position_index, ragged):
         """x: [n * max_batch, hidden] bf16 (rows ordered chunk row, then sequence)."""
@@ -88,10 +120,17 @@ class AttentionStack:
         """One pass of all layers over a chunk: x [n, max_batch, hidden] -> same shape."""
         n = x.shape[0]
         batch = self.max_batch if batch is None else batch
-        y = x.reshape(n * self.max_batch, self.hidden)
+        rows = n * self.max_batch
+        y = x.reshape(rows, self.hidden)
         with torch.cuda.stream(self.stream):
-            for i in range(self.layers):
-                y = self._layer(i, y, n, batch, position_index, ragged)
+            if self.tensor_core_rows is not None and rows >= self.tensor_core_rows:
+                self.x[:rows].copy_(y)
+                for i in range(self.layers):
+                    self._layer_tensor_core(i, n, batch, position_index, ragged)
+                y = self.x[:rows].clone()
+            else:
+                for i in range(self.layers):
+                    y = self._layer(i, y, n, batch, position_index, ragged)
         return y.view(n, self.max_batch, self.hidden)
 
     def capture_decode_step(self, x_static):
@@ -111,7 +150,7 @@ class AttentionStack:
         return graph, out
 
     def close(self):
-        for op in self.ops:
+        for op in self.ops + self.qkv_ops + self.out_ops:
             op.close()
 
 
@@ -130,13 +169,15 @@ def main():
     ap.add_argument("--prefill", type=int, default=32768)
     ap.add_argument("--decode", type=int, default=256)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--projections", choices=["tcgen05", "library"], default="tcgen05")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     stream = torch.cuda.Stream(dev)
     S = args.prefill
     max_seq = S + args.decode + 8
-    stack = AttentionStack(args.layers, args.hidden, args.q_heads, args.kv_heads, max_seq, S, stream=stream)
+    stack = AttentionStack(args.layers, args.hidden, args.q_heads, args.kv_heads, max_seq, S, stream=stream,
+                           projections=args.projections)
     g = torch.Generator(device=dev).manual_seed(3)
     x0 = torch.randn(S, 1, args.hidden, device=dev, generator=g).to(torch.bfloat16)
     with torch.cuda.stream(stream):
@@ -181,7 +222,7 @@ def main():
                     f"prefill {S} then {args.decode} decode steps, 1 sequence, synthetic weights and activations",
         "ttft_ms": ttft, "prefill_tflops": (flops_attn + flops_proj) / ttft / 1e9,
         "prefill_attention_flops_share": flops_attn / (flops_attn + flops_proj),
-        "tpot_ms": tpot, "decode_gbs": (kv_bytes + w_bytes) / tpot / 1e6, "decode_cuda_graph": not args.no_graph,
+        "prefill_projections": args.projections, "tpot_ms": tpot, "decode_gbs": (kv_bytes + w_bytes) / tpot / 1e6, "decode_cuda_graph": not args.no_graph,
         "final_positions": int(stack.positions[0]), "finite": bool(torch.isfinite(x1.float()).all())}))
     stack.close()
 

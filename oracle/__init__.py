@@ -14,6 +14,7 @@ from .binding import (  # noqa: F401
     flash_attention_f32,
     kv_append_bf16,
     load,
+    matmul_nt_bf16,
     merge_partials,
     qk_norm_rope_append_bf16,
     rope_table,

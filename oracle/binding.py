@@ -59,6 +59,8 @@ def load():
     lib.oracle_qk_norm_rope_append_bf16.restype = None
     lib.oracle_qk_norm_rope_append_bf16.argtypes = ([C.c_void_p] * 9 + [C.POINTER(C.c_size_t)] + [C.c_size_t] * 5
                                                      + [C.c_void_p, C.c_size_t, C.c_size_t, C.c_float])
+    lib.oracle_matmul_nt_bf16.restype = None
+    lib.oracle_matmul_nt_bf16.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p] + [C.c_size_t] * 5
     lib.oracle_f32_to_bf16.restype = C.c_uint16
     lib.oracle_f32_to_bf16.argtypes = [C.c_float]
     lib.oracle_f16_available.restype = C.c_int
@@ -225,3 +227,17 @@ def qk_norm_rope_append_bf16(q_in, k_in, v_in, k_cache, v_cache, rope, kv_stride
         _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(qw), _ptr(kw), _ptr(rope), (C.c_size_t * 4)(*kv_strides),
         max_batch, q_heads, kv_heads, d, position_index, _ptr(pos), position_interval, batch_size, eps)
     return q_out
+
+
+def matmul_nt_bf16(a, w_nt, residual=None, threads=None):
+    """bf16 bits: (residual +) a[m, k] . w_nt[n, k]^T with fp32 accumulation, rounded once."""
+    a = np.ascontiguousarray(a, dtype=np.uint16)
+    w_nt = np.ascontiguousarray(w_nt, dtype=np.uint16)
+    m, k = a.shape
+    n = w_nt.shape[0]
+    assert w_nt.shape[1] == k
+    res = None if residual is None else np.ascontiguousarray(residual, dtype=np.uint16)
+    out = np.zeros((m, n), dtype=np.uint16)
+    threads = threads or min(os.cpu_count() or 1, 16)
+    load().oracle_matmul_nt_bf16(_ptr(a), k, _ptr(w_nt), _ptr(res), n, _ptr(out), n, m, n, k, threads)
+    return out

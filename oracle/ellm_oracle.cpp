@@ -20,6 +20,8 @@
 //   oracle_complex_mul_f32        src/kernel/generic/complex_mul.rs:3-20
 //   oracle_precompute_freqs_cis   src/qwen3_moe/rope.rs:7-28
 //   oracle_qk_norm_rope_append    src/kernel/x86_64/f16_512/matmul_rms_complex.rs:76-96
+//   oracle_matmul_nt_bf16         src/compiler/mul/matmul_add.rs:128-232 (C = residual, C += A x B),
+//                                 src/compiler/mul/matmul3.rs:289-385 (the three projections)
 //
 // Pinning.  The reference's own tests for this path hold only uniform-input
 // known-answer cases (all-ones attention -> all-ones output, 1*1+2*2=5,
@@ -397,6 +399,41 @@ void oracle_qk_norm_rope_append_bf16(const uint16_t* q_in, const uint16_t* k_in,
                 for (size_t c = 0; c < D; ++c) v_cache[dst + c * kv_strides[3]] = v_in[off + c];
             }
         }
+}
+
+// C = (residual +) A . W_nt^T, the arithmetic of the reference's projection operators
+// (src/compiler/mul/matmul_add.rs:128-232: tile <- residual, then tile += A x B over the k blocks;
+// src/compiler/mul/matmul3.rs:289-385 without a residual).  A is [m x k] with lda elements between
+// rows, W_nt is [n x k] contiguous.  The reference accumulates in its storage type; here, as for
+// attention, products and sums are fp32 (k ascending, the residual added last) and the result is
+// rounded to bf16 once.  Rows are split over `threads` with assign().
+void oracle_matmul_nt_bf16(const uint16_t* a, size_t lda, const uint16_t* w_nt, const uint16_t* residual,
+                           size_t ldr, uint16_t* out, size_t ldc, size_t m, size_t n, size_t k, size_t threads) {
+    if (threads == 0) threads = 1;
+    std::vector<float> wf(n * k);
+    for (size_t i = 0; i < n * k; ++i) wf[i] = bf16_to_f32(w_nt[i]);
+    auto work = [&](size_t tid) {
+        size_t begin = 0, end = 0;
+        if (!oracle_assign(m, threads, tid, &begin, &end)) return;
+        std::vector<float> row(k);
+        for (size_t i = begin; i < end; ++i) {
+            for (size_t c = 0; c < k; ++c) row[c] = bf16_to_f32(a[i * lda + c]);
+            for (size_t j = 0; j < n; ++j) {
+                const float* w = wf.data() + j * k;
+                float acc = 0.0f;
+                for (size_t c = 0; c < k; ++c) acc = acc + row[c] * w[c];
+                if (residual) acc = acc + bf16_to_f32(residual[i * ldr + j]);
+                out[i * ldc + j] = f32_to_bf16(acc);
+            }
+        }
+    };
+    if (threads == 1) {
+        work(0);
+        return;
+    }
+    std::vector<std::thread> pool;
+    for (size_t t = 0; t < threads; ++t) pool.emplace_back(work, t);
+    for (auto& t : pool) t.join();
 }
 
 uint16_t oracle_f32_to_bf16(float f) { return f32_to_bf16(f); }

@@ -51,6 +51,8 @@ void oracle_qk_norm_rope_append_bf16(const uint16_t* q_in, const uint16_t* k_in,
                                      size_t kv_heads, size_t head_size, size_t position_index,
                                      const int32_t* positions, size_t position_interval, size_t batch_size,
                                      float eps);
+void oracle_matmul_nt_bf16(const uint16_t* a, size_t lda, const uint16_t* w_nt, const uint16_t* residual,
+                           size_t ldr, uint16_t* out, size_t ldc, size_t m, size_t n, size_t k, size_t threads);
 uint16_t oracle_f32_to_bf16(float f);
 float oracle_bf16_to_f32(uint16_t h);
 

@@ -1,0 +1,163 @@
+"""The tensor-core projections (MatMul3 with its fused norm + rope + cache write, MatMulAdd)
+against the CPU oracle, through the C ABI (B200 only).
+
+The oracle sums a dot product in k order in fp32; the tensor core sums the same fp32 products in
+another order, so a result may land one bf16 step away from the oracle's.  For the fused
+projection that step happens before the norm, so the bar is the one of the norm + rope kernel:
+nearly all values bit-equal, the rest within a bf16 step of the larger member of their rotation
+pair (the rotation mixes the pair, so a small output inherits the step of its large partner).
+Rows and cache lines the kernels must not touch are bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+import ellm_b200
+import oracle
+from ellm_b200.projection import MatMul3, MatMulAdd
+from helpers import bits
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _close(got, want, exact_min, steps=1, atol=0.0):
+    g32, w32 = oracle.bf16_bits_to_f32(got), oracle.bf16_bits_to_f32(want)
+    assert np.isfinite(g32).all()
+    exact = (got == want).mean()
+    assert exact >= exact_min, exact
+    assert (np.abs(g32 - w32) <= steps * np.abs(w32) * 2.0 ** -7 + atol).all(), np.abs(g32 - w32).max()
+
+
+def _close_rotated(got, want):
+    g32, w32 = oracle.bf16_bits_to_f32(got), oracle.bf16_bits_to_f32(want)
+    assert np.isfinite(g32).all()
+    assert (got == want).mean() >= 0.97, (got == want).mean()
+    pair = np.abs(w32).reshape(-1, 2).max(axis=1, keepdims=True).repeat(2, axis=1).reshape(w32.shape)
+    d = np.abs(g32 - w32)
+    assert (d <= 2 * pair * 2.0 ** -7 + 1e-30).all(), d.max()
+    assert d.mean() <= 2e-4, d.mean()
+
+
+def _matmul_add(seed, interval, max_batch, batch, n, k, residual, in_place=False, a_pad=0):
+    g = torch.Generator().manual_seed(seed)
+    m = interval * max_batch
+    a_full = torch.randn(m, k + a_pad, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16)
+    res = torch.randn(m, n, generator=g).to(torch.bfloat16) if residual else None
+    canary = torch.randn(m, n, generator=g).to(torch.bfloat16)
+    want = oracle.matmul_nt_bf16(bits(a_full)[:, :k], bits(w), None if res is None else bits(res))
+    da, dw = a_full.to(DEV), w.to(DEV)
+    dres = None if res is None else res.to(DEV)
+    out = dres if in_place else canary.to(DEV)
+    op = MatMulAdd.new(da, dw, dres, out, m, n, k, max_batch=max_batch, a_row_stride=k + a_pad)
+    op.run(0, interval, batch)
+    got = bits(out).reshape(interval, max_batch, n)
+    want = want.reshape(interval, max_batch, n)
+    # the accumulated rounding of k fp32 additions, against values of size ~ sqrt(k) * 0.05
+    _close(got[:, :batch], want[:, :batch], 0.99, atol=2e-5 * np.sqrt(k))
+    if batch < max_batch:   # dead sequence slots keep what they held
+        before = bits(res if in_place else canary).reshape(interval, max_batch, n)
+        assert np.array_equal(got[:, batch:], before[:, batch:])
+    assert op.kernel_stats()[0] == 1
+    op.close()
+
+
+def test_matmul_plain_ragged_edges():
+    _matmul_add(1, interval=300, max_batch=1, batch=1, n=200, k=256, residual=False)
+
+
+def test_matmul_add_residual_in_place_dead_slots():
+    _matmul_add(2, interval=67, max_batch=3, batch=2, n=640, k=192, residual=True, in_place=True)
+
+
+def test_matmul_add_strided_a_many_k_blocks():
+    # 32 k-blocks go eight times round the 4-slot ring; 20 column tiles x 8 row tiles > SMs
+    _matmul_add(3, interval=1024, max_batch=1, batch=1, n=5120, k=2048, residual=True, a_pad=64)
+
+
+def test_matmul_decode_rows():
+    _matmul_add(4, interval=1, max_batch=16, batch=16, n=2048, k=4096, residual=True)
+
+
+def _matmul3(seed, interval, max_batch, batch, q_heads, kv_heads, hidden, max_seq, position_index=0, positions=None,
+             weights=True):
+    g = torch.Generator().manual_seed(seed)
+    m = interval * max_batch
+    x = torch.randn(m, hidden, generator=g).to(torch.bfloat16)
+    wq = (torch.randn(q_heads * 128, hidden, generator=g) * 0.05).to(torch.bfloat16)
+    wk = (torch.randn(kv_heads * 128, hidden, generator=g) * 0.05).to(torch.bfloat16)
+    wv = (torch.randn(kv_heads * 128, hidden, generator=g) * 0.05).to(torch.bfloat16)
+    ck = torch.randn(max_batch, kv_heads, max_seq, 128, generator=g).to(torch.bfloat16)   # canaries
+    cv = torch.randn(max_batch, kv_heads, max_seq, 128, generator=g).to(torch.bfloat16)
+    qw = (1 + 0.02 * torch.randn(128, generator=g)).float() if weights else None
+    kw = (1 + 0.02 * torch.randn(128, generator=g)).float() if weights else None
+    rope = ellm_b200.precompute_freqs_cis(128, max_seq, 1e6)
+    strides = [kv_heads * max_seq * 128, max_seq * 128, 128, 1]
+    # oracle: the three projections, stored as bf16, then the norm + rope + cache-write step
+    pq = oracle.matmul_nt_bf16(bits(x), bits(wq)).reshape(interval, max_batch, q_heads, 128)
+    pk = oracle.matmul_nt_bf16(bits(x), bits(wk)).reshape(interval, max_batch, kv_heads, 128)
+    pv = oracle.matmul_nt_bf16(bits(x), bits(wv)).reshape(interval, max_batch, kv_heads, 128)
+    want_ck, want_cv = bits(ck).copy(), bits(cv).copy()
+    want_q = oracle.qk_norm_rope_append_bf16(pq, pk, pv, want_ck, want_cv, rope, strides, q_heads, kv_heads,
+                                             position_index, interval, batch, 1e-6,
+                                             q_weight=None if qw is None else qw.numpy(),
+                                             k_weight=None if kw is None else kw.numpy(), positions=positions,
+                                             max_batch=max_batch)
+    dx, dck, dcv = x.to(DEV), ck.to(DEV), cv.to(DEV)
+    q_out = torch.zeros(interval, max_batch, q_heads, 128, dtype=torch.bfloat16, device=DEV)
+    op = MatMul3.new(dx, wq.to(DEV), q_out, wk.to(DEV), dck, wv.to(DEV), dcv, torch.from_numpy(rope).to(DEV), 128, m,
+                     hidden, q_heads * 128, kv_heads * 128, kv_strides=strides, max_batch=max_batch, max_seq=max_seq,
+                     rope_rows=max_seq, eps=1e-6, q_norm_weight=None if qw is None else qw.to(DEV),
+                     k_norm_weight=None if kw is None else kw.to(DEV))
+    if positions is None:
+        op.run(position_index, interval, batch)
+    else:
+        op.run_ragged(torch.tensor(positions, dtype=torch.int32, device=DEV), interval, batch)
+    # V: the projection itself, rounded once; rows of other positions / sequences bit-equal to the canaries
+    _close(bits(dcv), want_cv, 0.99, atol=2e-5 * np.sqrt(hidden))
+    touched_v = bits(dcv) != bits(cv)
+    assert not touched_v[batch:].any()
+    _close_rotated(bits(q_out)[:, :batch], want_q[:, :batch])
+    _close_rotated(bits(dck), want_ck)
+    assert (bits(q_out)[:, batch:] == 0).all()   # dead sequence slots untouched
+    untouched = want_ck == bits(ck)              # cache rows the oracle left alone
+    assert np.array_equal(bits(dck)[untouched], bits(ck)[untouched])
+    op.close()
+
+
+def test_matmul3_prefill_chunk():
+    _matmul3(11, interval=200, max_batch=2, batch=2, q_heads=4, kv_heads=2, hidden=256, max_seq=256, position_index=37)
+
+
+def test_matmul3_odd_head_counts_no_weights_dead_slot():
+    _matmul3(12, interval=70, max_batch=3, batch=2, q_heads=3, kv_heads=1, hidden=128, max_seq=96, position_index=5,
+             weights=False)
+
+
+def test_matmul3_decode_ragged_positions():
+    _matmul3(13, interval=1, max_batch=3, batch=3, q_heads=8, kv_heads=2, hidden=512, max_seq=300,
+             positions=[0, 299, 128])
+
+
+def test_matmul3_model_shape():
+    # the benchmark stack's layer shape on a short chunk: 40 heads of columns, 32 k-blocks
+    _matmul3(14, interval=384, max_batch=1, batch=1, q_heads=32, kv_heads=4, hidden=2048, max_seq=512,
+             position_index=100)
+
+
+def test_invalid_arguments():
+    x = torch.zeros(128, 100, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(256, 100, dtype=torch.bfloat16, device=DEV)
+    o = torch.zeros(128, 256, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ellm_b200.EllmError):   # k not a multiple of 64
+        MatMulAdd.new(x, w, None, o, 128, 256, 100)
+    x = torch.zeros(128, 128, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(256, 128, dtype=torch.bfloat16, device=DEV)
+    op = MatMulAdd.new(x, w, None, o, 128, 256, 128, max_batch=4)
+    with pytest.raises(ellm_b200.EllmError):   # more live sequences than slots
+        op.run(0, 1, 5)
+    with pytest.raises(ellm_b200.EllmError):   # more rows than the buffers hold
+        op.run(0, 33, 4)
+    op.run(0, 32, 4, cpu_num=8, thread_id=3)   # a worker that is not thread 0 launches nothing
+    assert op.kernel_stats()[0] == 0
+    op.close()

@@ -1,9 +1,10 @@
 """The attention-only decoder stack (projections + norm/rope/append + attention + output
 projection with residual) on a small configuration against a CPU restatement (B200 only).
 
-The projections run on cuBLAS, whose summation order differs from the CPU's, so a projected
-value may land one bf16 step away and the deviation grows a little through the layers; the
-tolerances here are for the whole stack, the per-kernel parity bars are in the kernels' own tests."""
+The prefill chunk runs the projections on the tcgen05 kernel (fused epilogues), the decode steps on
+cuBLAS; both sum in another order than the CPU, so a projected value may land one bf16 step away
+and the deviation grows a little through the layers; the tolerances here are for the whole stack,
+the per-kernel parity bars are in the kernels' own tests."""
 import numpy as np
 import pytest
 import torch
@@ -79,3 +80,25 @@ def test_small_stack_prefill_then_decode_with_and_without_graph():
     stream.synchronize()
     assert int(stack.positions[0]) == S + steps and torch.isfinite(out.float()).all()
     stack.close()
+
+
+def test_tensor_core_and_library_projections_agree():
+    dev = torch.device("cuda:0")
+    layers, hidden, Hq, Hkv, S = 2, 512, 8, 2, 300
+    outs, caches = [], []
+    for mode in ("tcgen05", "library"):
+        stream = torch.cuda.Stream(dev)
+        stack = AttentionStack(layers, hidden, Hq, Hkv, max_seq=S + 4, max_interval=S, stream=stream, seed=21,
+                               max_batch=2, projections=mode)
+        g = torch.Generator().manual_seed(22)
+        x0 = torch.randn(S, 2, hidden, generator=g).to(torch.bfloat16).to(dev)
+        outs.append(stack.forward(x0, 0).float().cpu().numpy())
+        stream.synchronize()
+        caches.append([t.float().cpu().numpy() for t in stack.cache.layer(layers - 1)])
+        if mode == "tcgen05":
+            assert stack.qkv_ops[0].kernel_stats()[0] == 1 and stack.out_ops[0].kernel_stats()[0] == 1
+        stack.close()
+    d = np.abs(outs[0] - outs[1])
+    assert np.isfinite(outs[0]).all() and d.mean() <= 5e-3 and d.max() <= 0.25, (d.mean(), d.max())
+    for a, b in zip(caches[0], caches[1]):
+        assert np.abs(a - b).mean() <= 2e-3
