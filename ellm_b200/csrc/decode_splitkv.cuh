@@ -125,8 +125,11 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t warp_smem = smem_u32(smem) + warp * kDecStages * kDecWarpStageBytes;
 
-    // let a dependent grid (the merge) be set up while this one runs
+    // let a dependent grid (the merge) be set up while this one runs; under a programmatic
+    // dependent launch of this grid itself, wait here for the kernel before it (it wrote the
+    // positions, the queries and the newest cache row); a no-op for an ordinary launch
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     dec_build_prefix(p, prefix, lens);
     if (blockIdx.x == 0)
         for (int i = threadIdx.x; i <= p.batch; i += kDecThreads) p.prefix_out[i] = prefix[i];

@@ -3,6 +3,7 @@
 #pragma once
 #include "../../include/ellm_proj.h"
 #include "proj_tcgen05.cuh"
+#include "proj_skinny.cuh"
 
 struct ProjHandle {
     int which = 0;                 // 0 = MatMul3, 1 = MatMulAdd
@@ -15,6 +16,15 @@ struct ProjHandle {
     CUtensorMap map_w[3];
     CUtensorMap map_a;
     size_t map_a_rows = 0;         // rows map_a was encoded for (0 = none yet)
+    // decode steps (at most 16 rows): the weight-streaming kernel
+    struct Skinny {
+        const void* w = nullptr;
+        size_t n = 0;
+        int cols = 0, ctas = 0;
+    } sk[3];
+    int sk_count = 0;              // 0 = unavailable for this shape, 1 = one matrix, 3 = Wq, Wk, Wv apart
+    __nv_bfloat16* qkv_scratch = nullptr;   // MatMul3: the projected rows of a decode step, [16 x (Nq + 2 Nkv)]
+    uint64_t skinny_launches = 0;
     int* status_dev = nullptr;
     int* status_host = nullptr;    // pinned mirror
     std::mutex mu;
@@ -27,6 +37,8 @@ struct ellm_matmul3 : ProjHandle {};
 struct ellm_matmul_add : ProjHandle {};
 
 namespace {
+
+int proj_check_status(ProjHandle* h);
 
 int proj_common_create(ProjHandle* h, int device, void* stream, int async) {
     h->device = device;
@@ -43,6 +55,9 @@ int proj_common_create(ProjHandle* h, int device, void* stream, int async) {
     }
     *h->status_host = 0;
     ELLM_CUDA(cudaMemset(h->status_dev, 0, sizeof(int)));
+    static_assert(ellm::kSkSmemMax + 1024 <= 232448, "shared memory budget");
+    if (cudaFuncSetAttribute(ellm::proj_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kSkSmemMax + 1024) != cudaSuccess)
+        return fail(ELLM_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(cudaGetLastError()));
     return ELLM_OK;
 }
 
@@ -53,7 +68,73 @@ void proj_common_destroy(ProjHandle* h) {
         cudaEventDestroy(pr.second);
     }
     cudaFree(h->status_dev);
+    cudaFree(h->qkv_scratch);
     if (h->status_host) cudaFreeHost(h->status_host);
+}
+
+// Plans the weight-streaming kernel for one [n x k] weight: column slices of a multiple of 16 sized
+// so that the whole grid is resident at once.  Returns false (and leaves sk.ctas 0) when the shape
+// does not fit its shared-memory budget; such handles use the tensor-memory kernel for every run.
+bool skinny_plan(ProjHandle* h, ProjHandle::Skinny& sk, const void* w, size_t n, size_t k) {
+    sk.ctas = 0;
+    const long long blocks16 = static_cast<long long>((n + 15) / 16);
+    long long per_cta = (blocks16 + h->plan.sm_count - 1) / h->plan.sm_count;
+    if (per_cta * 16 > ellm::kSkMaxCols) per_cta = ellm::kSkMaxCols / 16;
+    const int cols = static_cast<int>(per_cta * 16);
+    if (ellm::skinny_pick_pass_chunks(static_cast<int>(k / 8), cols, 1) < 0) return false;   // not even one row fits
+    sk.w = w;
+    sk.n = n;
+    sk.cols = cols;
+    sk.ctas = static_cast<int>((n + cols - 1) / cols);
+    return true;
+}
+
+// One launch of the weight-streaming kernel, allowed to start while the stream's previous kernel
+// is still running: its weight loads do not depend on that kernel, its activations are read after
+// a device-side wait for it.
+int skinny_launch(ProjHandle* h, const ProjHandle::Skinny& sk, const void* a, size_t lda, size_t k, size_t rows,
+                  size_t batch, size_t max_batch, void* c, size_t ldc, const void* residual, size_t ldr) {
+    ellm::SkinnyParams p{};
+    p.a = static_cast<const __nv_bfloat16*>(a);
+    p.lda = static_cast<long long>(lda);
+    p.m_rows = static_cast<int>(rows);
+    p.batch = static_cast<int>(batch);
+    p.max_batch = static_cast<int>(max_batch);
+    p.w = static_cast<const __nv_bfloat16*>(sk.w);
+    p.k_chunks = static_cast<int>(k / 8);
+    p.cols = sk.cols;
+    p.n_cols = static_cast<int>(sk.n);
+    // the slice takes what the activation rows of this run leave of the shared memory
+    p.pass_chunks = ellm::skinny_pick_pass_chunks(p.k_chunks, sk.cols, p.m_rows);
+    if (p.pass_chunks < 0) return fail(ELLM_ERR_UNSUPPORTED, "no shared-memory plan for %zu rows of %zu", rows, k);
+    p.c = static_cast<__nv_bfloat16*>(c);
+    p.ldc = static_cast<long long>(ldc);
+    p.residual = static_cast<const __nv_bfloat16*>(residual);
+    p.ldr = static_cast<long long>(ldr);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(sk.ctas));
+    cfg.blockDim = dim3(ellm::kSkThreads);
+    cfg.dynamicSmemBytes = static_cast<size_t>(ellm::skinny_smem_bytes(p.k_chunks, sk.cols, p.pass_chunks, p.m_rows));
+    cfg.stream = h->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, ellm::proj_skinny_kernel, p);
+    if (e != cudaSuccess) return fail(ELLM_ERR_CUDA, "projection launch failed: %s", cudaGetErrorString(e));
+    ++h->skinny_launches;
+    return ELLM_OK;
+}
+
+// Tail of a run.  A synchronous handle waits for the stream and reads the status word; an
+// enqueue-only handle adds nothing to the stream (its caller may be capturing a graph of many
+// small steps) and learns of a timed-out wait from ellm_matmul_check().
+int proj_finish(ProjHandle* h) {
+    if (h->async) return ELLM_OK;
+    ELLM_CUDA(cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
+    ELLM_CUDA(cudaStreamSynchronize(h->stream));
+    return proj_check_status(h);
 }
 
 void proj_collect(ProjHandle* h) {  // folds finished event pairs into the totals
@@ -73,7 +154,6 @@ void proj_collect(ProjHandle* h) {  // folds finished event pairs into the total
     h->pending.resize(keep);
 }
 
-// A timed-out wait of an earlier enqueue-only run shows up here, at the next call.
 int proj_check_status(ProjHandle* h) {
     if (h->status_host && *h->status_host != 0) {
         const int code = *h->status_host;
@@ -111,10 +191,7 @@ int proj_launch(ProjHandle* h, const void* a, size_t lda, size_t k, size_t rows,
         ELLM_CUDA(cudaEventRecord(e1, h->stream));
         h->pending.emplace_back(e0, e1);
     }
-    ELLM_CUDA(cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
-    if (h->async) return ELLM_OK;
-    ELLM_CUDA(cudaStreamSynchronize(h->stream));
-    return proj_check_status(h);
+    return proj_finish(h);
 }
 
 int matmul3_run_impl(ellm_matmul3* h, const int32_t* positions, size_t position_index, size_t interval, size_t batch,
@@ -132,10 +209,28 @@ int matmul3_run_impl(ellm_matmul3* h, const int32_t* positions, size_t position_
     std::lock_guard<std::mutex> lock(h->mu);
     DeviceGuard guard(h->device);
     if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", h->device);
-    if (int st = proj_check_status(h)) return st;
+    const size_t q_heads = d.b_q_row / 128, kv_heads = d.b_kv_row / 128;
+    const size_t rows = interval * d.max_batch;
+    if (rows <= static_cast<size_t>(ellm::kSkRows) && h->sk_count > 0) {
+        // decode step: stream the weights once, then norm + rope + cache write on the projected rows
+        const size_t lda = d.hidden_row_stride ? d.hidden_row_stride : d.col;
+        const size_t ldq = d.b_q_row + 2 * d.b_kv_row;
+        size_t col0 = 0;
+        for (int i = 0; i < h->sk_count; ++i) {
+            if (int st = skinny_launch(h, h->sk[i], d.hidden, lda, d.col, rows, batch, d.max_batch, h->qkv_scratch + col0, ldq,
+                                       nullptr, 0))
+                return st;
+            col0 += h->sk[i].n;
+        }
+        if (int st = ellm_qk_norm_rope_append(h->qkv_scratch, h->qkv_scratch + d.b_q_row, h->qkv_scratch + d.b_q_row + d.b_kv_row,
+                                              d.q_state, d.k_cache, d.v_cache, d.q_norm_weight, d.k_norm_weight, d.rope,
+                                              d.rope_rows, d.kv_strides, d.max_batch, q_heads, kv_heads, 128, d.max_seq,
+                                              position_index, positions, interval, batch, d.eps, ldq, ldq, h->device, h->stream))
+            return st;
+        return proj_finish(h);
+    }
     ellm::ProjParams p{};
     p.mode = ellm::kPjQkv;
-    const size_t q_heads = d.b_q_row / 128, kv_heads = d.b_kv_row / 128;
     p.tiles_q = static_cast<int>((q_heads + 1) / 2);
     p.tiles_kv = static_cast<int>((kv_heads + 1) / 2);
     p.tiles_n = p.tiles_q + 2 * p.tiles_kv;
@@ -156,7 +251,7 @@ int matmul3_run_impl(ellm_matmul3* h, const int32_t* positions, size_t position_
     p.kv_heads = static_cast<int>(kv_heads);
     p.eps = d.eps;
     const size_t lda = d.hidden_row_stride ? d.hidden_row_stride : d.col;
-    return proj_launch(h, d.hidden, lda, d.col, interval * d.max_batch, p);
+    return proj_launch(h, d.hidden, lda, d.col, rows, p);
 }
 
 bool proj_stride_ok(size_t stride, size_t width) { return stride % 8 == 0 && stride >= width; }
@@ -201,6 +296,25 @@ int ellm_matmul3_create(const ellm_matmul3_desc* d, ellm_matmul3** out) {
         for (int i = 0; i < 3 && st == ELLM_OK; ++i)
             if (!ellm::proj_encode_2d(h->plan, &h->map_w[i], w[i], n[i], d->col, d->col, ellm::kPjBN))
                 st = fail(ELLM_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled(weight %d) failed", i);
+    }
+    if (st == ELLM_OK) {
+        // decode path: one matrix when Wq, Wk, Wv lie back to back, else one launch per weight
+        const char* wq = static_cast<const char*>(d->wq_nt);
+        const bool contiguous = static_cast<const char*>(d->wk_nt) == wq + d->b_q_row * d->col * 2 &&
+                                static_cast<const char*>(d->wv_nt) == wq + (d->b_q_row + d->b_kv_row) * d->col * 2;
+        bool ok;
+        if (contiguous) {
+            ok = skinny_plan(h, h->sk[0], d->wq_nt, d->b_q_row + 2 * d->b_kv_row, d->col);
+            h->sk_count = ok ? 1 : 0;
+        } else {
+            ok = skinny_plan(h, h->sk[0], d->wq_nt, d->b_q_row, d->col) && skinny_plan(h, h->sk[1], d->wk_nt, d->b_kv_row, d->col) &&
+                 skinny_plan(h, h->sk[2], d->wv_nt, d->b_kv_row, d->col);
+            h->sk_count = ok ? 3 : 0;
+        }
+        if (ok && cudaMalloc(&h->qkv_scratch, ellm::kSkRows * (d->b_q_row + 2 * d->b_kv_row) * 2) != cudaSuccess) {
+            cudaGetLastError();
+            st = fail(ELLM_ERR_NO_MEMORY, "scratch allocation failed");
+        }
     }
     if (st != ELLM_OK) {
         proj_common_destroy(h);
@@ -263,6 +377,7 @@ int ellm_matmul_add_create(const ellm_matmul_add_desc* d, ellm_matmul_add** out)
     }
     h->map_w[1] = h->map_w[0];
     h->map_w[2] = h->map_w[0];
+    h->sk_count = skinny_plan(h, h->sk[0], d->w_nt, d->n_max, d->k_max) ? 1 : 0;
     *out = h;
     return ELLM_OK;
 }
@@ -288,7 +403,14 @@ int ellm_matmul_add_run(ellm_matmul_add* h, size_t position_index, size_t positi
     std::lock_guard<std::mutex> lock(h->mu);
     DeviceGuard guard(h->device);
     if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", h->device);
-    if (int st = proj_check_status(h)) return st;
+    const size_t rows = position_interval * d.max_batch;
+    if (rows <= static_cast<size_t>(ellm::kSkRows) && h->sk_count > 0) {
+        if (int st = skinny_launch(h, h->sk[0], d.a, d.a_row_stride ? d.a_row_stride : d.k_max, d.k_max, rows, batch_size,
+                                   d.max_batch, d.output, d.output_row_stride ? d.output_row_stride : d.n_max, d.residual,
+                                   d.residual_row_stride ? d.residual_row_stride : d.n_max))
+            return st;
+        return proj_finish(h);
+    }
     ellm::ProjParams p{};
     p.mode = ellm::kPjPlain;
     p.tiles_n = static_cast<int>((d.n_max + ellm::kPjBN - 1) / ellm::kPjBN);
@@ -300,7 +422,7 @@ int ellm_matmul_add_run(ellm_matmul_add* h, size_t position_index, size_t positi
     p.ldr = static_cast<long long>(d.residual_row_stride ? d.residual_row_stride : d.n_max);
     p.n_cols = static_cast<int>(d.n_max);
     const size_t lda = d.a_row_stride ? d.a_row_stride : d.k_max;
-    return proj_launch(h, d.a, lda, d.k_max, position_interval * d.max_batch, p);
+    return proj_launch(h, d.a, lda, d.k_max, rows, p);
 }
 
 static ProjHandle* proj_cast(void* handle, int which) {
@@ -322,10 +444,21 @@ int ellm_matmul_kernel_stats(void* handle, int which, uint64_t* launches, uint64
     std::lock_guard<std::mutex> lock(h->mu);
     DeviceGuard guard(h->device);
     proj_collect(h);
-    if (launches) *launches = h->launches;
+    if (launches) *launches = h->launches + h->skinny_launches;
     if (timed_launches) *timed_launches = h->timed;
     if (ms) *ms = h->ms;
     return ELLM_OK;
+}
+
+int ellm_matmul_check(void* handle, int which) {
+    ProjHandle* h = proj_cast(handle, which);
+    if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL or not of kind %d", which);
+    std::lock_guard<std::mutex> lock(h->mu);
+    DeviceGuard guard(h->device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", h->device);
+    ELLM_CUDA(cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
+    ELLM_CUDA(cudaStreamSynchronize(h->stream));
+    return proj_check_status(h);
 }
 
 int ellm_matmul_set_wait_timeout(void* handle, int which, unsigned long long ns) {

@@ -31,6 +31,8 @@ __device__ __forceinline__ void store_row4<__nv_bfloat16>(__nv_bfloat16* dst, fl
 // memory.  out: [max_batch, q_heads, 128], lse: [max_batch, q_heads].
 template <typename OutT>
 __global__ void __launch_bounds__(128) decode_merge_kernel(const DecodeParams p, OutT* out, float* lse) {
+    // a following kernel launched as a programmatic dependent may start its own prologue now
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // under a programmatic dependent launch: wait until the decode grid's writes are visible
     // (a no-op for an ordinary launch)
     asm volatile("griddepcontrol.wait;" ::: "memory");

@@ -1,0 +1,179 @@
+// K7: the projections of a decode step - at most 16 activation rows against a whole weight
+// matrix:  C[m x N] = (residual +) A[m x K] . W_nt[N x K]^T,  m <= 16.
+//
+// Same arithmetic as proj_tcgen05.cuh (the reference's MatMul / MatMulAdd / the GEMM part of
+// MatMul3, src/compiler/mul/matmul_add.rs:128-232, src/compiler/mul/matmul3.rs:289-385), other
+// regime: with so few rows every weight is used once, so the step is bound by streaming W from HBM
+// (2 bytes per 2*m flops) and a 128-row tensor-memory tile would be empty.  Design for bandwidth:
+//   * a CTA owns a slice of `cols` output columns (a multiple of 16) and all of K for them; the
+//     grid is sized so that every CTA is resident at once (<= one per SM);
+//   * the slice is brought into shared memory by 16-byte asynchronous copies, every one of them
+//     requested up front (a warp instruction takes 512 contiguous bytes of one weight row).  TMA
+//     was measured first and streams from DRAM at no more than ~30 GB/s per SM whatever the box
+//     size (about 32 KB in flight per SM), half of what this needs; the load/store path keeps far
+//     more in flight;
+//   * the copies are requested before the kernel waits for its predecessor in the stream
+//     (programmatic dependent launch): weights do not depend on it, activations do;
+//   * then legacy warp-level MMA (m16n8k16) with the activation rows as M - the tensor core is
+//     only the cheapest way to multiply up to 16 rows by a tile - the 16-wide k steps going round
+//     the 8 warps; the eight partial sums of an output are added in warp order, the residual is
+//     added, the sum is rounded to bf16 once.
+// When the activation rows leave too little shared memory for the whole slice (many rows, long K)
+// the slice is taken in several passes over K.
+#pragma once
+#include "proj_tcgen05.cuh"
+
+namespace ellm {
+
+constexpr int kSkRows = 16;                    // activation rows = M of the MMA
+constexpr int kSkWarps = 8;
+constexpr int kSkThreads = kSkWarps * 32;
+constexpr int kSkMaxCols = 64;                 // columns per CTA (accumulators: cols/8 x 4 registers)
+constexpr int kSkSmemMax = 232448 - 1024;
+
+struct SkinnyParams {
+    const __nv_bfloat16* a;
+    long long lda;
+    const __nv_bfloat16* w;   // [n_cols x K]
+    int m_rows;               // rows of A that exist (<= 16): chunk rows x max_batch
+    int batch, max_batch;     // rows with (row % max_batch) >= batch are skipped
+    int k_chunks;             // K / 8: 16-byte pieces per row
+    int pass_chunks;          // pieces of a weight row held in shared memory at a time (multiple of 8)
+    int cols;                 // columns per CTA, multiple of 16
+    int n_cols;               // N
+    __nv_bfloat16* c;
+    long long ldc;
+    const __nv_bfloat16* residual;
+    long long ldr;
+};
+
+// shared memory: [x tile: m_rows x K bf16][128 zero bytes][slice: cols x pass_chunks x 16 bytes];
+// in both tiles the 16-byte piece p of row r sits at p ^ (r & 7), so that the 8 rows one ldmatrix
+// phase reads fall in 8 different bank groups.
+__host__ __device__ inline int skinny_x_bytes(int k_chunks, int m_rows) { return m_rows * k_chunks * 16 + 128; }
+// Largest number of pieces per pass (a multiple of 32, i.e. 512-byte runs, or all of K) that fits.
+inline int skinny_pick_pass_chunks(int k_chunks, int cols, int m_rows) {
+    const int room = kSkSmemMax - skinny_x_bytes(k_chunks, m_rows);
+    int pc = room / (cols * 16);
+    if (pc >= k_chunks) return k_chunks;
+    pc &= ~31;
+    return pc < 32 ? -1 : pc;   // 32 pieces per row also make room for the partial sums (512 bytes per column)
+}
+inline int skinny_smem_bytes(int k_chunks, int cols, int pass_chunks, int m_rows) {
+    int slice = cols * pass_chunks * 16;
+    if (slice < kSkWarps * kSkRows * cols * 4) slice = kSkWarps * kSkRows * cols * 4;
+    return skinny_x_bytes(k_chunks, m_rows) + slice + 128;
+}
+
+__global__ void __launch_bounds__(kSkThreads, 1) proj_skinny_kernel(const SkinnyParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int x_bytes = skinny_x_bytes(p.k_chunks, p.m_rows);
+    const uint32_t x_base = smem_u32(smem), zero_addr = x_base + p.m_rows * p.k_chunks * 16, w_base = x_base + x_bytes;
+    const int n0 = blockIdx.x * p.cols;
+    const int passes = (p.k_chunks + p.pass_chunks - 1) / p.pass_chunks;
+
+    // pieces [pass * pass_chunks, ...) of every row of the slice; rows past N arrive as zeros
+    auto request_pass = [&](int pass) {
+        const int c_begin = pass * p.pass_chunks;
+        const int pc = min(p.pass_chunks, p.k_chunks - c_begin);
+        const int total = p.cols * pc;
+        for (int i = threadIdx.x; i < total; i += kSkThreads) {
+            const int n = i / pc, cc = i % pc;
+            const bool real = n0 + n < p.n_cols;
+            const __nv_bfloat16* src = p.w + (real ? static_cast<long long>(n0 + n) * p.k_chunks * 8 + (c_begin + cc) * 8 : 0);
+            cp_async_16(w_base + (n * p.pass_chunks + (cc ^ (n & 7))) * 16, src, real ? 16 : 0);
+        }
+        cp_async_commit();
+    };
+    request_pass(0);
+    // the next kernel of the stream may start its own prologue now
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // activations (and the residual) are the previous kernels' output: wait for them
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int m = 0; m < p.m_rows; ++m) {
+        const bool live = (m % p.max_batch) < p.batch;
+        const __nv_bfloat16* src = p.a + (live ? m * p.lda : 0);
+        for (int c = threadIdx.x; c < p.k_chunks; c += kSkThreads)
+            cp_async_16(x_base + (m * p.k_chunks + (c ^ (m & 7))) * 16, src + c * 8, live ? 16 : 0);
+    }
+    if (threadIdx.x < 8) cp_async_16(zero_addr + threadIdx.x * 16, p.a, 0);   // the row every missing row reads
+    cp_async_commit();
+    // the residual values of this thread's outputs, requested now, used at the very end
+    const int outs = p.m_rows * p.cols;
+    float res[4] = {0.f, 0.f, 0.f, 0.f};
+    if (p.residual) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = threadIdx.x + i * kSkThreads;
+            const int m = idx / p.cols, n = n0 + idx % p.cols;
+            if (idx < outs && (m % p.max_batch) < p.batch && n < p.n_cols) res[i] = __bfloat162float(p.residual[m * p.ldr + n]);
+        }
+    }
+
+    float acc[kSkMaxCols / 8][4];
+#pragma unroll
+    for (int i = 0; i < kSkMaxCols / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+    const int nblocks16 = p.cols >> 4;
+    const int a_row = lane & 15;
+    const bool a_live = a_row < p.m_rows;
+    for (int pass = 0; pass < passes; ++pass) {
+        if (pass > 0) {
+            __syncthreads();   // every warp is done with the previous part of the slice
+            request_pass(pass);
+        }
+        cp_async_wait<0>();
+        __syncthreads();
+        const int c_begin = pass * p.pass_chunks;
+        const int steps = min(p.pass_chunks, p.k_chunks - c_begin) >> 1;   // 16-wide k steps of this pass
+        for (int step = warp; step < steps; step += kSkWarps) {
+            uint32_t af[4];
+            {
+                const int piece = c_begin + step * 2 + (lane >> 4);
+                const uint32_t addr = a_live ? x_base + (a_row * p.k_chunks + (piece ^ (a_row & 7))) * 16 : zero_addr;
+                ldmatrix_x4(addr, af[0], af[1], af[2], af[3]);
+            }
+#pragma unroll
+            for (int nb = 0; nb < kSkMaxCols / 16; ++nb) {
+                if (nb < nblocks16) {
+                    // matrices: (cols 0-7, k 0-7), (cols 0-7, k 8-15), (cols 8-15, k 0-7), (cols 8-15, k 8-15)
+                    const int n = nb * 16 + ((lane >> 4) << 3) + (lane & 7), piece = step * 2 + ((lane >> 3) & 1);
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4(w_base + (n * p.pass_chunks + (piece ^ (n & 7))) * 16, b0, b1, b2, b3);
+                    mma_bf16_16816(acc[nb * 2], af, b0, b1);
+                    mma_bf16_16816(acc[nb * 2 + 1], af, b2, b3);
+                }
+            }
+        }
+    }
+    // every warp is done with the slice: the partial sums go over it
+    __syncthreads();
+    float* part = reinterpret_cast<float*>(smem + x_bytes);   // [warp][row][col]
+    {
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int i = 0; i < kSkMaxCols / 8; ++i) {
+            if (i * 8 < p.cols) {
+                float* dst = part + (warp * kSkRows) * p.cols + i * 8 + c0;
+                dst[r0 * p.cols] = acc[i][0];
+                dst[r0 * p.cols + 1] = acc[i][1];
+                dst[(r0 + 8) * p.cols] = acc[i][2];
+                dst[(r0 + 8) * p.cols + 1] = acc[i][3];
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int idx = threadIdx.x + i * kSkThreads;
+        if (idx >= outs) break;
+        const int m = idx / p.cols, j = idx % p.cols, n = n0 + j;
+        if ((m % p.max_batch) >= p.batch || n >= p.n_cols) continue;
+        float sum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kSkWarps; ++w) sum += part[(w * kSkRows + m) * p.cols + j];
+        p.c[m * p.ldc + n] = __float2bfloat16_rn(sum + res[i]);
+    }
+}
+
+}  // namespace ellm

@@ -13,6 +13,10 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __re
     __shared__ float warp_sums[8];
     __shared__ float s_rrms;
     const long long row = blockIdx.x;
+    // a following kernel launched as a programmatic dependent may start its own prologue now;
+    // this one, when launched that way itself, waits for the kernel that wrote x
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (row >= rows) return;
     const uint4* src = reinterpret_cast<const uint4*>(x + row * length);
     uint4* dst = reinterpret_cast<uint4*>(y + row * length);

@@ -30,6 +30,10 @@ class _Projection:
         L.check(self._lib.ellm_matmul_kernel_stats(self._h, self._which, C.byref(n), C.byref(t), C.byref(ms)))
         return n.value, t.value, ms.value
 
+    def check(self):
+        """Waits for the stream; raises if a device-side wait ran out since the last check."""
+        L.check(self._lib.ellm_matmul_check(self._h, self._which))
+
     def set_wait_timeout(self, ns):
         L.check(self._lib.ellm_matmul_set_wait_timeout(self._h, self._which, int(ns)))
 

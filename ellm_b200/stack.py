@@ -9,14 +9,14 @@ Per layer, following the reference's decoder layer and attention block minus the
     a   = Attention(q, cache)                      ellm_attn_run
     x   = x + a Wo^T                               matmul_add (src/compiler/mul/matmul_add.rs:186-226)
 
-Chunks of at least `tensor_core_rows` rows run the projections on this repository's tcgen05
-kernel: MatMul3 with the norm + rope + cache write in its epilogue, and MatMulAdd with the
-residual in its epilogue (ellm_b200/projection.py).  Shorter chunks (decode steps) use library
-GEMMs (torch / cuBLAS) followed by the separate norm + rope + append kernel: a 128-row tile would
-be nearly empty there and the step is bound by streaming the weights, not by the tensor cores.
-The input norm and attention are this repository's kernels on both paths.  Decode steps can be
-captured once in a CUDA graph and replayed: every kernel takes the per-sequence positions from a
-device array that the graph itself advances.
+With projections="tcgen05" (the default) every step runs on this repository's kernels
+(ellm_b200/projection.py): MatMul3 and MatMulAdd pick the tcgen05 kernel with the norm + rope +
+cache write (or the residual) in its epilogue for chunks, and the weight-streaming kernel for
+decode steps of at most 16 rows.  projections="library" keeps torch / cuBLAS GEMMs followed by the
+separate norm + rope + append kernel, as a comparison.  The input norm and attention are this
+repository's kernels on both paths.  Decode steps can be captured once in a CUDA graph and
+replayed: every kernel takes the per-sequence positions from a device array that the graph
+itself advances.
 """
 import numpy as np
 import torch
@@ -30,8 +30,7 @@ from .rope import precompute_freqs_cis
 
 class AttentionStack:
     def __init__(self, layers, hidden, q_heads, kv_heads, max_seq, max_interval, *, head_dim=128, theta=1e6,
-                 eps=1e-6, seed=3, device="cuda:0", stream=None, max_batch=1, projections="tcgen05",
-                 tensor_core_rows=128):
+                 eps=1e-6, seed=3, device="cuda:0", stream=None, max_batch=1, projections="tcgen05"):
         dev = torch.device(device)
         self.dev, self.layers, self.hidden = dev, layers, hidden
         self.q_heads, self.kv_heads, self.head_dim = q_heads, kv_heads, head_dim
@@ -43,13 +42,16 @@ class AttentionStack:
             return (torch.randn(*shape, device=dev, generator=g) * std + mean).to(dtype)
 
         qd, kd = q_heads * head_dim, kv_heads * head_dim
-        # N x K row-major, like the reference's W_nt (matmul3.rs:22-28)
-        self.wq = [w(qd, hidden) for _ in range(layers)]
-        self.wk = [w(kd, hidden) for _ in range(layers)]
-        self.wv = [w(kd, hidden) for _ in range(layers)]
-        self.wo = [w(hidden, qd) for _ in range(layers)]
-        # the three projections as one GEMM: rows of [Wq; Wk; Wv]
-        self.wqkv = [torch.cat([self.wq[i], self.wk[i], self.wv[i]]).contiguous() for i in range(layers)]
+        # N x K row-major, like the reference's W_nt (matmul3.rs:22-28); Wq, Wk, Wv are views of one
+        # [Wq; Wk; Wv] matrix so that a decode step can stream them as one
+        self.wqkv, self.wo = [], []
+        for _ in range(layers):
+            wq, wk, wv, wo = w(qd, hidden), w(kd, hidden), w(kd, hidden), w(hidden, qd)
+            self.wqkv.append(torch.cat([wq, wk, wv]).contiguous())
+            self.wo.append(wo)
+        self.wq = [m[:qd] for m in self.wqkv]
+        self.wk = [m[qd:qd + kd] for m in self.wqkv]
+        self.wv = [m[qd + kd:] for m in self.wqkv]
         self.qkv = torch.zeros(max_interval * max_batch, qd + 2 * kd, dtype=torch.bfloat16, device=dev)
         self.h = torch.zeros(max_interval * max_batch, hidden, dtype=torch.bfloat16, device=dev)
         self.q_norm = [w(head_dim, mean=1.0, dtype=torch.float32) for _ in range(layers)]
@@ -64,7 +66,7 @@ class AttentionStack:
         self.ops, self.qkv_ops, self.out_ops = [], [], []
         if projections not in ("tcgen05", "library"):
             raise ValueError("projections must be 'tcgen05' or 'library'")
-        self.tensor_core_rows = tensor_core_rows if projections == "tcgen05" else None
+        self.own_projections = projections == "tcgen05"
         self.x = torch.zeros(rows, hidden, dtype=torch.bfloat16, device=dev)   # the residual stream, updated in place
         dev_index, raw_stream = dev.index or 0, self.stream.cuda_stream
         for i in range(layers):
@@ -72,7 +74,7 @@ class AttentionStack:
             self.ops.append(Attention.new(self.q, ck, cv, self.a, max_batch, q_heads, kv_heads, head_dim,
                                           self.cache.strides, self.scale, max_seq=max_seq, max_interval=max_interval,
                                           device=dev_index, stream=raw_stream, async_=True))
-            if self.tensor_core_rows is not None:
+            if self.own_projections:
                 self.qkv_ops.append(MatMul3.new(self.h, self.wq[i], self.q, self.wk[i], ck, self.wv[i], cv, self.rope,
                                                 head_dim, rows, hidden, qd, kd, kv_strides=self.cache.strides,
                                                 max_batch=max_batch, max_seq=max_seq, rope_rows=max_seq, eps=eps,
@@ -83,7 +85,7 @@ class AttentionStack:
         self._rows = rows
 
     def _layer_tensor_core(self, i, n, batch, position_index, ragged):
-        """One layer on self.x[:n * max_batch] in place, projections on the tcgen05 kernel."""
+        """One layer on self.x[:n * max_batch] in place, projections on this repository's kernels."""
         rows = n * self.max_batch
         rms_norm(self.x[:rows], self.h[:rows], self.eps, device=self.dev.index or 0, stream=self.stream.cuda_stream)
         if ragged:
@@ -123,7 +125,7 @@ class AttentionStack:
         rows = n * self.max_batch
         y = x.reshape(rows, self.hidden)
         with torch.cuda.stream(self.stream):
-            if self.tensor_core_rows is not None and rows >= self.tensor_core_rows:
+            if self.own_projections:
                 self.x[:rows].copy_(y)
                 for i in range(self.layers):
                     self._layer_tensor_core(i, n, batch, position_index, ragged)

@@ -108,6 +108,10 @@ int ellm_matmul_add_run(ellm_matmul_add* h, size_t position_index, size_t positi
  * every launch; for measurement only).  `which`: 0 = ellm_matmul3, 1 = ellm_matmul_add. */
 int ellm_matmul_set_profiling(void* handle, int which, int on);
 int ellm_matmul_kernel_stats(void* handle, int which, uint64_t* launches, uint64_t* timed_launches, double* ms);
+/* Waits for the handle's stream and reports a device-side wait that ran out since the last check
+ * (ELLM_ERR_DEVICE_TIMEOUT).  Synchronous handles check after every run; enqueue-only handles
+ * (async = 1) add nothing to the stream and are checked here. */
+int ellm_matmul_check(void* handle, int which);
 /* Bound of every device-side wait of the handle's kernel, nanoseconds (default 2e9). */
 int ellm_matmul_set_wait_timeout(void* handle, int which, unsigned long long ns);
 

@@ -76,11 +76,20 @@ def test_matmul_add_strided_a_many_k_blocks():
 
 
 def test_matmul_decode_rows():
+    # 64 k-blocks through a 48-slot ring, 128 CTAs of 16 columns
     _matmul_add(4, interval=1, max_batch=16, batch=16, n=2048, k=4096, residual=True)
 
 
+def test_matmul_decode_one_row_odd_columns_in_place():
+    _matmul_add(5, interval=1, max_batch=1, batch=1, n=200, k=128, residual=True, in_place=True)
+
+
+def test_matmul_decode_dead_slots_no_residual():
+    _matmul_add(6, interval=1, max_batch=5, batch=3, n=1024, k=512, residual=False)
+
+
 def _matmul3(seed, interval, max_batch, batch, q_heads, kv_heads, hidden, max_seq, position_index=0, positions=None,
-             weights=True):
+             weights=True, one_matrix=False):
     g = torch.Generator().manual_seed(seed)
     m = interval * max_batch
     x = torch.randn(m, hidden, generator=g).to(torch.bfloat16)
@@ -105,7 +114,12 @@ def _matmul3(seed, interval, max_batch, batch, q_heads, kv_heads, hidden, max_se
                                              max_batch=max_batch)
     dx, dck, dcv = x.to(DEV), ck.to(DEV), cv.to(DEV)
     q_out = torch.zeros(interval, max_batch, q_heads, 128, dtype=torch.bfloat16, device=DEV)
-    op = MatMul3.new(dx, wq.to(DEV), q_out, wk.to(DEV), dck, wv.to(DEV), dcv, torch.from_numpy(rope).to(DEV), 128, m,
+    if one_matrix:   # Wq, Wk, Wv back to back in memory: a decode step streams them as one matrix
+        wqkv = torch.cat([wq, wk, wv]).to(DEV)
+        dwq, dwk, dwv = wqkv[:q_heads * 128], wqkv[q_heads * 128:(q_heads + kv_heads) * 128], wqkv[(q_heads + kv_heads) * 128:]
+    else:
+        dwq, dwk, dwv = wq.to(DEV), wk.to(DEV), wv.to(DEV)
+    op = MatMul3.new(dx, dwq, q_out, dwk, dck, dwv, dcv, torch.from_numpy(rope).to(DEV), 128, m,
                      hidden, q_heads * 128, kv_heads * 128, kv_strides=strides, max_batch=max_batch, max_seq=max_seq,
                      rope_rows=max_seq, eps=1e-6, q_norm_weight=None if qw is None else qw.to(DEV),
                      k_norm_weight=None if kw is None else kw.to(DEV))
@@ -137,6 +151,17 @@ def test_matmul3_odd_head_counts_no_weights_dead_slot():
 def test_matmul3_decode_ragged_positions():
     _matmul3(13, interval=1, max_batch=3, batch=3, q_heads=8, kv_heads=2, hidden=512, max_seq=300,
              positions=[0, 299, 128])
+
+
+def test_matmul3_decode_model_shape_one_matrix():
+    # 16 sequences, one dead; 5120 columns in slices of 48 over 107 CTAs; the ring wraps (32 k-blocks, 26 slots)
+    _matmul3(15, interval=1, max_batch=16, batch=15, q_heads=32, kv_heads=4, hidden=2048, max_seq=64,
+             positions=list(range(3, 48, 3)), one_matrix=True)
+
+
+def test_matmul3_two_row_chunk_of_one_sequence():
+    _matmul3(16, interval=2, max_batch=1, batch=1, q_heads=4, kv_heads=2, hidden=256, max_seq=40, position_index=17,
+             one_matrix=True)
 
 
 def test_matmul3_model_shape():
