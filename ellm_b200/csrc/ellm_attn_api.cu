@@ -239,7 +239,7 @@ int launch_decode(ellm_attn* h, const int32_t* positions, size_t position_index,
         LaunchScope ls(h, ELLM_KERNEL_MERGE);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(blocks);
-        cfg.blockDim = dim3(128);
+        cfg.blockDim = dim3(ellm::kMergeThreads);
         cfg.dynamicSmemBytes = 0;
         cfg.stream = h->stream;
         cudaLaunchAttribute attr[1];
@@ -925,7 +925,7 @@ extern "C" int ellm_attn_decode_noalloc(const void* q, const void* k_cache, cons
     ellm::decode_splitkv_kernel<<<num_ctas, ellm::kDecThreads, ellm::kDecSmemBytes, s>>>(p);
     ELLM_CUDA(cudaGetLastError());
     const unsigned blocks = static_cast<unsigned>(batch_size * q_heads);
-    ellm::decode_merge_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(p, static_cast<__nv_bfloat16*>(out), lse);
+    ellm::decode_merge_kernel<__nv_bfloat16><<<blocks, ellm::kMergeThreads, 0, s>>>(p, static_cast<__nv_bfloat16*>(out), lse);
     ELLM_CUDA(cudaGetLastError());
     return ELLM_OK;
 }

@@ -25,19 +25,27 @@ __device__ __forceinline__ void store_row4<__nv_bfloat16>(__nv_bfloat16* dst, fl
     *reinterpret_cast<uint2*>(dst) = u;
 }
 
-// Combines the pieces the decode kernel left in its workspace.  Grid: one CTA of 4 warps per
-// (sequence, query head); the warps share the row's pieces (a segment spread over many CTAs
-// has many), each keeps a running (max, sum, O) and the four are combined through shared
-// memory.  out: [max_batch, q_heads, 128], lse: [max_batch, q_heads].
+// Combines the pieces the decode kernel left in its workspace.  Grid: one CTA of 8 warps per
+// (sequence, query head).  A segment spread over many CTAs has many pieces (a single long sequence:
+// one per CTA of the decode grid), so the combine is laid out for latency: first every thread
+// fetches the log-sum-exp of one piece and the CTA agrees on their maximum, which fixes every
+// piece's weight; then the warps take the pieces round-robin, four loads in flight each, with no
+// dependence between pieces; last the eight partial rows are added through shared memory.
+// out: [max_batch, q_heads, 128], lse: [max_batch, q_heads].
+constexpr int kMergeThreads = 256;
+constexpr int kMergeMaxPieces = 1024;   // weights kept in shared memory; more pieces are handled in rounds
+
 template <typename OutT>
-__global__ void __launch_bounds__(128) decode_merge_kernel(const DecodeParams p, OutT* out, float* lse) {
+__global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const DecodeParams p, OutT* out, float* lse) {
     // a following kernel launched as a programmatic dependent may start its own prologue now
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // under a programmatic dependent launch: wait until the decode grid's writes are visible
     // (a no-op for an ordinary launch)
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    __shared__ float s_m[4], s_w[4];
-    __shared__ float4 s_acc[4][32];
+    __shared__ float s_l[kMergeMaxPieces];
+    __shared__ float s_red[kMergeThreads / 32];
+    __shared__ float4 s_acc[kMergeThreads / 32][32];
+    constexpr int kWarps = kMergeThreads / 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long row = blockIdx.x;
     const int b = static_cast<int>(row / p.q_heads), qh = static_cast<int>(row % p.q_heads);
@@ -59,33 +67,64 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(const DecodeParams p,
                          static_cast<long long>(seg_in_seq) * tiles_b;
     const long long c_first = cta_of_tile(total, p.num_ctas, t0);
     const long long c_last = cta_of_tile(total, p.num_ctas, t0 + tiles_b - 1);
-    float m = -INFINITY, wsum = 0.0f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (long long c = c_first + warp; c <= c_last; c += 4) {
-        const long long slot = c + segment;
-        const float l = p.part_lse[slot * 16 + r];
-        const float4 x = *reinterpret_cast<const float4*>(p.part_o + (slot * 16 + r) * kHeadDim + lane * 4);
-        const float mn = fmaxf(m, l);
-        const float a = __expf(m - mn), w = __expf(l - mn);   // m = -inf on the first piece: a = 0
-        wsum = wsum * a + w;
-        acc.x = acc.x * a + w * x.x; acc.y = acc.y * a + w * x.y;
-        acc.z = acc.z * a + w * x.z; acc.w = acc.w * a + w * x.w;
-        m = mn;
+    const int pieces = static_cast<int>(c_last - c_first + 1);
+    const float* lse_base = p.part_lse + (c_first + segment) * 16 + r;            // piece i at + i * 16
+    const float* o_base = p.part_o + ((c_first + segment) * 16 + r) * kHeadDim + lane * 4;   // piece i at + i * 16 * 128
+
+    // 1. the maximum of the pieces' log-sum-exps (every piece has seen at least one key: finite)
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < pieces; i += kMergeThreads) {
+        const float l = lse_base[static_cast<long long>(i) * 16];
+        if (i < kMergeMaxPieces) s_l[i] = l;
+        mx = fmaxf(mx, l);
     }
-    if (lane == 0) { s_m[warp] = m; s_w[warp] = wsum; }
-    s_acc[warp][lane] = acc;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) s_red[warp] = mx;
     __syncthreads();
+    float mm = s_red[0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) mm = fmaxf(mm, s_red[w]);
+
+    // 2. weighted sums, pieces round-robin over the warps, four in flight
+    float wsum = 0.0f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    auto piece_lse = [&](int i) { return i < kMergeMaxPieces ? s_l[i] : lse_base[static_cast<long long>(i) * 16]; };
+    int i = warp;
+    for (; i + 3 * kWarps < pieces; i += 4 * kWarps) {
+        float4 x[4];
+        float w[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            x[u] = *reinterpret_cast<const float4*>(o_base + static_cast<long long>(i + u * kWarps) * 16 * kHeadDim);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) w[u] = __expf(piece_lse(i + u * kWarps) - mm);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            wsum += w[u];
+            acc.x += w[u] * x[u].x; acc.y += w[u] * x[u].y; acc.z += w[u] * x[u].z; acc.w += w[u] * x[u].w;
+        }
+    }
+    for (; i < pieces; i += kWarps) {
+        const float4 x = *reinterpret_cast<const float4*>(o_base + static_cast<long long>(i) * 16 * kHeadDim);
+        const float w = __expf(piece_lse(i) - mm);
+        wsum += w;
+        acc.x += w * x.x; acc.y += w * x.y; acc.z += w * x.z; acc.w += w * x.w;
+    }
+    s_acc[warp][lane] = acc;
+    __syncthreads();   // also: every read of s_red above is done
+    if (lane == 0) s_red[warp] = wsum;
+    __syncthreads();
+
+    // 3. the eight partial rows
     if (warp == 0) {
-        float mm = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
         float tot = 0.0f;
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int w4 = 0; w4 < 4; ++w4) {
-            if (s_m[w4] == -INFINITY) continue;   // this warp had no piece
-            const float a = __expf(s_m[w4] - mm);
-            const float4 x = s_acc[w4][lane];
-            tot += a * s_w[w4];
-            o.x += a * x.x; o.y += a * x.y; o.z += a * x.z; o.w += a * x.w;
+        for (int w8 = 0; w8 < kWarps; ++w8) {
+            const float4 x = s_acc[w8][lane];
+            tot += s_red[w8];
+            o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w;
         }
         const float inv = 1.0f / tot;
         o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
