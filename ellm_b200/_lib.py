@@ -43,6 +43,7 @@ class MatMul3Desc(C.Structure):
         ("m_row", C.c_size_t), ("col", C.c_size_t), ("b_q_row", C.c_size_t), ("b_kv_row", C.c_size_t),
         ("max_batch", C.c_size_t), ("max_seq", C.c_size_t), ("eps", C.c_float), ("device", C.c_int),
         ("stream", C.c_void_p), ("async_", C.c_int),
+        ("input_norm", C.c_int), ("input_norm_eps", C.c_float), ("normed_scratch", C.c_void_p),
     ]
 
 

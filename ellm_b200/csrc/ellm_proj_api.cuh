@@ -55,8 +55,8 @@ int proj_common_create(ProjHandle* h, int device, void* stream, int async) {
     }
     *h->status_host = 0;
     ELLM_CUDA(cudaMemset(h->status_dev, 0, sizeof(int)));
-    static_assert(ellm::kSkSmemMax + 1024 <= 232448, "shared memory budget");
-    if (cudaFuncSetAttribute(ellm::proj_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kSkSmemMax + 1024) != cudaSuccess)
+    static_assert(ellm::kSkSmemMax + 256 + 1024 <= 232448, "shared memory budget: dynamic + static");
+    if (cudaFuncSetAttribute(ellm::proj_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kSkSmemMax + 256) != cudaSuccess)
         return fail(ELLM_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(cudaGetLastError()));
     return ELLM_OK;
 }
@@ -93,7 +93,8 @@ bool skinny_plan(ProjHandle* h, ProjHandle::Skinny& sk, const void* w, size_t n,
 // is still running: its weight loads do not depend on that kernel, its activations are read after
 // a device-side wait for it.
 int skinny_launch(ProjHandle* h, const ProjHandle::Skinny& sk, const void* a, size_t lda, size_t k, size_t rows,
-                  size_t batch, size_t max_batch, void* c, size_t ldc, const void* residual, size_t ldr) {
+                  size_t batch, size_t max_batch, void* c, size_t ldc, const void* residual, size_t ldr,
+                  float input_norm_eps = -1.0f) {
     ellm::SkinnyParams p{};
     p.a = static_cast<const __nv_bfloat16*>(a);
     p.lda = static_cast<long long>(lda);
@@ -111,6 +112,7 @@ int skinny_launch(ProjHandle* h, const ProjHandle::Skinny& sk, const void* a, si
     p.ldc = static_cast<long long>(ldc);
     p.residual = static_cast<const __nv_bfloat16*>(residual);
     p.ldr = static_cast<long long>(ldr);
+    p.input_norm_eps = input_norm_eps;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(sk.ctas));
     cfg.blockDim = dim3(ellm::kSkThreads);
@@ -218,7 +220,7 @@ int matmul3_run_impl(ellm_matmul3* h, const int32_t* positions, size_t position_
         size_t col0 = 0;
         for (int i = 0; i < h->sk_count; ++i) {
             if (int st = skinny_launch(h, h->sk[i], d.hidden, lda, d.col, rows, batch, d.max_batch, h->qkv_scratch + col0, ldq,
-                                       nullptr, 0))
+                                       nullptr, 0, d.input_norm ? d.input_norm_eps : -1.0f))
                 return st;
             col0 += h->sk[i].n;
         }
@@ -251,6 +253,11 @@ int matmul3_run_impl(ellm_matmul3* h, const int32_t* positions, size_t position_
     p.kv_heads = static_cast<int>(kv_heads);
     p.eps = d.eps;
     const size_t lda = d.hidden_row_stride ? d.hidden_row_stride : d.col;
+    if (d.input_norm) {
+        if (lda != d.col) return fail(ELLM_ERR_UNSUPPORTED, "input_norm needs contiguous rows of hidden");
+        if (int st = ellm_rms_norm(d.hidden, d.normed_scratch, rows, d.col, d.input_norm_eps, h->device, h->stream)) return st;
+        return proj_launch(h, d.normed_scratch, d.col, d.col, rows, p);
+    }
     return proj_launch(h, d.hidden, lda, d.col, rows, p);
 }
 
@@ -283,6 +290,8 @@ int ellm_matmul3_create(const ellm_matmul3_desc* d, ellm_matmul3** out) {
         return fail(ELLM_ERR_INVALID_ARG, "buffers must be 16-byte aligned");
     if (!(d->eps >= 0.0f)) return fail(ELLM_ERR_INVALID_ARG, "eps must be >= 0");
     if (d->max_seq == 0 || d->rope_rows == 0) return fail(ELLM_ERR_INVALID_ARG, "max_seq and rope_rows must be > 0");
+    if (d->input_norm && (!(d->input_norm_eps >= 0.0f) || !d->normed_scratch || !aligned16(d->normed_scratch)))
+        return fail(ELLM_ERR_INVALID_ARG, "input_norm needs input_norm_eps >= 0 and a 16-byte aligned normed_scratch");
     DeviceGuard guard(d->device);
     if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", d->device);
     ellm_matmul3* h = new (std::nothrow) ellm_matmul3();

@@ -22,6 +22,7 @@
 // the slice is taken in several passes over K.
 #pragma once
 #include "proj_tcgen05.cuh"
+#include "rms_norm.cuh"
 
 namespace ellm {
 
@@ -29,7 +30,7 @@ constexpr int kSkRows = 16;                    // activation rows = M of the MMA
 constexpr int kSkWarps = 8;
 constexpr int kSkThreads = kSkWarps * 32;
 constexpr int kSkMaxCols = 64;                 // columns per CTA (accumulators: cols/8 x 4 registers)
-constexpr int kSkSmemMax = 232448 - 1024;
+constexpr int kSkSmemMax = 232448 - 2048;          // dynamic part; the kernel also has a few static words
 
 struct SkinnyParams {
     const __nv_bfloat16* a;
@@ -45,6 +46,7 @@ struct SkinnyParams {
     long long ldc;
     const __nv_bfloat16* residual;
     long long ldr;
+    float input_norm_eps;     // >= 0: the rows of A are RMS-normalised (no weight) on their way in; < 0: taken as they are
 };
 
 // shared memory: [x tile: m_rows x K bf16][128 zero bytes][slice: cols x pass_chunks x 16 bytes];
@@ -91,11 +93,26 @@ __global__ void __launch_bounds__(kSkThreads, 1) proj_skinny_kernel(const Skinny
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // activations (and the residual) are the previous kernels' output: wait for them
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (int m = 0; m < p.m_rows; ++m) {
-        const bool live = (m % p.max_batch) < p.batch;
-        const __nv_bfloat16* src = p.a + (live ? m * p.lda : 0);
-        for (int c = threadIdx.x; c < p.k_chunks; c += kSkThreads)
-            cp_async_16(x_base + (m * p.k_chunks + (c ^ (m & 7))) * 16, src + c * 8, live ? 16 : 0);
+    if (p.input_norm_eps >= 0.0f) {
+        // the layer's input norm, y = x / (sqrt(mean x^2) + eps) rounded to bf16, on the few rows
+        // of a decode step (src/kernel/generic/rms_norm.rs:6-26); the same code as rms_norm_kernel
+        __shared__ float warp_sums[8];
+        __shared__ float s_rrms;
+        for (int m = 0; m < p.m_rows; ++m) {
+            const bool live = (m % p.max_batch) < p.batch;   // uniform over the CTA
+            const uint4* src = reinterpret_cast<const uint4*>(p.a + (live ? m * p.lda : 0));
+            const float rrms = live ? block_row_rrms(src, p.k_chunks, p.k_chunks * 8, p.input_norm_eps, warp_sums, &s_rrms) : 0.0f;
+            for (int c = threadIdx.x; c < p.k_chunks; c += kSkThreads)
+                *reinterpret_cast<uint4*>(smem + (m * p.k_chunks + (c ^ (m & 7))) * 16) =
+                    live ? scale_piece(src[c], rrms) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    } else {
+        for (int m = 0; m < p.m_rows; ++m) {
+            const bool live = (m % p.max_batch) < p.batch;
+            const __nv_bfloat16* src = p.a + (live ? m * p.lda : 0);
+            for (int c = threadIdx.x; c < p.k_chunks; c += kSkThreads)
+                cp_async_16(x_base + (m * p.k_chunks + (c ^ (m & 7))) * 16, src + c * 8, live ? 16 : 0);
+        }
     }
     if (threadIdx.x < 8) cp_async_16(zero_addr + threadIdx.x * 16, p.a, 0);   // the row every missing row reads
     cp_async_commit();

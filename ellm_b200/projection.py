@@ -57,7 +57,9 @@ class MatMul3(_Projection):
     def new(cls, hidden_ptr, q_weight_ptr_nt, q_state_ptr, k_weight_ptr_nt, k_cache, v_weight_ptr_nt, v_cache,
             rope_ptr, head_dim, m_row, col, b_q_row, b_kv_row, *, kv_strides, max_batch, max_seq, rope_rows,
             eps=1e-6, q_norm_weight=None, k_norm_weight=None, hidden_row_stride=0, device=0, stream=None,
-            async_=False):
+            async_=False, input_norm_eps=None, normed_scratch=None):
+        """input_norm_eps: when given, hidden_ptr is the layer's un-normalised input and the operator
+        applies the weight-free RMS norm itself (normed_scratch [m_row, col] is then required)."""
         self = object.__new__(cls)
         lib = L.load()
         d = L.MatMul3Desc()
@@ -70,11 +72,13 @@ class MatMul3(_Projection):
         d.head_dim, d.m_row, d.col, d.b_q_row, d.b_kv_row = head_dim, m_row, col, b_q_row, b_kv_row
         d.max_batch, d.max_seq, d.eps = max_batch, max_seq, float(eps)
         d.device, d.stream, d.async_ = device, stream, 1 if async_ else 0
+        if input_norm_eps is not None:
+            d.input_norm, d.input_norm_eps, d.normed_scratch = 1, float(input_norm_eps), _ptr(normed_scratch)
         handle = C.c_void_p()
         L.check(lib.ellm_matmul3_create(C.byref(d), C.byref(handle)))
         self._lib, self._h, self.desc = lib, handle, d
         self._keep = (hidden_ptr, q_weight_ptr_nt, q_state_ptr, k_weight_ptr_nt, k_cache, v_weight_ptr_nt, v_cache,
-                      rope_ptr, q_norm_weight, k_norm_weight)
+                      rope_ptr, q_norm_weight, k_norm_weight, normed_scratch)
         return self
 
     def run(self, position_index, position_interval, batch_size, cpu_num=1, thread_id=0):

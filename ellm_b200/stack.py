@@ -3,7 +3,8 @@
 Per layer, following the reference's decoder layer and attention block minus the MoE part
 (src/qwen3_moe/decoder_layer.rs:139-165, src/qwen3_moe/attention.rs:126-196):
 
-    h   = rms(x)                                   input norm, weight-free (generic/rms_norm.rs:6-26): ellm_rms_norm
+    h   = rms(x)                                   input norm, weight-free (generic/rms_norm.rs:6-26): ellm_rms_norm,
+                                                   or inside MatMul3 (input_norm)
     q,k,v = h [Wq;Wk;Wv]^T                         matmul3 (src/compiler/mul/matmul3.rs:289-385), one GEMM
     q,k = rope(qk_norm(q, k)); cache <- k, v       ellm_qk_norm_rope_append
     a   = Attention(q, cache)                      ellm_attn_run
@@ -75,19 +76,19 @@ class AttentionStack:
                                           self.cache.strides, self.scale, max_seq=max_seq, max_interval=max_interval,
                                           device=dev_index, stream=raw_stream, async_=True))
             if self.own_projections:
-                self.qkv_ops.append(MatMul3.new(self.h, self.wq[i], self.q, self.wk[i], ck, self.wv[i], cv, self.rope,
+                # the layer's input norm rides inside the projection operator
+                self.qkv_ops.append(MatMul3.new(self.x, self.wq[i], self.q, self.wk[i], ck, self.wv[i], cv, self.rope,
                                                 head_dim, rows, hidden, qd, kd, kv_strides=self.cache.strides,
                                                 max_batch=max_batch, max_seq=max_seq, rope_rows=max_seq, eps=eps,
                                                 q_norm_weight=self.q_norm[i], k_norm_weight=self.k_norm[i],
-                                                device=dev_index, stream=raw_stream, async_=True))
+                                                device=dev_index, stream=raw_stream, async_=True,
+                                                input_norm_eps=eps, normed_scratch=self.h))
                 self.out_ops.append(MatMulAdd.new(self.a, self.wo[i], self.x, self.x, rows, hidden, qd,
                                                   max_batch=max_batch, device=dev_index, stream=raw_stream, async_=True))
         self._rows = rows
 
     def _layer_tensor_core(self, i, n, batch, position_index, ragged):
         """One layer on self.x[:n * max_batch] in place, projections on this repository's kernels."""
-        rows = n * self.max_batch
-        rms_norm(self.x[:rows], self.h[:rows], self.eps, device=self.dev.index or 0, stream=self.stream.cuda_stream)
         if ragged:
             self.qkv_ops[i].run_ragged(self.positions, n, batch)
             self.ops[i].run_ragged(self.positions, n, batch, 1, 0)

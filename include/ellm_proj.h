@@ -65,6 +65,16 @@ typedef struct ellm_matmul3_desc {
     int device;
     void* stream;
     int async;                 /* 0: run() returns after the stream drained; 1: only enqueues   */
+    /* Optional: the layer's input norm taken into the operator.  With input_norm != 0, `hidden` is
+     * the layer's un-normalised input and every row is first replaced by x / (sqrt(mean x^2) +
+     * input_norm_eps), rounded to bf16 - the weight-free rms_norm the reference runs as its own
+     * operator before this one (src/qwen3_moe/decoder_layer.rs:139-143, src/kernel/generic/
+     * rms_norm.rs:6-26); same bits as ellm_rms_norm followed by this operator.  A decode step
+     * normalises its few rows inside the projection kernel; a chunk writes the normalised rows to
+     * normed_scratch ([m_row x col] bf16, the caller's, may be shared by all layers) first. */
+    int input_norm;
+    float input_norm_eps;
+    void* normed_scratch;
 } ellm_matmul3_desc;
 
 int ellm_matmul3_create(const ellm_matmul3_desc* desc, ellm_matmul3** out);

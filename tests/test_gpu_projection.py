@@ -186,3 +186,36 @@ def test_invalid_arguments():
     op.run(0, 32, 4, cpu_num=8, thread_id=3)   # a worker that is not thread 0 launches nothing
     assert op.kernel_stats()[0] == 0
     op.close()
+
+
+@pytest.mark.parametrize("interval,max_batch", [(1, 4), (1, 16), (160, 2)])
+def test_matmul3_input_norm_equals_separate_norm(interval, max_batch):
+    """The input norm inside the operator gives the bits of ellm_rms_norm followed by the operator."""
+    g = torch.Generator().manual_seed(31)
+    q_heads, kv_heads, hidden, max_seq = 8, 2, 1024, 256
+    m = interval * max_batch
+    x = (torch.randn(m, hidden, generator=g) * 3).to(torch.bfloat16).to(DEV)
+    wqkv = (torch.randn((q_heads + 2 * kv_heads) * 128, hidden, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    wq, wk, wv = wqkv[:q_heads * 128], wqkv[q_heads * 128:(q_heads + kv_heads) * 128], wqkv[(q_heads + kv_heads) * 128:]
+    rope = torch.from_numpy(ellm_b200.precompute_freqs_cis(128, max_seq, 1e6)).to(DEV)
+    strides = [kv_heads * max_seq * 128, max_seq * 128, 128, 1]
+    outs = []
+    for fused in (False, True):
+        ck = torch.zeros(max_batch, kv_heads, max_seq, 128, dtype=torch.bfloat16, device=DEV)
+        cv = torch.zeros_like(ck)
+        q_out = torch.zeros(interval, max_batch, q_heads, 128, dtype=torch.bfloat16, device=DEV)
+        h = torch.zeros_like(x)
+        if fused:
+            op = MatMul3.new(x, wq, q_out, wk, ck, wv, cv, rope, 128, m, hidden, q_heads * 128, kv_heads * 128,
+                             kv_strides=strides, max_batch=max_batch, max_seq=max_seq, rope_rows=max_seq,
+                             input_norm_eps=1e-6, normed_scratch=h)
+        else:
+            ellm_b200.rms_norm(x, h, 1e-6)
+            op = MatMul3.new(h, wq, q_out, wk, ck, wv, cv, rope, 128, m, hidden, q_heads * 128, kv_heads * 128,
+                             kv_strides=strides, max_batch=max_batch, max_seq=max_seq, rope_rows=max_seq)
+        op.run(7, interval, max_batch - 1 if max_batch > 2 else max_batch)
+        outs.append((bits(q_out), bits(ck), bits(cv)))
+        op.close()
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
+    assert outs[0][0].any() and outs[0][1].any()
