@@ -245,6 +245,81 @@ def prefill_long(dev, stream_ptr):
                          "peak_source": src + " bf16_tflops (burst: the kernel is timed alone)"}}
 
 
+def projections_extra(dev, stream_ptr):
+    """Secondary figures: the projections either side of attention at one layer of BASELINE
+    configs[3] (hidden 2048, 32 q / 4 kv heads): the tcgen05 kernel on a 32768-row chunk, and the
+    weight-streaming kernel on a one-row decode step (8 weight sets in rotation, 300 MB > L2)."""
+    import ellm_b200
+    from ellm_b200.projection import MatMul3, MatMulAdd
+    S, hidden, Hq, Hkv = 32768, 2048, 32, 4
+    qd, kd = Hq * D, Hkv * D
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(S, hidden, device=dev, generator=g).to(torch.bfloat16)
+    wqkv = [(torch.randn(qd + 2 * kd, hidden, device=dev, generator=g) * 0.02).to(torch.bfloat16) for _ in range(8)]
+    wo = [(torch.randn(hidden, qd, device=dev, generator=g) * 0.02).to(torch.bfloat16) for _ in range(8)]
+    ck = torch.zeros(1, Hkv, S, D, dtype=torch.bfloat16, device=dev)
+    cv = torch.zeros_like(ck)
+    strides = [Hkv * S * D, S * D, D, 1]
+    rope = torch.from_numpy(ellm_b200.precompute_freqs_cis(D, S, 1e6)).to(dev)
+    q = torch.zeros(S, 1, Hq, D, dtype=torch.bfloat16, device=dev)
+    a = torch.randn(S, qd, device=dev, generator=g).to(torch.bfloat16)
+    y = torch.zeros(S, hidden, dtype=torch.bfloat16, device=dev)
+    ones = torch.ones(D, device=dev)
+    burst, sustained, src = measured_tensor_peaks()
+
+    def timed(fn, reps, rounds=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize(dev)
+        times = []
+        for _ in range(rounds):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            times.append(e0.elapsed_time(e1) / reps)
+        return statistics.median(times)
+
+    out = {}
+    qkv_ops = [MatMul3.new(x, w[:qd], q, w[qd:qd + kd], ck, w[qd + kd:], cv, rope, D, S, hidden, qd, kd, kv_strides=strides,
+                           max_batch=1, max_seq=S, rope_rows=S, q_norm_weight=ones, k_norm_weight=ones, device=dev.index,
+                           stream=stream_ptr, async_=True) for w in wqkv]
+    out_ops = [MatMulAdd.new(a, w, y, y, S, hidden, qd, max_batch=1, device=dev.index, stream=stream_ptr, async_=True)
+               for w in wo]
+    ms = timed(lambda: qkv_ops[0].run(0, S, 1), 4)
+    tf = 2.0 * S * hidden * (qd + 2 * kd) / ms / 1e9
+    out["qkv_norm_rope_append_chunk"] = {"kernel": "proj_tcgen05_kernel", "rows": S, "ms": ms, "tflops": tf,
+                                         "frac_of_measured_burst_peak": tf / burst}
+    ms = timed(lambda: out_ops[0].run(0, S, 1), 4)
+    tf = 2.0 * S * hidden * qd / ms / 1e9
+    out["out_proj_residual_chunk"] = {"kernel": "proj_tcgen05_kernel", "rows": S, "ms": ms, "tflops": tf,
+                                      "frac_of_measured_burst_peak": tf / burst}
+    peak, peak_src = measured_peaks()
+
+    def all_qkv():
+        for op in qkv_ops:
+            op.run(0, 1, 1)
+
+    def all_out():
+        for op in out_ops:
+            op.run(0, 1, 1)
+
+    ms = timed(all_qkv, 4) / len(qkv_ops)
+    gbs = (qd + 2 * kd) * hidden * 2 / ms / 1e6
+    out["qkv_decode_step"] = {"kernel": "proj_skinny_kernel + qk_norm_rope_append_kernel", "rows": 1, "us": ms * 1e3,
+                              "weight_gbs": gbs, "frac_of_measured_hbm": gbs / peak}
+    ms = timed(all_out, 4) / len(out_ops)
+    gbs = hidden * qd * 2 / ms / 1e6
+    out["out_proj_decode_step"] = {"kernel": "proj_skinny_kernel", "rows": 1, "us": ms * 1e3, "weight_gbs": gbs,
+                                   "frac_of_measured_hbm": gbs / peak}
+    out["peaks"] = {"bf16_tflops_burst": burst, "hbm_gbs": peak, "source": src}
+    for op in qkv_ops + out_ops:
+        op.close()
+    return out
+
+
 def prefill_extra(dev, stream_ptr, steps, warmup):
     """Secondary figure: causal prefill of BASELINE configs[0] (seq 2048, 32/32 heads)."""
     from ellm_b200 import Attention
@@ -423,7 +498,8 @@ def main():
                                 "sample": leg[2], "ms_per_step": leg[3], **cpu_info()}
     if world == 1 and not args.no_extra:
         line["extra"] = {"prefill": prefill_extra(dev, stream.cuda_stream, args.steps, args.warmup),
-                         "prefill_long": prefill_long(dev, stream.cuda_stream)}
+                         "prefill_long": prefill_long(dev, stream.cuda_stream),
+                         "projections": projections_extra(dev, stream.cuda_stream)}
     print(json.dumps(line))
     if world > 1:
         dist.barrier()

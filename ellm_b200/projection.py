@@ -115,3 +115,78 @@ class MatMulAdd(_Projection):
     def run(self, position_index, position_interval, batch_size, cpu_num=1, thread_id=0):
         L.check(self._lib.ellm_matmul_add_run(self._h, position_index, position_interval, batch_size, cpu_num,
                                               thread_id))
+
+
+def main():
+    """Times the two projection operators at one layer's shape (defaults: BASELINE configs[3]):
+
+        python -m ellm_b200.projection --rows 32768        # tcgen05 kernel, a prefill chunk
+        python -m ellm_b200.projection --rows 1            # weight-streaming kernel, a decode step
+    """
+    import argparse
+    import json
+
+    import torch
+
+    from .rope import precompute_freqs_cis
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows", type=int, default=32768)
+    ap.add_argument("--hidden", type=int, default=2048)
+    ap.add_argument("--q-heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=4)
+    ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--weight-sets", type=int, default=8, help="rotated so that decode steps stream weights from HBM, not L2")
+    args = ap.parse_args()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    S, hidden, qd, kd = args.rows, args.hidden, args.q_heads * 128, args.kv_heads * 128
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(S, hidden, device=dev, generator=g).to(torch.bfloat16)
+    a = torch.randn(S, qd, device=dev, generator=g).to(torch.bfloat16)
+    y = torch.zeros(S, hidden, dtype=torch.bfloat16, device=dev)
+    q = torch.zeros(S, 1, args.q_heads, 128, dtype=torch.bfloat16, device=dev)
+    max_seq = max(S, 64)
+    ck = torch.zeros(1, args.kv_heads, max_seq, 128, dtype=torch.bfloat16, device=dev)
+    cv = torch.zeros_like(ck)
+    strides = [args.kv_heads * max_seq * 128, max_seq * 128, 128, 1]
+    rope = torch.from_numpy(precompute_freqs_cis(128, max_seq, 1e6)).to(dev)
+    ones = torch.ones(128, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    sets = args.weight_sets if S <= 16 else 1
+    qkv_ops, out_ops = [], []
+    for _ in range(sets):
+        w = (torch.randn(qd + 2 * kd, hidden, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        wo = (torch.randn(hidden, qd, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        qkv_ops.append(MatMul3.new(x, w[:qd], q, w[qd:qd + kd], ck, w[qd + kd:], cv, rope, 128, S, hidden, qd, kd,
+                                   kv_strides=strides, max_batch=1, max_seq=max_seq, rope_rows=max_seq, q_norm_weight=ones,
+                                   k_norm_weight=ones, stream=stream, async_=True))
+        out_ops.append(MatMulAdd.new(a, wo, y, y, S, hidden, qd, max_batch=1, stream=stream, async_=True))
+
+    def timed(ops):
+        for op in ops:
+            op.run(0, S, 1)
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.reps):
+            for op in ops:
+                op.run(0, S, 1)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / (args.reps * len(ops))
+
+    t3, ta = timed(qkv_ops), timed(out_ops)
+    for op in qkv_ops + out_ops:
+        op.check()
+    print(json.dumps({
+        "rows": S, "hidden": hidden, "q_heads": args.q_heads, "kv_heads": args.kv_heads,
+        "matmul3_ms": t3, "matmul3_tflops": 2.0 * S * hidden * (qd + 2 * kd) / t3 / 1e9,
+        "matmul3_weight_gbs": (qd + 2 * kd) * hidden * 2 / t3 / 1e6,
+        "matmul_add_ms": ta, "matmul_add_tflops": 2.0 * S * hidden * qd / ta / 1e9,
+        "matmul_add_weight_gbs": hidden * qd * 2 / ta / 1e6}))
+    for op in qkv_ops + out_ops:
+        op.close()
+
+
+if __name__ == "__main__":
+    main()
