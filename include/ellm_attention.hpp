@@ -6,6 +6,9 @@
 //
 //   ellm::Attention<T>::make(...)   Attention::new        src/compiler/mul/attention.rs:41-67
 //   ellm::Attention<T>::run(...)    Attention::run        src/compiler/mul/attention.rs:69-76
+//   ellm::MatMul3<T>::make / run    MatMul3::new / run    src/compiler/mul/matmul3.rs:60-119, 289-385
+//   ellm::MatMulAdd<T>::make / run  MatMulAdd::new / run  src/compiler/mul/matmul_add.rs:60-126, 128-232
+//   ellm::Operator                  enum Operator<T>      src/compiler/operator.rs:30-75 (one run() for all)
 //   ellm::Barrier                   runtime::barrier      src/runtime/barrier.rs:7-40
 //   ellm::assign(...)               compiler::assign      src/compiler/assign.rs:11-38
 //   ellm::start(...)                serving::start::start src/serving/start.rs:18-86
@@ -21,6 +24,8 @@
 #include <cstddef>
 #include <cstdint>
 #include <exception>
+#include <functional>
+#include <memory>
 #include <optional>
 #include <stdexcept>
 #include <string>
@@ -32,6 +37,7 @@
 #include <sched.h>
 
 #include "ellm_attn.h"
+#include "ellm_proj.h"
 
 namespace ellm {
 
@@ -122,6 +128,144 @@ class Attention {
   private:
     Attention() = default;
     ellm_attn* handle_ = nullptr;
+};
+
+// What the projections need beyond the reference's constructor arguments.
+struct ProjectionOptions {
+    size_t max_batch = 1;          // sequences per chunk row: matrix row = chunk row * max_batch + sequence
+    int device = 0;
+    void* stream = nullptr;
+    bool async = false;
+};
+
+// The three projections of an attention block with their finalize step (per-head RMS norm, RoPE)
+// and the write of K and V into the static cache.
+template <typename T>
+class MatMul3 {
+    static_assert(sizeof(T) == 2, "bf16 storage (2-byte elements) only");
+
+  public:
+    struct Cache {                 // where K and V rows go instead of k_state_ptr / v_state_ptr
+        T* k_cache = nullptr;
+        T* v_cache = nullptr;
+        std::vector<size_t> kv_strides;
+        size_t max_seq = 0;
+    };
+    struct Norms {                 // optional extensions: head-norm weights, the layer's input norm
+        const float* q_weight = nullptr;
+        const float* k_weight = nullptr;
+        float eps = 1e-6f;
+        bool input_norm = false;
+        float input_norm_eps = 1e-6f;
+        T* normed_scratch = nullptr;
+    };
+    // MatMul3::new(hidden_ptr, q_weight_ptr_nt, q_state_ptr, k_weight_ptr_nt, [k_state_ptr], v_weight_ptr_nt,
+    //              [v_state_ptr], rope_ptr, head_dim, m_row, col, b_q_row, b_kv_row, ...)
+    static MatMul3 make(const T* hidden_ptr, const T* q_weight_ptr_nt, T* q_state_ptr, const T* k_weight_ptr_nt,
+                        const T* v_weight_ptr_nt, const float* rope_ptr, size_t rope_rows, size_t head_dim, size_t m_row,
+                        size_t col, size_t b_q_row, size_t b_kv_row, const Cache& cache, const Norms& norms,
+                        const ProjectionOptions& opt) {
+        if (cache.kv_strides.size() != 4) throw std::invalid_argument("kv_strides must have 4 entries");
+        ellm_matmul3_desc d{};
+        d.hidden = hidden_ptr;
+        d.wq_nt = q_weight_ptr_nt;
+        d.wk_nt = k_weight_ptr_nt;
+        d.wv_nt = v_weight_ptr_nt;
+        d.q_state = q_state_ptr;
+        d.k_cache = cache.k_cache;
+        d.v_cache = cache.v_cache;
+        for (int i = 0; i < 4; ++i) d.kv_strides[i] = cache.kv_strides[i];
+        d.rope = rope_ptr;
+        d.rope_rows = rope_rows;
+        d.q_norm_weight = norms.q_weight;
+        d.k_norm_weight = norms.k_weight;
+        d.head_dim = head_dim;
+        d.m_row = m_row;
+        d.col = col;
+        d.b_q_row = b_q_row;
+        d.b_kv_row = b_kv_row;
+        d.max_batch = opt.max_batch;
+        d.max_seq = cache.max_seq;
+        d.eps = norms.eps;
+        d.device = opt.device;
+        d.stream = opt.stream;
+        d.async = opt.async ? 1 : 0;
+        d.input_norm = norms.input_norm ? 1 : 0;
+        d.input_norm_eps = norms.input_norm_eps;
+        d.normed_scratch = norms.normed_scratch;
+        MatMul3 m;
+        check(ellm_matmul3_create(&d, &m.handle_));
+        return m;
+    }
+    MatMul3(MatMul3&& o) noexcept : handle_(o.handle_) { o.handle_ = nullptr; }
+    MatMul3(const MatMul3&) = delete;
+    MatMul3& operator=(const MatMul3&) = delete;
+    ~MatMul3() { ellm_matmul3_destroy(handle_); }
+    void run(size_t position_index, size_t position_interval, size_t batch_size, size_t cpu_num, size_t thread_id) const {
+        check(ellm_matmul3_run(handle_, position_index, position_interval, batch_size, cpu_num, thread_id));
+    }
+
+  private:
+    MatMul3() = default;
+    ellm_matmul3* handle_ = nullptr;
+};
+
+// output = residual + A . W_nt^T (residual may be null: the plain MatMul).
+template <typename T>
+class MatMulAdd {
+    static_assert(sizeof(T) == 2, "bf16 storage (2-byte elements) only");
+
+  public:
+    // MatMulAdd::new(ptr1, ptr2 (N x K), ptr3 (residual), output_ptr, m_max, n_max, k_max, ...)
+    static MatMulAdd make(const T* ptr1, const T* ptr2_nt, const T* ptr3, T* output_ptr, size_t m_max, size_t n_max,
+                          size_t k_max, const ProjectionOptions& opt) {
+        ellm_matmul_add_desc d{};
+        d.a = ptr1;
+        d.w_nt = ptr2_nt;
+        d.residual = ptr3;
+        d.output = output_ptr;
+        d.m_max = m_max;
+        d.n_max = n_max;
+        d.k_max = k_max;
+        d.max_batch = opt.max_batch;
+        d.device = opt.device;
+        d.stream = opt.stream;
+        d.async = opt.async ? 1 : 0;
+        MatMulAdd m;
+        check(ellm_matmul_add_create(&d, &m.handle_));
+        return m;
+    }
+    MatMulAdd(MatMulAdd&& o) noexcept : handle_(o.handle_) { o.handle_ = nullptr; }
+    MatMulAdd(const MatMulAdd&) = delete;
+    MatMulAdd& operator=(const MatMulAdd&) = delete;
+    ~MatMulAdd() { ellm_matmul_add_destroy(handle_); }
+    void run(size_t position_index, size_t position_interval, size_t batch_size, size_t cpu_num, size_t thread_id) const {
+        check(ellm_matmul_add_run(handle_, position_index, position_interval, batch_size, cpu_num, thread_id));
+    }
+
+  private:
+    MatMulAdd() = default;
+    ellm_matmul_add* handle_ = nullptr;
+};
+
+// One entry of the executor's operator queue: any operator behind the common run() signature
+// (the reference's enum Operator<T> dispatches to the variant's run, src/compiler/operator.rs:68-75).
+class Operator {
+  public:
+    using Run = std::function<void(size_t, size_t, size_t, size_t, size_t)>;
+    explicit Operator(Run run) : run_(std::move(run)) {}
+    // takes ownership of an operator object with a run(position_index, position_interval, batch, cpus, tid)
+    template <class Op>
+    static Operator own(Op&& op) {
+        auto held = std::make_shared<std::decay_t<Op>>(std::forward<Op>(op));
+        return Operator([held](size_t p, size_t n, size_t b, size_t c, size_t t) { held->run(p, n, b, c, t); });
+    }
+    void run(size_t position_index, size_t position_interval, size_t batch_size, size_t cpu_num, size_t thread_id) const {
+        run_(position_index, position_interval, batch_size, cpu_num, thread_id);
+    }
+
+  private:
+    Run run_;
 };
 
 // Arrival counter + generation word; waiters spin on the generation.

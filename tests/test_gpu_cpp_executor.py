@@ -1,6 +1,7 @@
-"""Builds and runs the C++ host mirror's executor test (tests/cpp/executor_test.cpp) on a B200:
-pinned threads, every thread calls run(), spin barrier per operator, chunked prompt then
-decode steps, checked against the CPU oracle inside the binary."""
+"""Builds and runs the C++ host mirror's executor tests (tests/cpp/) on a B200: pinned threads,
+every thread calls run(), spin barrier per operator, chunked prompt then decode steps, checked
+against the CPU oracle inside the binaries - the attention operator alone, and a whole
+attention-only layer (projection operators either side of it)."""
 import os
 import shutil
 import subprocess
@@ -14,18 +15,31 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def test_cpp_executor_spmd_generation(tmp_path):
+def _build(tmp_path, name):
     ellm_b200.load()
     oracle.load()
     cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
-    exe = str(tmp_path / "executor_test")
-    cmd = [shutil.which("g++") or "g++", "-std=c++17", "-O2", "-pthread", os.path.join(ROOT, "tests", "cpp", "executor_test.cpp"),
+    exe = str(tmp_path / name)
+    cmd = [shutil.which("g++") or "g++", "-std=c++17", "-O2", "-pthread", os.path.join(ROOT, "tests", "cpp", name + ".cpp"),
            "-I", os.path.join(ROOT, "include"), "-I", os.path.join(ROOT, "oracle"), "-I", os.path.join(cuda, "include"),
            "-L", os.path.join(ROOT, "ellm_b200"), "-lellm_attn", "-L", os.path.join(ROOT, "oracle", "_build"), "-lellm_oracle",
            "-L", os.path.join(cuda, "lib64"), "-lcudart",
            "-Wl,-rpath," + os.path.join(ROOT, "ellm_b200"), "-Wl,-rpath," + os.path.join(ROOT, "oracle", "_build"),
            "-Wl,-rpath," + os.path.join(cuda, "lib64"), "-o", exe]
     subprocess.run(cmd, check=True, capture_output=True, text=True)
+    return exe
+
+
+def test_cpp_layer_through_operator_queue(tmp_path):
+    exe = _build(tmp_path, "layer_test")
+    for threads in ("1", "5"):
+        res = subprocess.run([exe, threads], capture_output=True, text=True, timeout=300)
+        assert res.returncode == 0, res.stdout + res.stderr
+        assert "V rows off 0" in res.stdout
+
+
+def test_cpp_executor_spmd_generation(tmp_path):
+    exe = _build(tmp_path, "executor_test")
     for threads in ("1", "7"):
         res = subprocess.run([exe, threads], capture_output=True, text=True, timeout=300)
         assert res.returncode == 0, res.stdout + res.stderr
