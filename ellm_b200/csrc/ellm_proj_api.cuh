@@ -177,6 +177,7 @@ int proj_launch(ProjHandle* h, const void* a, size_t lda, size_t k, size_t rows,
     p.tiles_m = static_cast<int>((rows + ellm::kPjBM - 1) / ellm::kPjBM);
     p.status = h->status_dev;
     p.wait_timeout_ns = h->plan.wait_timeout_ns;
+    p.debug_skip_load = h->plan.debug_skip_load;
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     const unsigned grid = static_cast<unsigned>(tiles < h->plan.sm_count ? tiles : h->plan.sm_count);
     cudaEvent_t e0 = nullptr, e1 = nullptr;
@@ -468,6 +469,14 @@ int ellm_matmul_check(void* handle, int which) {
     ELLM_CUDA(cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
     ELLM_CUDA(cudaStreamSynchronize(h->stream));
     return proj_check_status(h);
+}
+
+int ellm_matmul_debug_skip_load(void* handle, int which, int item) {
+    ProjHandle* h = proj_cast(handle, which);
+    if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL or not of kind %d", which);
+    std::lock_guard<std::mutex> lock(h->mu);
+    h->plan.debug_skip_load = item < 0 ? -1 : item;
+    return ELLM_OK;
 }
 
 int ellm_matmul_set_wait_timeout(void* handle, int which, unsigned long long ns) {

@@ -57,6 +57,7 @@ struct ProjParams {
     int tiles_q, tiles_kv;    // kPjQkv: column tiles of Wq and of Wk (= of Wv)
     int* status;
     unsigned long long wait_timeout_ns;
+    int debug_skip_load;      // test hook: ring item of CTA 0 the producer never loads (its barrier stays unsignalled); -1 = none
     int batch, max_batch;     // rows are (chunk row r, sequence b) = r * max_batch + b; rows with b >= batch are skipped
     // ---- kPjPlain
     __nv_bfloat16* c;
@@ -254,6 +255,7 @@ proj_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const int slot = item % kPjStages, round = item / kPjStages;
                     ok = mbar_wait(bar_empty(slot), (round & 1) ^ 1, abort_word, p.status, kPjWaitEmpty, p.wait_timeout_ns);
                     if (!ok) break;
+                    if (item == p.debug_skip_load && blockIdx.x == 0) continue;   // test hook: this block never arrives
                     const uint32_t dst = smem_base + slot * kPjStageBytes;
                     mbar_arrive_expect_tx(bar_full(slot), kPjStageBytes);
                     tma_load_2d(dst, &map_a, bar_full(slot), kb * kPjBK, tm * kPjBM);
@@ -380,6 +382,7 @@ struct ProjPlan {
     void* encode = nullptr;
     int sm_count = 0;
     unsigned long long wait_timeout_ns = 2000000000ull;
+    int debug_skip_load = -1;
 };
 
 inline void proj_plan_init(ProjPlan& plan, int sm_count) {

@@ -34,6 +34,9 @@ class _Projection:
         """Waits for the stream; raises if a device-side wait ran out since the last check."""
         L.check(self._lib.ellm_matmul_check(self._h, self._which))
 
+    def debug_skip_load(self, item):
+        L.check(self._lib.ellm_matmul_debug_skip_load(self._h, self._which, int(item)))
+
     def set_wait_timeout(self, ns):
         L.check(self._lib.ellm_matmul_set_wait_timeout(self._h, self._which, int(ns)))
 

@@ -124,6 +124,10 @@ int ellm_matmul_kernel_stats(void* handle, int which, uint64_t* launches, uint64
 int ellm_matmul_check(void* handle, int which);
 /* Bound of every device-side wait of the handle's kernel, nanoseconds (default 2e9). */
 int ellm_matmul_set_wait_timeout(void* handle, int which, unsigned long long ns);
+/* Test hook for the failure path: the tensor-memory kernel's loader leaves operand block `item`
+ * (counted over the first CTA's k-blocks) unloaded, so the wait on it runs out after the bound above
+ * and the run reports ELLM_ERR_DEVICE_TIMEOUT; -1 switches it off. */
+int ellm_matmul_debug_skip_load(void* handle, int which, int item);
 
 #ifdef __cplusplus
 }

@@ -170,6 +170,35 @@ def test_matmul3_model_shape():
              position_index=100)
 
 
+def test_matmul_between_the_two_kernels_row_counts():
+    # 17 .. 127 rows: more than the streaming kernel takes, less than one full tile of the other
+    _matmul_add(7, interval=20, max_batch=2, batch=2, n=512, k=256, residual=True)
+    _matmul3(17, interval=9, max_batch=3, batch=3, q_heads=4, kv_heads=2, hidden=256, max_seq=64, position_index=30)
+
+
+def test_device_wait_timeout_is_reported_and_the_handle_stays_usable():
+    """Failure detection without a fault: the loader leaves one operand block unloaded (a barrier that
+    nothing signals), the wait on it runs out after the configured bound, every role leaves, tensor
+    memory is released and the run reports ELLM_ERR_DEVICE_TIMEOUT.  The same handle then runs
+    normally and matches the oracle."""
+    from ellm_b200 import _lib as L
+    g = torch.Generator().manual_seed(41)
+    m, n, k = 256, 512, 256
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16)
+    out = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    op = MatMulAdd.new(a.to(DEV), w.to(DEV), None, out, m, n, k, max_batch=1)
+    op.set_wait_timeout(200_000_000)   # 0.2 s
+    op.debug_skip_load(2)
+    with pytest.raises(ellm_b200.EllmError) as e:
+        op.run(0, m, 1)
+    assert e.value.status == L.ERR_DEVICE_TIMEOUT
+    op.debug_skip_load(-1)
+    op.run(0, m, 1)                    # same handle, same context
+    _close(bits(out), oracle.matmul_nt_bf16(bits(a), bits(w)), 0.99, atol=2e-5 * np.sqrt(k))
+    op.close()
+
+
 def test_invalid_arguments():
     x = torch.zeros(128, 100, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(256, 100, dtype=torch.bfloat16, device=DEV)
