@@ -87,6 +87,7 @@ _SIGNATURES = {
     "ellm_matmul_set_profiling": (_I, [_VP, _I, _I]),
     "ellm_matmul_kernel_stats": (_I, [_VP, _I, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),
     "ellm_matmul_check": (_I, [_VP, _I]),
+    "ellm_matmul_set_pairing": (_I, [_VP, _I, _I]),
     "ellm_matmul_debug_skip_load": (_I, [_VP, _I, _I]),
     "ellm_matmul_set_wait_timeout": (_I, [_VP, _I, C.c_ulonglong]),
     "ellm_last_error": (C.c_char_p, []),

@@ -13,7 +13,8 @@ struct ProjHandle {
     cudaStream_t stream = nullptr;
     bool async = false;
     ellm::ProjPlan plan;
-    CUtensorMap map_w[3];
+    CUtensorMap map_w[3];          // boxes of 256 weight rows (one CTA per tile)
+    CUtensorMap map_wp[3];         // boxes of 128 weight rows (a CTA pair per tile: each CTA loads half)
     CUtensorMap map_a;
     size_t map_a_rows = 0;         // rows map_a was encoded for (0 = none yet)
     // decode steps (at most 16 rows): the weight-streaming kernel
@@ -174,21 +175,45 @@ int proj_launch(ProjHandle* h, const void* a, size_t lda, size_t k, size_t rows,
     }
     p.m_rows = static_cast<int>(rows);
     p.k_blocks = static_cast<int>(k / ellm::kPjBK);
-    p.tiles_m = static_cast<int>((rows + ellm::kPjBM - 1) / ellm::kPjBM);
     p.status = h->status_dev;
     p.wait_timeout_ns = h->plan.wait_timeout_ns;
     p.debug_skip_load = h->plan.debug_skip_load;
-    const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
-    const unsigned grid = static_cast<unsigned>(tiles < h->plan.sm_count ? tiles : h->plan.sm_count);
+    // CTA pairs on 256 x 256 tiles when every pair gets at least four of them (a pair loads a third
+    // less per CTA from L2; with few tiles the finer 128-row tiles balance better)
+    const long long tiles256 = static_cast<long long>((rows + 255) / 256) * p.tiles_n;
+    const int pairs = h->plan.sm_count / 2;
+    const bool pair = h->plan.pairing == 1 ? rows > 128 : (h->plan.pairing == -1 && tiles256 >= 4ll * pairs);
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     if (h->profiling) {
         ELLM_CUDA(cudaEventCreate(&e0));
         ELLM_CUDA(cudaEventCreate(&e1));
         ELLM_CUDA(cudaEventRecord(e0, h->stream));
     }
-    ellm::proj_tcgen05_kernel<<<grid, ellm::kPjThreads, ellm::kPjSmemBytes, h->stream>>>(h->map_a, h->map_w[0], h->map_w[1],
-                                                                                        h->map_w[2], p);
-    ELLM_CUDA(cudaGetLastError());
+    if (pair) {
+        p.tiles_m = static_cast<int>((rows + 255) / 256);
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>(2 * (tiles256 < pairs ? tiles256 : pairs)));
+        cfg.blockDim = dim3(ellm::kPjThreads);
+        cfg.dynamicSmemBytes = ellm::kPjSmemBytes;
+        cfg.stream = h->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, ellm::proj_tcgen05_kernel<true>, h->map_a, h->map_wp[0], h->map_wp[1],
+                                                 h->map_wp[2], p);
+        if (e != cudaSuccess) return fail(ELLM_ERR_CUDA, "projection launch failed: %s", cudaGetErrorString(e));
+    } else {
+        p.tiles_m = static_cast<int>((rows + ellm::kPjBM - 1) / ellm::kPjBM);
+        const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+        const unsigned grid = static_cast<unsigned>(tiles < h->plan.sm_count ? tiles : h->plan.sm_count);
+        ellm::proj_tcgen05_kernel<false><<<grid, ellm::kPjThreads, ellm::kPjSmemBytes, h->stream>>>(h->map_a, h->map_w[0], h->map_w[1],
+                                                                                                   h->map_w[2], p);
+        ELLM_CUDA(cudaGetLastError());
+    }
     ++h->launches;
     if (h->profiling) {
         ELLM_CUDA(cudaEventRecord(e1, h->stream));
@@ -304,7 +329,8 @@ int ellm_matmul3_create(const ellm_matmul3_desc* d, ellm_matmul3** out) {
         const void* w[3] = {d->wq_nt, d->wk_nt, d->wv_nt};
         const size_t n[3] = {d->b_q_row, d->b_kv_row, d->b_kv_row};
         for (int i = 0; i < 3 && st == ELLM_OK; ++i)
-            if (!ellm::proj_encode_2d(h->plan, &h->map_w[i], w[i], n[i], d->col, d->col, ellm::kPjBN))
+            if (!ellm::proj_encode_2d(h->plan, &h->map_w[i], w[i], n[i], d->col, d->col, ellm::kPjBN) ||
+                !ellm::proj_encode_2d(h->plan, &h->map_wp[i], w[i], n[i], d->col, d->col, ellm::kPjBN / 2))
                 st = fail(ELLM_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled(weight %d) failed", i);
     }
     if (st == ELLM_OK) {
@@ -378,15 +404,16 @@ int ellm_matmul_add_create(const ellm_matmul_add_desc* d, ellm_matmul_add** out)
     h->which = 1;
     h->da = *d;
     int st = proj_common_create(h, d->device, d->stream, d->async);
-    if (st == ELLM_OK && !ellm::proj_encode_2d(h->plan, &h->map_w[0], d->w_nt, d->n_max, d->k_max, d->k_max, ellm::kPjBN))
+    if (st == ELLM_OK && (!ellm::proj_encode_2d(h->plan, &h->map_w[0], d->w_nt, d->n_max, d->k_max, d->k_max, ellm::kPjBN) ||
+                          !ellm::proj_encode_2d(h->plan, &h->map_wp[0], d->w_nt, d->n_max, d->k_max, d->k_max, ellm::kPjBN / 2)))
         st = fail(ELLM_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled(weight) failed");
     if (st != ELLM_OK) {
         proj_common_destroy(h);
         delete h;
         return st;
     }
-    h->map_w[1] = h->map_w[0];
-    h->map_w[2] = h->map_w[0];
+    h->map_w[1] = h->map_w[2] = h->map_w[0];
+    h->map_wp[1] = h->map_wp[2] = h->map_wp[0];
     h->sk_count = skinny_plan(h, h->sk[0], d->w_nt, d->n_max, d->k_max) ? 1 : 0;
     *out = h;
     return ELLM_OK;
@@ -469,6 +496,15 @@ int ellm_matmul_check(void* handle, int which) {
     ELLM_CUDA(cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
     ELLM_CUDA(cudaStreamSynchronize(h->stream));
     return proj_check_status(h);
+}
+
+int ellm_matmul_set_pairing(void* handle, int which, int mode) {
+    ProjHandle* h = proj_cast(handle, which);
+    if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL or not of kind %d", which);
+    if (mode < -1 || mode > 1) return fail(ELLM_ERR_INVALID_ARG, "mode must be -1, 0 or 1");
+    std::lock_guard<std::mutex> lock(h->mu);
+    h->plan.pairing = mode;
+    return ELLM_OK;
 }
 
 int ellm_matmul_debug_skip_load(void* handle, int which, int item) {

@@ -32,11 +32,16 @@ namespace ellm {
 constexpr int kPjBM = 128;         // rows per tile = tensor-memory lanes
 constexpr int kPjBN = 256;         // columns per tile = two heads
 constexpr int kPjBK = 64;          // k-elements per ring slot: one 128-byte swizzled row
-constexpr int kPjStages = 4;
 constexpr int kPjABytes = kPjBM * 128;                 // 16 KB
-constexpr int kPjBBytes = kPjBN * 128;                 // 32 KB
-constexpr int kPjStageBytes = kPjABytes + kPjBBytes;   // 48 KB
-constexpr int kPjSmemBar = kPjStages * kPjStageBytes;
+// One CTA per tile: 4 ring slots of A (16 KB) + W (256 rows, 32 KB).  Two CTAs per 256 x 256 tile
+// (cta_group::2): 6 slots of A (this CTA's 128 rows) + half of W (this CTA's 128 of the 256 columns).
+template <bool kPair> struct PjRing {
+    static constexpr int kStages = kPair ? 6 : 4;
+    static constexpr int kBBytes = kPair ? 128 * 128 : kPjBN * 128;
+    static constexpr int kStageBytes = kPjABytes + kBBytes;
+};
+constexpr int kPjSmemBar = PjRing<false>::kStages * PjRing<false>::kStageBytes;   // 192 KB either way
+static_assert(PjRing<true>::kStages * PjRing<true>::kStageBytes == kPjSmemBar, "both rings fill the same space");
 constexpr int kPjEpiWarps = 8;                          // two per tensor-memory lane quarter
 constexpr int kPjRopePitch = 64 + 16;                   // a staged piece of a rotation row (16 floats) + pad against bank conflicts
 constexpr int kPjStageWarpBytes = 32 * kPjRopePitch;    // per epilogue warp
@@ -52,7 +57,7 @@ struct ProjParams {
     int mode;                 // kPjPlain or kPjQkv
     int m_rows;               // rows of A that exist: chunk rows x max_batch
     int k_blocks;             // K / 64
-    int tiles_m;
+    int tiles_m;              // row tiles: of 128 rows, or of 256 rows for CTA pairs
     int tiles_n;              // all column tiles; in kPjQkv = tiles_q + 2 * tiles_kv
     int tiles_q, tiles_kv;    // kPjQkv: column tiles of Wq and of Wk (= of Wv)
     int* status;
@@ -86,9 +91,46 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
-// bf16 x bf16 -> fp32, M = 128, N = n, both operands K-major.
-__host__ __device__ constexpr uint32_t umma_idesc_n(uint32_t n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+// bf16 x bf16 -> fp32, M = m (128 for one CTA, 256 over a CTA pair), N = n, both operands K-major.
+__host__ __device__ constexpr uint32_t umma_idesc_mn(uint32_t m, uint32_t n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// ---- CTA pairs: two CTAs of a cluster share one 256 x 256 tile; CTA 0 issues the MMAs for both
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// the shared::cluster address of `addr` (a shared-memory address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's shared memory whose completion is counted on a barrier that may live in the pair's other CTA
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrival on a barrier (of either CTA of the pair) once every MMA issued so far has completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
@@ -196,42 +238,56 @@ __device__ __forceinline__ void proj_head_epilogue(const ProjParams& p, uint32_t
     }
 }
 
+template <bool kPair>
 __global__ void __launch_bounds__(kPjThreads, 1)
 proj_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w0,
                     const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUtensorMap map_w2,
                     const ProjParams p) {
+    constexpr int kStages = PjRing<kPair>::kStages, kStageBytes = PjRing<kPair>::kStageBytes;
+    constexpr int kTileRows = kPair ? 2 * kPjBM : kPjBM;   // rows of a tile over the CTA(s) that share it
     extern __shared__ unsigned char smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // pair mode: `rank` is this CTA's place in its pair, `unit` the pair's number; CTA 0 of a pair leads
+    const int rank = kPair ? static_cast<int>(cluster_ctarank()) : 0;
+    const int unit = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int units = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     const uint32_t bar0 = smem_base + kPjSmemBar;
-    auto bar_full = [&](int s) { return bar0 + 8u * s; };
-    auto bar_empty = [&](int s) { return bar0 + 8u * (kPjStages + s); };
-    auto bar_acc_full = [&](int a) { return bar0 + 8u * (2 * kPjStages + a); };
-    auto bar_acc_empty = [&](int a) { return bar0 + 8u * (2 * kPjStages + 2 + a); };
-    constexpr int kNumBars = 2 * kPjStages + 4;
+    auto bar_full = [&](int s) { return bar0 + 8u * s; };                        // used in the leader only
+    auto bar_empty = [&](int s) { return bar0 + 8u * (kStages + s); };
+    auto bar_acc_full = [&](int a) { return bar0 + 8u * (2 * kStages + a); };
+    auto bar_acc_empty = [&](int a) { return bar0 + 8u * (2 * kStages + 2 + a); };   // used in the leader only
+    constexpr int kNumBars = 2 * kStages + 4;
+    static_assert(8 * kNumBars + 16 <= 256, "barrier region too small");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kPjSmemBar + 8 * kNumBars);
     volatile int* abort_word = reinterpret_cast<volatile int*>(smem + kPjSmemBar + 8 * kNumBars + 8);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kPjStages; ++s) {
+        for (int s = 0; s < kStages; ++s) {
             mbar_init(bar_full(s), 1);
             mbar_init(bar_empty(s), 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(bar_acc_full(a), 1);
-            mbar_init(bar_acc_empty(a), kPjEpiWarps);   // one arrival per epilogue warp
+            mbar_init(bar_acc_empty(a), kPjEpiWarps * (kPair ? 2 : 1));   // one arrival per epilogue warp (of both CTAs)
         }
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (warp == 1) {   // in pair mode the same warp of both CTAs allocates together
+        if constexpr (kPair) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();   // the other CTA's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
@@ -242,7 +298,7 @@ proj_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             bool ok = true;
             int item = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int tile = unit; tile < total_tiles && ok; tile += units) {
                 const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
                 const CUtensorMap* map_w = &map_w0;
                 int n0 = tn * kPjBN;
@@ -252,41 +308,66 @@ proj_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     n0 = (tn - p.tiles_q - (is_k ? 0 : p.tiles_kv)) * kPjBN;
                 }
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++item) {
-                    const int slot = item % kPjStages, round = item / kPjStages;
+                    const int slot = item % kStages, round = item / kStages;
                     ok = mbar_wait(bar_empty(slot), (round & 1) ^ 1, abort_word, p.status, kPjWaitEmpty, p.wait_timeout_ns);
                     if (!ok) break;
                     if (item == p.debug_skip_load && blockIdx.x == 0) continue;   // test hook: this block never arrives
-                    const uint32_t dst = smem_base + slot * kPjStageBytes;
-                    mbar_arrive_expect_tx(bar_full(slot), kPjStageBytes);
-                    tma_load_2d(dst, &map_a, bar_full(slot), kb * kPjBK, tm * kPjBM);
-                    tma_load_2d(dst + kPjABytes, map_w, bar_full(slot), kb * kPjBK, n0);
+                    const uint32_t dst = smem_base + slot * kStageBytes;
+                    if constexpr (kPair) {
+                        // both CTAs' loads are counted on the leader's barrier: its own 32 KB and the other CTA's
+                        if (rank == 0) mbar_arrive_expect_tx(bar_full(slot), 2 * kStageBytes);
+                        const uint32_t full = mapa_shared(bar_full(slot), 0);
+                        tma_load_2d_pair(dst, &map_a, full, kb * kPjBK, tm * kTileRows + rank * kPjBM);
+                        tma_load_2d_pair(dst + kPjABytes, map_w, full, kb * kPjBK, n0 + rank * (kPjBN / 2));
+                    } else {
+                        mbar_arrive_expect_tx(bar_full(slot), kStageBytes);
+                        tma_load_2d(dst, &map_a, bar_full(slot), kb * kPjBK, tm * kPjBM);
+                        tma_load_2d(dst + kPjABytes, map_w, bar_full(slot), kb * kPjBK, n0);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         // =============================== MMA issuer ===============================
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             bool ok = true;
-            constexpr uint32_t idesc = umma_idesc_n(kPjBN);
+            constexpr uint32_t idesc = umma_idesc_mn(kTileRows, kPjBN);
             int item = 0, local = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+            for (int tile = unit; tile < total_tiles && ok; tile += units, ++local) {
                 const int acc = local & 1;
                 ok = mbar_wait(bar_acc_empty(acc), ((local >> 1) & 1) ^ 1, abort_word, p.status, kPjWaitAccEmpty, p.wait_timeout_ns);
                 if (!ok) break;
                 tc_fence_after();
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++item) {
-                    const int slot = item % kPjStages, round = item / kPjStages;
+                    const int slot = item % kStages, round = item / kStages;
                     ok = mbar_wait(bar_full(slot), round & 1, abort_word, p.status, kPjWaitFull, p.wait_timeout_ns);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_base + slot * kPjStageBytes, b_addr = a_addr + kPjABytes;
+                    const uint32_t a_addr = smem_base + slot * kStageBytes, b_addr = a_addr + kPjABytes;
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks)
-                        umma_bf16(tmem + acc * kPjBN, umma_desc(a_addr + ks * 32, 0, 1024), umma_desc(b_addr + ks * 32, 0, 1024),
-                                  idesc, (kb | ks) != 0);
-                    umma_commit(bar_empty(slot));
+                    for (int ks = 0; ks < 4; ++ks) {
+                        if constexpr (kPair)   // operands at the same offsets in both CTAs: A rows 128 + 128, W columns 128 + 128
+                            umma_bf16_pair(tmem + acc * kPjBN, umma_desc(a_addr + ks * 32, 0, 1024),
+                                           umma_desc(b_addr + ks * 32, 0, 1024), idesc, (kb | ks) != 0);
+                        else
+                            umma_bf16(tmem + acc * kPjBN, umma_desc(a_addr + ks * 32, 0, 1024), umma_desc(b_addr + ks * 32, 0, 1024),
+                                      idesc, (kb | ks) != 0);
+                    }
+                    if constexpr (kPair) {   // the slot is free in both CTAs
+                        umma_commit_pair(bar_empty(slot));
+                        umma_commit_pair(mapa_shared(bar_empty(slot), 1));
+                    } else {
+                        umma_commit(bar_empty(slot));
+                    }
                 }
-                if (ok) umma_commit(bar_acc_full(acc));
+                if (ok) {
+                    if constexpr (kPair) {
+                        umma_commit_pair(bar_acc_full(acc));
+                        umma_commit_pair(mapa_shared(bar_acc_full(acc), 1));
+                    } else {
+                        umma_commit(bar_acc_full(acc));
+                    }
+                }
             }
         }
         __syncwarp();
@@ -298,7 +379,7 @@ proj_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         bool ok = true;
         int local = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        for (int tile = unit; tile < total_tiles && ok; tile += units, ++local) {
             const int acc = local & 1;
             const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
             ok = lane == 0 ? mbar_wait(bar_acc_full(acc), (local >> 1) & 1, abort_word, p.status, kPjWaitAccFull, p.wait_timeout_ns) : true;
@@ -306,7 +387,7 @@ proj_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (!ok) break;
             tc_fence_after();
             const uint32_t tacc = tmem + lane_base + acc * kPjBN;
-            const long long m = static_cast<long long>(tm) * kPjBM + row;
+            const long long m = static_cast<long long>(tm) * kTileRows + rank * kPjBM + row;
             const int b = static_cast<int>(m % p.max_batch);
             const bool live = m < p.m_rows && b < p.batch;
             if (p.mode == kPjPlain) {
@@ -357,7 +438,10 @@ proj_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_acc_empty(acc));
+            if (lane == 0) {
+                if constexpr (kPair) mbar_arrive_cluster(mapa_shared(bar_acc_empty(acc), 0));
+                else mbar_arrive(bar_acc_empty(acc));
+            }
         }
     }
 
@@ -369,9 +453,12 @@ proj_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int i = 0; i < 200; ++i) __nanosleep(1000);
         __syncthreads();
     }
+    // neither CTA of a pair goes away while the other may still signal its barriers or read its operands
+    if constexpr (kPair) cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+        if constexpr (kPair) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
     }
 }
 
@@ -383,6 +470,7 @@ struct ProjPlan {
     int sm_count = 0;
     unsigned long long wait_timeout_ns = 2000000000ull;
     int debug_skip_load = -1;
+    int pairing = -1;   // CTA pairs per 256 x 256 tile: -1 = when the problem has enough tiles, 0 = never, 1 = whenever possible
 };
 
 inline void proj_plan_init(ProjPlan& plan, int sm_count) {
@@ -396,7 +484,8 @@ inline void proj_plan_init(ProjPlan& plan, int sm_count) {
         snprintf(plan.why, sizeof(plan.why), "driver does not export cuTensorMapEncodeTiled");
         return;
     }
-    if (cudaFuncSetAttribute(proj_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPjSmemBytes) != cudaSuccess) {
+    if (cudaFuncSetAttribute(proj_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPjSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(proj_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPjSmemBytes) != cudaSuccess) {
         snprintf(plan.why, sizeof(plan.why), "cannot reserve %d bytes of shared memory: %s", kPjSmemBytes,
                  cudaGetErrorString(cudaGetLastError()));
         return;

@@ -34,6 +34,10 @@ class _Projection:
         """Waits for the stream; raises if a device-side wait ran out since the last check."""
         L.check(self._lib.ellm_matmul_check(self._h, self._which))
 
+    def set_pairing(self, mode):
+        """CTA pairs per 256 x 256 tile in the tensor-memory kernel: -1 auto, 0 never, 1 whenever possible."""
+        L.check(self._lib.ellm_matmul_set_pairing(self._h, self._which, int(mode)))
+
     def debug_skip_load(self, item):
         L.check(self._lib.ellm_matmul_debug_skip_load(self._h, self._which, int(item)))
 

@@ -124,6 +124,10 @@ int ellm_matmul_kernel_stats(void* handle, int which, uint64_t* launches, uint64
 int ellm_matmul_check(void* handle, int which);
 /* Bound of every device-side wait of the handle's kernel, nanoseconds (default 2e9). */
 int ellm_matmul_set_wait_timeout(void* handle, int which, unsigned long long ns);
+/* Tuning knob of the tensor-memory kernel: two CTAs of a cluster share a 256 x 256 tile
+ * (tcgen05 cta_group::2; each CTA loads its 128 rows of A and half of the weight tile).
+ * mode -1 (default): when every pair gets at least two tiles; 0: never; 1: whenever rows > 128. */
+int ellm_matmul_set_pairing(void* handle, int which, int mode);
 /* Test hook for the failure path: the tensor-memory kernel's loader leaves operand block `item`
  * (counted over the first CTA's k-blocks) unloaded, so the wait on it runs out after the bound above
  * and the run reports ELLM_ERR_DEVICE_TIMEOUT; -1 switches it off. */

@@ -38,7 +38,7 @@ def _close_rotated(got, want):
     assert d.mean() <= 2e-4, d.mean()
 
 
-def _matmul_add(seed, interval, max_batch, batch, n, k, residual, in_place=False, a_pad=0):
+def _matmul_add(seed, interval, max_batch, batch, n, k, residual, in_place=False, a_pad=0, pairing=None):
     g = torch.Generator().manual_seed(seed)
     m = interval * max_batch
     a_full = torch.randn(m, k + a_pad, generator=g).to(torch.bfloat16)
@@ -50,6 +50,8 @@ def _matmul_add(seed, interval, max_batch, batch, n, k, residual, in_place=False
     dres = None if res is None else res.to(DEV)
     out = dres if in_place else canary.to(DEV)
     op = MatMulAdd.new(da, dw, dres, out, m, n, k, max_batch=max_batch, a_row_stride=k + a_pad)
+    if pairing is not None:
+        op.set_pairing(pairing)
     op.run(0, interval, batch)
     got = bits(out).reshape(interval, max_batch, n)
     want = want.reshape(interval, max_batch, n)
@@ -89,7 +91,7 @@ def test_matmul_decode_dead_slots_no_residual():
 
 
 def _matmul3(seed, interval, max_batch, batch, q_heads, kv_heads, hidden, max_seq, position_index=0, positions=None,
-             weights=True, one_matrix=False):
+             weights=True, one_matrix=False, pairing=None):
     g = torch.Generator().manual_seed(seed)
     m = interval * max_batch
     x = torch.randn(m, hidden, generator=g).to(torch.bfloat16)
@@ -123,6 +125,8 @@ def _matmul3(seed, interval, max_batch, batch, q_heads, kv_heads, hidden, max_se
                      hidden, q_heads * 128, kv_heads * 128, kv_strides=strides, max_batch=max_batch, max_seq=max_seq,
                      rope_rows=max_seq, eps=1e-6, q_norm_weight=None if qw is None else qw.to(DEV),
                      k_norm_weight=None if kw is None else kw.to(DEV))
+    if pairing is not None:
+        op.set_pairing(pairing)
     if positions is None:
         op.run(position_index, interval, batch)
     else:
@@ -168,6 +172,21 @@ def test_matmul3_model_shape():
     # the benchmark stack's layer shape on a short chunk: 40 heads of columns, 32 k-blocks
     _matmul3(14, interval=384, max_batch=1, batch=1, q_heads=32, kv_heads=4, hidden=2048, max_seq=512,
              position_index=100)
+
+
+def test_cta_pairs_matmul_add():
+    # two CTAs per 256 x 256 tile: ragged rows (300 = 256 + 44) and columns, then a many-tile case
+    _matmul_add(21, interval=300, max_batch=1, batch=1, n=200, k=256, residual=False, pairing=1)
+    _matmul_add(22, interval=67, max_batch=3, batch=2, n=640, k=192, residual=True, in_place=True, pairing=1)
+    _matmul_add(23, interval=1024, max_batch=1, batch=1, n=5120, k=2048, residual=True, a_pad=64, pairing=1)
+
+
+def test_cta_pairs_matmul3():
+    _matmul3(24, interval=200, max_batch=2, batch=2, q_heads=4, kv_heads=2, hidden=256, max_seq=256, position_index=37, pairing=1)
+    _matmul3(25, interval=70, max_batch=3, batch=2, q_heads=3, kv_heads=1, hidden=128, max_seq=96, position_index=5,
+             weights=False, pairing=1)
+    _matmul3(26, interval=384, max_batch=1, batch=1, q_heads=32, kv_heads=4, hidden=2048, max_seq=512, position_index=100,
+             pairing=1)
 
 
 def test_matmul_between_the_two_kernels_row_counts():
