@@ -23,6 +23,35 @@
 #include "qk_norm_rope_append.cuh"
 #include "rms_norm.cuh"
 
+namespace ellm {
+
+// The inputs of a host-buffer decode step, fetched from page-locked host memory by one small kernel
+// instead of one copy node per buffer: up to four (destination, source, bytes) ranges, bytes a
+// multiple of 4, both ends 16-byte aligned.
+struct StageIn {
+    void* dst[4];
+    const void* src[4];
+    unsigned long long bytes[4];
+    int n;
+};
+
+__global__ void __launch_bounds__(256) stage_in_kernel(const StageIn s) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const unsigned long long tid = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const unsigned long long step = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
+    for (int i = 0; i < s.n; ++i) {
+        const unsigned long long chunks = s.bytes[i] / 16, words = (s.bytes[i] % 16) / 4;
+        const uint4* src = static_cast<const uint4*>(s.src[i]);
+        uint4* dst = static_cast<uint4*>(s.dst[i]);
+        for (unsigned long long c = tid; c < chunks; c += step) dst[c] = src[c];
+        if (tid < words)
+            static_cast<unsigned*>(s.dst[i])[chunks * 4 + tid] = static_cast<const unsigned*>(s.src[i])[chunks * 4 + tid];
+    }
+}
+
+}  // namespace ellm
+
 namespace {
 
 thread_local char g_err[512] = "";
@@ -197,7 +226,8 @@ int launch_append(ellm_attn* h, cudaStream_t stream, void* k_cache, void* v_cach
 // Decode (interval == 1): K2 then K3.  out_f32 != nullptr selects the fp32
 // partial output of the windowed form.
 int launch_decode(ellm_attn* h, const int32_t* positions, size_t position_index, size_t batch,
-                  long long key_begin, long long key_end, float* out_f32, float* lse_out, bool append) {
+                  long long key_begin, long long key_end, float* out_f32, float* lse_out, bool append,
+                  void* out_override = nullptr) {
     if (batch > static_cast<size_t>(ellm::kDecMaxBatch))
         return fail(ELLM_ERR_UNSUPPORTED, "decode batch %zu exceeds %d", batch, ellm::kDecMaxBatch);
     ellm::DecodeParams p;
@@ -251,7 +281,8 @@ int launch_decode(ellm_attn* h, const int32_t* positions, size_t position_index,
         if (out_f32)
             e = cudaLaunchKernelEx(&cfg, ellm::decode_merge_kernel<float>, p, out_f32, lse_out);
         else
-            e = cudaLaunchKernelEx(&cfg, ellm::decode_merge_kernel<__nv_bfloat16>, p, static_cast<__nv_bfloat16*>(h->d.out), lse_out);
+            e = cudaLaunchKernelEx(&cfg, ellm::decode_merge_kernel<__nv_bfloat16>, p,
+                                   static_cast<__nv_bfloat16*>(out_override ? out_override : h->d.out), lse_out);
         if (e != cudaSuccess) return fail(ELLM_ERR_CUDA, "merge launch failed: %s", cudaGetErrorString(e));
     }
     ELLM_CUDA(cudaGetLastError());
@@ -317,7 +348,8 @@ int finish(ellm_attn* h, bool enqueue_only) {
 // Common body of run / run_ragged / run_window.
 int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size_t interval,
              size_t batch, long long key_begin, long long key_end, float* out_f32, float* lse_out,
-             bool append, int enqueue_only = -1, const cudaStream_t* stream_override = nullptr) {
+             bool append, int enqueue_only = -1, const cudaStream_t* stream_override = nullptr,
+             void* decode_out_override = nullptr) {
     if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL");
     if (interval == 0 || batch == 0) return ELLM_OK;  // nothing to do, as an empty assign() range
     if (batch > h->d.max_batch) return fail(ELLM_ERR_INVALID_ARG, "batch_size %zu > max_batch %zu", batch, h->d.max_batch);
@@ -348,7 +380,8 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
         if (rc) return rc;
     }
     if (interval == 1) {
-        rc = launch_decode(h, positions, position_index, batch, key_begin, key_end, out_f32, lse_out, do_append);
+        rc = launch_decode(h, positions, position_index, batch, key_begin, key_end, out_f32, lse_out, do_append,
+                           decode_out_override);
     } else {
         bool use_tc = false;
         if (key_begin == 0) {
@@ -512,6 +545,33 @@ int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
     const size_t kv_pitch = h->d.max_batch * h->d.kv_heads * D * 2, kv_width = batch_size * h->d.kv_heads * D * 2;
     const size_t l_pitch = h->d.max_batch * h->d.q_heads * 4, l_width = batch_size * h->d.q_heads * 4;
     const uint64_t tc_before = h->launches[ELLM_KERNEL_PREFILL_TCGEN05];
+    // The captured decode step moves its data without copy nodes: one small kernel fetches all
+    // inputs from the page-locked host buffers, and the merge kernel writes O and LSE straight
+    // into the host buffers (ordinary stores through the buffers' device addresses).
+    auto enqueue_direct = [&](cudaStream_t stream) -> int {
+        auto dev_ptr = [](const void* host, void** out) {
+            *out = nullptr;
+            if (!host) return true;
+            if (reinterpret_cast<uintptr_t>(host) & 15u) return false;
+            if (cudaHostGetDevicePointer(out, const_cast<void*>(host), 0) != cudaSuccess) { cudaGetLastError(); return false; }
+            return (reinterpret_cast<uintptr_t>(*out) & 15u) == 0;
+        };
+        void *dq, *dk, *dv, *dp, *dout, *dlse;
+        if (!dev_ptr(q_host, &dq) || !dev_ptr(k_new_host, &dk) || !dev_ptr(v_new_host, &dv) || !dev_ptr(positions_host, &dp) ||
+            !dev_ptr(out_host, &dout) || !dev_ptr(lse_host, &dlse))
+            return ELLM_ERR_UNSUPPORTED;
+        ellm::StageIn si{};
+        auto add = [&](const void* dst, const void* src, size_t bytes) {
+            si.dst[si.n] = const_cast<void*>(dst); si.src[si.n] = src; si.bytes[si.n] = bytes; ++si.n;
+        };
+        add(h->d.q, dq, q_width);
+        if (k_new_host) { add(h->d.k_new, dk, kv_width); add(h->d.v_new, dv, kv_width); }
+        add(h->positions_dev, dp, batch_size * sizeof(int32_t));
+        ellm::stage_in_kernel<<<32, 256, 0, stream>>>(si);
+        ELLM_CUDA(cudaGetLastError());
+        return run_impl(h, h->positions_dev, position_index, 1, batch_size, 0, INT64_MAX, nullptr,
+                        lse_host ? static_cast<float*>(dlse) : h->d.lse, k_new_host != nullptr, /*enqueue_only=*/1, &stream, dout);
+    };
     // everything a step enqueues on `stream`: inputs in, kernels, results out
     auto enqueue = [&](cudaStream_t stream) -> int {
         ELLM_CUDA(copy_rows(const_cast<void*>(h->d.q), q_host, q_pitch, q_width, position_interval, cudaMemcpyHostToDevice, stream));
@@ -567,7 +627,8 @@ int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
             cudaGraph_t graph = nullptr;
             bool ok = cudaStreamBeginCapture(h->graph_stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
             if (ok) {
-                const int rc = enqueue(h->graph_stream);
+                int rc = enqueue_direct(h->graph_stream);   // nothing is enqueued when it declines
+                if (rc == ELLM_ERR_UNSUPPORTED) rc = enqueue(h->graph_stream);
                 const cudaError_t e = cudaStreamEndCapture(h->graph_stream, &graph);
                 ok = rc == ELLM_OK && e == cudaSuccess && graph != nullptr;
             }

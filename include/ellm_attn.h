@@ -111,7 +111,10 @@ int ellm_attn_run_ragged(ellm_attn* h, const int32_t* positions, size_t position
  * runs, copies out (and lse) back, and returns when the results are in host
  * memory.  The KV cache stays resident on the device.  Decode steps with positions_host and
  * page-locked buffers are captured once into a CUDA graph and replayed for as long as the same
- * buffers are passed.  Calls on one handle must not overlap. */
+ * buffers are passed; in that graph one small kernel fetches all inputs from the host buffers
+ * and the last kernel of the step stores O and LSE directly into out_host / lse_host, so the
+ * handle's device out / lse buffers are not written by such a step.  Calls on one handle must
+ * not overlap. */
 int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
                        const void* v_new_host, void* out_host, float* lse_host,
                        const int32_t* positions_host, size_t position_index,
