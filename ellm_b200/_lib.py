@@ -81,6 +81,7 @@ _SIGNATURES = {
     "ellm_matmul3_destroy": (_I, [_VP]),
     "ellm_matmul3_run": (_I, [_VP, _SZ, _SZ, _SZ, _SZ, _SZ]),
     "ellm_matmul3_run_ragged": (_I, [_VP, _VP, _SZ, _SZ, _SZ, _SZ]),
+    "ellm_matmul3_set_decode_fusion": (_I, [_VP, _I]),
     "ellm_matmul_add_create": (_I, [C.POINTER(MatMulAddDesc), C.POINTER(_VP)]),
     "ellm_matmul_add_destroy": (_I, [_VP]),
     "ellm_matmul_add_run": (_I, [_VP, _SZ, _SZ, _SZ, _SZ, _SZ]),

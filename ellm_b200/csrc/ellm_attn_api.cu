@@ -831,6 +831,11 @@ int ellm_attn_set_option(ellm_attn* h, const char* name, long long value) {
         h->tc.wait_timeout_ns = static_cast<unsigned long long>(value);
         return ELLM_OK;
     }
+    if (std::strcmp(name, "decode_ctas") == 0) {   // grid of the decode kernel: 1 .. 2 x SMs (the workspace is sized for that)
+        if (value < 1 || value > 2 * h->sm_count) return fail(ELLM_ERR_INVALID_ARG, "decode_ctas must be in [1, %d]", 2 * h->sm_count);
+        h->dec_ctas = static_cast<int>(value);
+        return ELLM_OK;
+    }
     if (std::strcmp(name, "tc_debug_skip_kv_item") == 0) {
         h->tc.debug_skip_item = value < 0 ? -1 : static_cast<int>(value);
         return ELLM_OK;

@@ -24,6 +24,7 @@ struct ProjHandle {
         int cols = 0, ctas = 0;
     } sk[3];
     int sk_count = 0;              // 0 = unavailable for this shape, 1 = one matrix, 3 = Wq, Wk, Wv apart
+    bool decode_fused = true;      // MatMul3 decode steps: norm + rope + cache write inside the projection kernel
     __nv_bfloat16* qkv_scratch = nullptr;   // MatMul3: the projected rows of a decode step, [16 x (Nq + 2 Nkv)]
     uint64_t skinny_launches = 0;
     int* status_dev = nullptr;
@@ -56,7 +57,7 @@ int proj_common_create(ProjHandle* h, int device, void* stream, int async) {
     }
     *h->status_host = 0;
     ELLM_CUDA(cudaMemset(h->status_dev, 0, sizeof(int)));
-    static_assert(ellm::kSkSmemMax + 256 + 1024 <= 232448, "shared memory budget: dynamic + static");
+    static_assert(ellm::kSkSmemMax + 256 + 3072 <= 232448, "shared memory budget: dynamic + static");
     if (cudaFuncSetAttribute(ellm::proj_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kSkSmemMax + 256) != cudaSuccess)
         return fail(ELLM_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(cudaGetLastError()));
     return ELLM_OK;
@@ -93,10 +94,13 @@ bool skinny_plan(ProjHandle* h, ProjHandle::Skinny& sk, const void* w, size_t n,
 // One launch of the weight-streaming kernel, allowed to start while the stream's previous kernel
 // is still running: its weight loads do not depend on that kernel, its activations are read after
 // a device-side wait for it.
+// fused != nullptr: the head epilogue (its fields of SkinnyParams filled in), 16 columns per CTA, clusters of 8.
 int skinny_launch(ProjHandle* h, const ProjHandle::Skinny& sk, const void* a, size_t lda, size_t k, size_t rows,
                   size_t batch, size_t max_batch, void* c, size_t ldc, const void* residual, size_t ldr,
-                  float input_norm_eps = -1.0f) {
+                  float input_norm_eps = -1.0f, const ellm::SkinnyParams* fused = nullptr) {
     ellm::SkinnyParams p{};
+    if (fused) p = *fused;
+    const int cols = fused ? 16 : sk.cols;
     p.a = static_cast<const __nv_bfloat16*>(a);
     p.lda = static_cast<long long>(lda);
     p.m_rows = static_cast<int>(rows);
@@ -104,10 +108,10 @@ int skinny_launch(ProjHandle* h, const ProjHandle::Skinny& sk, const void* a, si
     p.max_batch = static_cast<int>(max_batch);
     p.w = static_cast<const __nv_bfloat16*>(sk.w);
     p.k_chunks = static_cast<int>(k / 8);
-    p.cols = sk.cols;
+    p.cols = cols;
     p.n_cols = static_cast<int>(sk.n);
     // the slice takes what the activation rows of this run leave of the shared memory
-    p.pass_chunks = ellm::skinny_pick_pass_chunks(p.k_chunks, sk.cols, p.m_rows);
+    p.pass_chunks = ellm::skinny_pick_pass_chunks(p.k_chunks, cols, p.m_rows);
     if (p.pass_chunks < 0) return fail(ELLM_ERR_UNSUPPORTED, "no shared-memory plan for %zu rows of %zu", rows, k);
     p.c = static_cast<__nv_bfloat16*>(c);
     p.ldc = static_cast<long long>(ldc);
@@ -115,15 +119,19 @@ int skinny_launch(ProjHandle* h, const ProjHandle::Skinny& sk, const void* a, si
     p.ldr = static_cast<long long>(ldr);
     p.input_norm_eps = input_norm_eps;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(static_cast<unsigned>(sk.ctas));
+    cfg.gridDim = dim3(static_cast<unsigned>(fused ? sk.n / 16 : sk.ctas));
     cfg.blockDim = dim3(ellm::kSkThreads);
-    cfg.dynamicSmemBytes = static_cast<size_t>(ellm::skinny_smem_bytes(p.k_chunks, sk.cols, p.pass_chunks, p.m_rows));
+    cfg.dynamicSmemBytes = static_cast<size_t>(ellm::skinny_smem_bytes(p.k_chunks, cols, p.pass_chunks, p.m_rows));
     cfg.stream = h->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;   // the 8 CTAs of a head
+    attr[1].val.clusterDim.x = 8;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = fused ? 2 : 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, ellm::proj_skinny_kernel, p);
     if (e != cudaSuccess) return fail(ELLM_ERR_CUDA, "projection launch failed: %s", cudaGetErrorString(e));
     ++h->skinny_launches;
@@ -243,6 +251,32 @@ int matmul3_run_impl(ellm_matmul3* h, const int32_t* positions, size_t position_
         // decode step: stream the weights once, then norm + rope + cache write on the projected rows
         const size_t lda = d.hidden_row_stride ? d.hidden_row_stride : d.col;
         const size_t ldq = d.b_q_row + 2 * d.b_kv_row;
+        if (h->decode_fused) {
+            // one kernel per weight matrix: projection, head norm, rotation, Q store and cache write
+            ellm::SkinnyParams f{};
+            f.q_heads = static_cast<int>(q_heads);
+            f.q_out = static_cast<__nv_bfloat16*>(d.q_state);
+            f.k_cache = static_cast<__nv_bfloat16*>(d.k_cache);
+            f.v_cache = static_cast<__nv_bfloat16*>(d.v_cache);
+            f.q_norm_weight = d.q_norm_weight;
+            f.k_norm_weight = d.k_norm_weight;
+            f.rope = d.rope;
+            f.positions = positions;
+            f.position_index = static_cast<long long>(position_index);
+            f.s0 = d.kv_strides[0]; f.s1 = d.kv_strides[1]; f.s2 = d.kv_strides[2];
+            f.max_seq = static_cast<long long>(d.max_seq);
+            f.rope_rows = static_cast<long long>(d.rope_rows);
+            f.eps = d.eps;
+            for (int i = 0; i < h->sk_count; ++i) {
+                f.heads = static_cast<int>(h->sk[i].n / 128);
+                f.mat_q_heads = h->sk_count == 1 ? static_cast<int>(q_heads) : (i == 0 ? f.heads : 0);
+                f.mat_k_heads = h->sk_count == 1 ? static_cast<int>(kv_heads) : (i == 1 ? f.heads : 0);
+                if (int st = skinny_launch(h, h->sk[i], d.hidden, lda, d.col, rows, batch, d.max_batch, nullptr, 0, nullptr, 0,
+                                           d.input_norm ? d.input_norm_eps : -1.0f, &f))
+                    return st;
+            }
+            return proj_finish(h);
+        }
         size_t col0 = 0;
         for (int i = 0; i < h->sk_count; ++i) {
             if (int st = skinny_launch(h, h->sk[i], d.hidden, lda, d.col, rows, batch, d.max_batch, h->qkv_scratch + col0, ldq,
@@ -496,6 +530,13 @@ int ellm_matmul_check(void* handle, int which) {
     ELLM_CUDA(cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
     ELLM_CUDA(cudaStreamSynchronize(h->stream));
     return proj_check_status(h);
+}
+
+int ellm_matmul3_set_decode_fusion(ellm_matmul3* h, int on) {
+    if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL");
+    std::lock_guard<std::mutex> lock(h->mu);
+    h->decode_fused = on != 0;
+    return ELLM_OK;
 }
 
 int ellm_matmul_set_pairing(void* handle, int which, int mode) {

@@ -30,7 +30,7 @@ constexpr int kSkRows = 16;                    // activation rows = M of the MMA
 constexpr int kSkWarps = 8;
 constexpr int kSkThreads = kSkWarps * 32;
 constexpr int kSkMaxCols = 64;                 // columns per CTA (accumulators: cols/8 x 4 registers)
-constexpr int kSkSmemMax = 232448 - 2048;          // dynamic part; the kernel also has a few static words
+constexpr int kSkSmemMax = 232448 - 4096;          // dynamic part; the kernel also has 2.2 KB of static shared memory
 
 struct SkinnyParams {
     const __nv_bfloat16* a;
@@ -47,6 +47,23 @@ struct SkinnyParams {
     const __nv_bfloat16* residual;
     long long ldr;
     float input_norm_eps;     // >= 0: the rows of A are RMS-normalised (no weight) on their way in; < 0: taken as they are
+    // ---- fused head epilogue (heads != 0): the columns are Q, K or V heads of 128, a cluster of
+    // 128 / cols CTAs owns one head, and instead of storing the projection the kernel finishes it:
+    // per-head RMS norm, weight, rotation at the token's position, Q to q_out, K and V into the cache
+    int heads;                // 0 = plain projection; else heads of this weight matrix (n_cols / 128):
+    int mat_q_heads;          //   the first mat_q_heads of them are Q heads, the next mat_k_heads K heads,
+    int mat_k_heads;          //   the rest V heads (a matrix of one kind has the other counts 0)
+    int q_heads;              // row pitch of q_out in heads
+    __nv_bfloat16* q_out;
+    __nv_bfloat16* k_cache;
+    __nv_bfloat16* v_cache;
+    const float* q_norm_weight;   // [128] or nullptr
+    const float* k_norm_weight;
+    const float* rope;
+    const int32_t* positions;
+    long long position_index;
+    long long s0, s1, s2, max_seq, rope_rows;
+    float eps;
 };
 
 // shared memory: [x tile: m_rows x K bf16][128 zero bytes][slice: cols x pass_chunks x 16 bytes];
@@ -180,6 +197,76 @@ __global__ void __launch_bounds__(kSkThreads, 1) proj_skinny_kernel(const Skinny
         }
     }
     __syncthreads();
+    if (p.heads != 0) {
+        // ---- fused head epilogue.  Thread t < 4 * m_rows owns 4 consecutive channels of one row of this
+        // CTA's 16 columns: exactly what one lane of qk_norm_rope_append_kernel owns, and the arithmetic
+        // below is that kernel's, so that both routes give the same bits.
+        __shared__ float ss_all[32][kSkRows];   // the head's 32 four-channel sums of squares of every row
+        const int t = threadIdx.x, m = t >> 2, quad = t & 3;
+        const bool mine = t < 4 * p.m_rows;
+        const bool live = mine && (m % p.max_batch) < p.batch;
+        const uint32_t crank = cluster_ctarank();          // which 16 columns of the head
+        int head = n0 >> 7, kind = 0;                       // head of this matrix -> kind and head of that kind
+        if (head >= p.mat_q_heads + p.mat_k_heads) { kind = 2; head -= p.mat_q_heads + p.mat_k_heads; }
+        else if (head >= p.mat_q_heads) { kind = 1; head -= p.mat_q_heads; }
+        float x[4] = {0.f, 0.f, 0.f, 0.f};
+        if (mine) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float sum = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kSkWarps; ++w) sum += part[(w * kSkRows + m) * p.cols + quad * 4 + e];
+                x[e] = bf16_round(sum);   // the projection as it would have been stored
+            }
+            if (kind != 2) {
+                const float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+                const uint32_t mine_addr = smem_u32(&ss_all[crank * 4 + quad][m]);
+#pragma unroll
+                for (uint32_t peer = 0; peer < 8; ++peer)
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(mapa_shared(mine_addr, peer)), "f"(ss) : "memory");
+            }
+        }
+        cluster_sync_all();   // every CTA of the head has every partial sum
+        if (live) {
+            const int b = m % p.max_batch;
+            const long long pos = (p.positions ? static_cast<long long>(p.positions[b]) : p.position_index) + m / p.max_batch;
+            const int ch = (n0 & 127) + quad * 4;   // channel of x[0] inside the head
+            if (kind == 2) {
+                if (pos >= 0 && pos < p.max_seq) {
+                    uint2 v;
+                    v.x = pack_bf16(x[0], x[1]);
+                    v.y = pack_bf16(x[2], x[3]);
+                    *reinterpret_cast<uint2*>(p.v_cache + b * p.s0 + head * p.s1 + pos * p.s2 + ch) = v;
+                }
+            } else if (!(kind == 1 && pos >= p.max_seq) && pos >= 0 && pos < p.rope_rows) {
+                // the butterfly of the separate kernel: lane i adds lane i ^ 16, then ^ 8, 4, 2, 1
+                float tsum[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) tsum[i] = ss_all[i][m];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    float nxt[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) nxt[i] = tsum[i] + tsum[i ^ o];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) tsum[i] = nxt[i];
+                }
+                const float rrms = 1.0f / (sqrtf(tsum[0] / static_cast<float>(kHeadDim)) + p.eps);
+                float4 wv = make_float4(1.f, 1.f, 1.f, 1.f);
+                const float* wgt = kind == 0 ? p.q_norm_weight : p.k_norm_weight;
+                if (wgt) wv = *reinterpret_cast<const float4*>(wgt + ch);
+                const float y0 = x[0] * rrms * wv.x, y1 = x[1] * rrms * wv.y, y2 = x[2] * rrms * wv.z, y3 = x[3] * rrms * wv.w;
+                const float4 cs = *reinterpret_cast<const float4*>(p.rope + pos * kHeadDim + ch);  // cos0 sin0 cos1 sin1
+                uint2 outv;
+                outv.x = pack_bf16(y0 * cs.x - y1 * cs.y, y0 * cs.y + y1 * cs.x);
+                outv.y = pack_bf16(y2 * cs.z - y3 * cs.w, y2 * cs.w + y3 * cs.z);
+                __nv_bfloat16* dst = kind == 0 ? p.q_out + (static_cast<long long>(m) * p.q_heads + head) * kHeadDim
+                                                      : p.k_cache + b * p.s0 + head * p.s1 + pos * p.s2;
+                *reinterpret_cast<uint2*>(dst + ch) = outv;
+            }
+        }
+        return;   // all remote stores into this CTA's shared memory were before the cluster barrier
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int idx = threadIdx.x + i * kSkThreads;

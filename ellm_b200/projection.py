@@ -91,6 +91,10 @@ class MatMul3(_Projection):
     def run(self, position_index, position_interval, batch_size, cpu_num=1, thread_id=0):
         L.check(self._lib.ellm_matmul3_run(self._h, position_index, position_interval, batch_size, cpu_num, thread_id))
 
+    def set_decode_fusion(self, on):
+        """Decode steps: head norm + rope + cache write inside the projection kernel (default) or as a second kernel."""
+        L.check(self._lib.ellm_matmul3_set_decode_fusion(self._h, 1 if on else 0))
+
     def run_ragged(self, positions, position_interval, batch_size, cpu_num=1, thread_id=0):
         L.check(self._lib.ellm_matmul3_run_ragged(self._h, _ptr(positions), position_interval, batch_size, cpu_num,
                                                   thread_id))

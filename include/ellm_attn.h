@@ -251,6 +251,8 @@ int ellm_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_c
  *   "tc_debug_skip_kv_item" test hook for that path: the kernel's loader never fetches ring item
  *                           N (0 = first K tile, 1 = first V tile, ...) so the wait on it runs
  *                           out; -1 (default) = off.  The context stays usable afterwards.
+ *   "decode_ctas"           grid of the decode kernel, 1 .. 2 x SMs (default 2 x SMs, for which the
+ *                           workspace is sized); a tuning knob.
  * Unknown names return ELLM_ERR_INVALID_ARG.  The reference has no counterpart (it aborts). */
 int ellm_attn_set_option(ellm_attn* h, const char* name, long long value);
 

@@ -86,6 +86,11 @@ int ellm_matmul3_run(ellm_matmul3* h, size_t position_index, size_t position_int
 int ellm_matmul3_run_ragged(ellm_matmul3* h, const int32_t* positions, size_t position_interval,
                             size_t batch_size, size_t cpu_num, size_t thread_id);
 
+/* Decode steps (at most 16 rows) run one kernel per weight matrix that projects and finishes the
+ * heads (default), or - with on = 0 - the projection kernel followed by ellm_qk_norm_rope_append's
+ * kernel; both give the same bits.  A tuning / comparison knob. */
+int ellm_matmul3_set_decode_fusion(ellm_matmul3* h, int on);
+
 /* ---- MatMulAdd: output = residual + A . W_nt^T ------------------------------------------------
  * Replaces MatMulAdd::new / run (src/compiler/mul/matmul_add.rs:60-126, 128-232: C = residual,
  * then C += A x B); with residual NULL it is the plain MatMul (src/compiler/mul/matmul.rs).

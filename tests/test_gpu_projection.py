@@ -267,3 +267,37 @@ def test_matmul3_input_norm_equals_separate_norm(interval, max_batch):
     for a, b in zip(*outs):
         assert np.array_equal(a, b)
     assert outs[0][0].any() and outs[0][1].any()
+
+
+@pytest.mark.parametrize("one_matrix", [True, False])
+def test_matmul3_decode_fusion_equals_two_kernels(one_matrix):
+    """A decode step finished inside the projection kernel (clusters of 8 CTAs per head) gives the bits
+    of the projection kernel followed by the norm + rope + append kernel."""
+    g = torch.Generator().manual_seed(51)
+    q_heads, kv_heads, hidden, max_seq, batch = 8, 2, 1024, 128, 5
+    x = torch.randn(batch, hidden, generator=g).to(torch.bfloat16).to(DEV)
+    wqkv = (torch.randn((q_heads + 2 * kv_heads) * 128, hidden, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    wq, wk, wv = wqkv[:q_heads * 128], wqkv[q_heads * 128:(q_heads + kv_heads) * 128], wqkv[(q_heads + kv_heads) * 128:]
+    if not one_matrix:
+        wq, wk, wv = wq.clone(), wk.clone(), wv.clone()
+    qw = (1 + 0.02 * torch.randn(128, generator=g)).float().to(DEV)
+    kw = (1 + 0.02 * torch.randn(128, generator=g)).float().to(DEV)
+    rope = torch.from_numpy(ellm_b200.precompute_freqs_cis(128, max_seq, 1e6)).to(DEV)
+    strides = [kv_heads * max_seq * 128, max_seq * 128, 128, 1]
+    positions = torch.tensor([0, 127, 64, 5, 99], dtype=torch.int32, device=DEV)
+    outs = []
+    for fused in (True, False):
+        ck = torch.zeros(batch, kv_heads, max_seq, 128, dtype=torch.bfloat16, device=DEV)
+        cv = torch.zeros_like(ck)
+        q_out = torch.zeros(1, batch, q_heads, 128, dtype=torch.bfloat16, device=DEV)
+        op = MatMul3.new(x, wq, q_out, wk, ck, wv, cv, rope, 128, batch, hidden, q_heads * 128, kv_heads * 128,
+                         kv_strides=strides, max_batch=batch, max_seq=max_seq, rope_rows=max_seq, q_norm_weight=qw,
+                         k_norm_weight=kw, input_norm_eps=1e-6, normed_scratch=torch.zeros_like(x))
+        op.set_decode_fusion(fused)
+        op.run_ragged(positions, 1, batch - 1)
+        outs.append((bits(q_out), bits(ck), bits(cv), op.kernel_stats()[0]))
+        op.close()
+    for a, b in zip(outs[0][:3], outs[1][:3]):
+        assert np.array_equal(a, b)
+    assert outs[0][0][0, :batch - 1].any() and not outs[0][0][0, batch - 1:].any()   # the dead slot stays untouched
+    assert outs[0][3] == (1 if one_matrix else 3)
