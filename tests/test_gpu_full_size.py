@@ -105,3 +105,67 @@ def test_tcgen05_and_warp_mma_kernels_agree_on_every_row_at_32768():
         d = (oc.float() - out_tc[c * chunk:(c + 1) * chunk].float()).abs()
         assert d.max().item() <= O_MAX_ABS and d.mean().item() <= O_MEAN_ABS
         assert (lc - lse_tc[c * chunk:(c + 1) * chunk]).abs().max().item() <= LSE_MAX_ABS
+
+
+def test_config4_layer_projections_full_chunk_sampled_rows():
+    """BASELINE configs[3]'s layer shape at its full prefill chunk (32768 rows, hidden 2048, 32 q / 4 kv
+    heads): the fused QKV projection and the output projection with residual run at full size (CTA pairs),
+    and 96 sampled rows - the first and last of the chunk, tile edges, random ones - are compared with the
+    oracle, which only needs those rows of A.  A second run with one CTA per tile must give the same bits
+    on every row (the two forms add the same products in the same order)."""
+    from ellm_b200.projection import MatMul3, MatMulAdd
+    dev = torch.device("cuda:0")
+    S, hidden, Hq, Hkv = 32768, 2048, 32, 4
+    qd, kd = Hq * 128, Hkv * 128
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(S, hidden, generator=g).to(torch.bfloat16)
+    wqkv = (torch.randn(qd + 2 * kd, hidden, generator=g) * 0.02).to(torch.bfloat16)
+    wo = (torch.randn(hidden, qd, generator=g) * 0.02).to(torch.bfloat16)
+    qw = (1 + 0.02 * torch.randn(128, generator=g)).float()
+    kw = (1 + 0.02 * torch.randn(128, generator=g)).float()
+    rope = ellm_b200.precompute_freqs_cis(128, S, 1e6)
+    strides = [Hkv * S * 128, S * 128, 128, 1]
+    rows = np.unique(np.concatenate([[0, 1, 127, 128, 255, 256, S - 257, S - 256, S - 129, S - 128, S - 1],
+                                     np.random.default_rng(4).integers(0, S, 85)]))
+    dx, dw, dwo = x.to(dev), wqkv.to(dev), wo.to(dev)
+    results = []
+    for pairing in (-1, 0):
+        ck = torch.zeros(1, Hkv, S, 128, dtype=torch.bfloat16, device=dev)
+        cv = torch.zeros_like(ck)
+        q = torch.zeros(S, 1, Hq, 128, dtype=torch.bfloat16, device=dev)
+        y = dx.clone()
+        op3 = MatMul3.new(dx, dw[:qd], q, dw[qd:qd + kd], ck, dw[qd + kd:], cv, torch.from_numpy(rope).to(dev), 128, S, hidden,
+                          qd, kd, kv_strides=strides, max_batch=1, max_seq=S, rope_rows=S, q_norm_weight=qw.to(dev),
+                          k_norm_weight=kw.to(dev))
+        op3.set_pairing(pairing)
+        op3.run(0, S, 1)
+        a = q.view(S, qd)   # any bf16 matrix serves as the output projection's input
+        opa = MatMulAdd.new(a, dwo, y, y, S, hidden, qd, max_batch=1)
+        opa.set_pairing(pairing)
+        opa.run(0, S, 1)
+        results.append((bits(q), bits(ck), bits(cv), bits(y)))
+        op3.close()
+        opa.close()
+    for u, v in zip(*results):
+        assert np.array_equal(u, v)
+    gq, gk, gv, gy = results[0]
+    # oracle on the sampled rows only: each row is the token at position = its index
+    xs = bits(x)[rows]
+    pq = oracle.matmul_nt_bf16(xs, bits(wqkv)[:qd]).reshape(len(rows), 1, Hq, 128)
+    pk = oracle.matmul_nt_bf16(xs, bits(wqkv)[qd:qd + kd]).reshape(len(rows), 1, Hkv, 128)
+    pv = oracle.matmul_nt_bf16(xs, bits(wqkv)[qd + kd:]).reshape(len(rows), 1, Hkv, 128)
+    for i, r in enumerate(rows):
+        ck1 = np.zeros((1, Hkv, S, 128), np.uint16) if i == 0 else ck1
+        cv1 = np.zeros((1, Hkv, S, 128), np.uint16) if i == 0 else cv1
+        wq_row = oracle.qk_norm_rope_append_bf16(pq[i:i + 1], pk[i:i + 1], pv[i:i + 1], ck1, cv1, rope, strides, Hq, Hkv,
+                                                 int(r), 1, 1, 1e-6, q_weight=qw.numpy(), k_weight=kw.numpy())
+        gw, ww = oracle.bf16_bits_to_f32(gq[r]), oracle.bf16_bits_to_f32(wq_row[0])
+        assert (gq[r] == wq_row[0]).mean() >= 0.95 and np.abs(gw - ww).max() <= 2.0 ** -5
+    for name, got, want in (("k", gk, ck1), ("v", gv, cv1)):
+        g32, w32 = oracle.bf16_bits_to_f32(got[0][:, rows]), oracle.bf16_bits_to_f32(want[0][:, rows])
+        assert (got[0][:, rows] == want[0][:, rows]).mean() >= 0.97, name
+        assert np.abs(g32 - w32).max() <= 2.0 ** -5, name
+    want_y = oracle.matmul_nt_bf16(gq.reshape(S, qd)[rows], bits(wo), bits(x)[rows])
+    g32, w32 = oracle.bf16_bits_to_f32(gy[rows]), oracle.bf16_bits_to_f32(want_y)
+    assert (gy[rows] == want_y).mean() >= 0.99
+    assert (np.abs(g32 - w32) <= np.abs(w32) * 2.0 ** -7 + 2e-5 * np.sqrt(qd)).all()
