@@ -23,6 +23,8 @@ struct AppendParams {
 };
 
 __global__ void __launch_bounds__(256) kv_append_kernel(const AppendParams p) {
+    // the kernel that follows (attention, launched as a programmatic dependent) may be set up now
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const long long rows = static_cast<long long>(p.interval) * p.batch * p.kv_heads;
     const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     const long long row = gid >> 4;

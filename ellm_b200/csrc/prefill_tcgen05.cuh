@@ -288,6 +288,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (threadIdx.x == (kTcTiles * 4) * 32) {   // the producer thread fetches the three descriptors ahead of its first copy
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+    }
 
     // barriers (8 bytes each) and two words behind them
     const uint32_t bar0 = smem_base + kTcSmemBar;
@@ -320,19 +326,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         kvh = head % p.kv_heads;
         b = head / p.kv_heads;
     }
-    const int total_rows = p.interval * p.group;
-    int steps[kTcTiles];
-#pragma unroll
-    // where this sequence's chunk starts and where its keys end
-    const long long base = p.positions ? static_cast<long long>(p.positions[b]) : p.base;
-    const long long key_end = p.positions ? min(base + p.interval, p.max_seq) : p.key_end;
-    for (int t = 0; t < kTcTiles; ++t) steps[t] = tc_tile_steps(p, (pair * kTcTiles + t) * kTcTileRows, total_rows, base, key_end);
-    const int nsteps = max(steps[0], steps[1]);
-    // With per-sequence chunk starts the K/V tensor maps are bounded by the cache, not by this
-    // sequence's end, so the last V tile may carry rows past key_end that hold anything; their P
-    // is 0 but 0 * NaN is NaN, so the producer zeroes them before the MMA may read the tile.
-    const bool zero_tail = p.positions != nullptr && static_cast<long long>(nsteps) * kTcKeys > key_end;
-
     if (threadIdx.x == 0) {
         for (int t = 0; t < kTcTiles; ++t) {
             mbar_init(bar_q(t), 1);
@@ -358,6 +351,23 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     // columns: S_0 [0,128), S_1 [128,256), O_0 [256,384), O_1 [384,512)
+
+    // Launched as a programmatic dependent, the set-up above ran while the stream's previous kernel
+    // was still at work; everything below reads or writes what that kernel may have touched.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int total_rows = p.interval * p.group;
+    int steps[kTcTiles];
+#pragma unroll
+    // where this sequence's chunk starts and where its keys end
+    const long long base = p.positions ? static_cast<long long>(p.positions[b]) : p.base;
+    const long long key_end = p.positions ? min(base + p.interval, p.max_seq) : p.key_end;
+    for (int t = 0; t < kTcTiles; ++t) steps[t] = tc_tile_steps(p, (pair * kTcTiles + t) * kTcTileRows, total_rows, base, key_end);
+    const int nsteps = max(steps[0], steps[1]);
+    // With per-sequence chunk starts the K/V tensor maps are bounded by the cache, not by this
+    // sequence's end, so the last V tile may carry rows past key_end that hold anything; their P
+    // is 0 but 0 * NaN is NaN, so the producer zeroes them before the MMA may read the tile.
+    const bool zero_tail = p.positions != nullptr && static_cast<long long>(nsteps) * kTcKeys > key_end;
+
 
     if (warp < kTcTiles * 4) {
         // =============================== softmax / correction / epilogue ===============================
@@ -837,12 +847,20 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
     // K and V rows this launch can touch, all heads and sequences together
     const unsigned long long kv_bytes = 2ull * static_cast<unsigned long long>(kv_rows) * 256ull * d.kv_heads * batch;
     p.pair_major = kv_bytes <= (96ull << 20) ? 1 : 0;
-    dim3 grid(static_cast<unsigned>(ctas));
-    if (out_f32)
-        prefill_tcgen05_kernel<float><<<grid, kTcThreads, kTcSmemBytes, stream>>>(map_q, map_k, map_v, p);
-    else
-        prefill_tcgen05_kernel<__nv_bfloat16><<<grid, kTcThreads, kTcSmemBytes, stream>>>(map_q, map_k, map_v, p);
-    return cudaGetLastError() == cudaSuccess ? ELLM_OK : ELLM_ERR_CUDA;
+    // a programmatic dependent of the stream's previous kernel: set-up overlaps that kernel's tail
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.dynamicSmemBytes = kTcSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = out_f32 ? cudaLaunchKernelEx(&cfg, prefill_tcgen05_kernel<float>, map_q, map_k, map_v, p)
+                                  : cudaLaunchKernelEx(&cfg, prefill_tcgen05_kernel<__nv_bfloat16>, map_q, map_k, map_v, p);
+    return e == cudaSuccess ? ELLM_OK : ELLM_ERR_CUDA;
 }
 
 }  // namespace ellm

@@ -249,6 +249,8 @@ proj_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the kernel that follows (attention, launched as a programmatic dependent) may be set up now
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // pair mode: `rank` is this CTA's place in its pair, `unit` the pair's number; CTA 0 of a pair leads
     const int rank = kPair ? static_cast<int>(cluster_ctarank()) : 0;
     const int unit = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);

@@ -67,3 +67,63 @@ def test_standalone_entry_points_check_arguments():
     assert lib.ellm_attn_merge_partials(0x1000, 0x1000, 0, 1, 128, 0x1000, None, 0, None) == L.ERR_INVALID_ARG
     out = C.c_void_p()
     assert lib.ellm_device_alloc(0, 0, C.byref(out)) == L.ERR_INVALID_ARG
+
+
+def _desc3(**kw):
+    d = L.MatMul3Desc()
+    d.hidden = d.wq_nt = d.wk_nt = d.wv_nt = d.q_state = d.k_cache = d.v_cache = d.rope = 0x1000
+    d.kv_strides = (C.c_size_t * 4)(2 * 64 * 128, 64 * 128, 128, 1)
+    d.rope_rows, d.head_dim, d.m_row, d.col, d.b_q_row, d.b_kv_row = 64, 128, 16, 256, 1024, 256
+    d.max_batch, d.max_seq, d.eps = 1, 64, 1e-6
+    for k, v in kw.items():
+        setattr(d, k, v)
+    return d
+
+
+def _desc_add(**kw):
+    d = L.MatMulAddDesc()
+    d.a = d.w_nt = d.output = 0x1000
+    d.m_max, d.n_max, d.k_max, d.max_batch = 16, 256, 128, 1
+    for k, v in kw.items():
+        setattr(d, k, v)
+    return d
+
+
+def test_bad_projection_descriptors_are_rejected_without_touching_a_gpu():
+    lib = ellm_b200.load()
+    h = C.c_void_p()
+    cases3 = [
+        (None, L.ERR_INVALID_ARG),
+        (_desc3(wk_nt=None), L.ERR_INVALID_ARG),
+        (_desc3(head_dim=64), L.ERR_UNSUPPORTED),
+        (_desc3(col=100), L.ERR_UNSUPPORTED),              # K not a multiple of 64
+        (_desc3(b_q_row=1000), L.ERR_INVALID_ARG),         # not whole heads
+        (_desc3(b_q_row=384), L.ERR_INVALID_ARG),          # 3 query heads over 2 KV heads
+        (_desc3(m_row=15, max_batch=2), L.ERR_INVALID_ARG),
+        (_desc3(hidden_row_stride=250), L.ERR_INVALID_ARG),
+        (_desc3(hidden=0x1008), L.ERR_INVALID_ARG),        # misaligned base
+        (_desc3(eps=-1.0), L.ERR_INVALID_ARG),
+        (_desc3(input_norm=1), L.ERR_INVALID_ARG),         # input norm without a scratch
+        (_desc3(kv_strides=(C.c_size_t * 4)(1024, 512, 128, 2)), L.ERR_UNSUPPORTED),
+    ]
+    for d, want in cases3:
+        rc = lib.ellm_matmul3_create(None if d is None else C.byref(d), C.byref(h))
+        assert rc == want, (rc, want, lib.ellm_last_error())
+        assert not h.value
+    cases_add = [
+        (None, L.ERR_INVALID_ARG),
+        (_desc_add(output=None), L.ERR_INVALID_ARG),
+        (_desc_add(k_max=96), L.ERR_UNSUPPORTED),
+        (_desc_add(n_max=100), L.ERR_UNSUPPORTED),
+        (_desc_add(m_max=10, max_batch=4), L.ERR_INVALID_ARG),
+        (_desc_add(a_row_stride=64), L.ERR_INVALID_ARG),   # shorter than a row
+        (_desc_add(residual=0x1002), L.ERR_INVALID_ARG),
+    ]
+    for d, want in cases_add:
+        rc = lib.ellm_matmul_add_create(None if d is None else C.byref(d), C.byref(h))
+        assert rc == want, (rc, want, lib.ellm_last_error())
+        assert not h.value
+    assert lib.ellm_matmul3_run(None, 0, 1, 1, 1, 0) == L.ERR_INVALID_ARG
+    assert lib.ellm_matmul_add_run(None, 0, 1, 1, 1, 0) == L.ERR_INVALID_ARG
+    assert lib.ellm_matmul3_destroy(None) == L.OK and lib.ellm_matmul_add_destroy(None) == L.OK
+    assert lib.ellm_matmul_check(None, 0) == L.ERR_INVALID_ARG
