@@ -649,12 +649,18 @@ int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
         }
     }
     if (use_graph) {
-        // order after whatever the caller queued on the handle's stream, then replay
-        ELLM_CUDA(cudaEventRecord(h->graph_event, h->stream));
-        ELLM_CUDA(cudaStreamWaitEvent(h->graph_stream, h->graph_event, 0));
-        ELLM_CUDA(cudaGraphLaunch(h->graph_exec, h->graph_stream));
+        // replay in the caller's stream; the legacy default stream cannot take a graph launch that
+        // must stay ordered with other streams' work, so there the graph runs in the handle's own
+        // stream, ordered after whatever the caller queued
+        const bool own = h->stream == nullptr || h->stream == cudaStreamLegacy || h->stream == cudaStreamPerThread;
+        cudaStream_t run_stream = own ? h->graph_stream : h->stream;
+        if (own) {
+            ELLM_CUDA(cudaEventRecord(h->graph_event, h->stream));
+            ELLM_CUDA(cudaStreamWaitEvent(h->graph_stream, h->graph_event, 0));
+        }
+        ELLM_CUDA(cudaGraphLaunch(h->graph_exec, run_stream));
         for (int i = 0; i < ELLM_KERNEL_COUNT; ++i) h->launches[i] += h->graph_launches[i];
-        ELLM_CUDA(cudaStreamSynchronize(h->graph_stream));
+        ELLM_CUDA(cudaStreamSynchronize(run_stream));
         return ELLM_OK;
     }
 
