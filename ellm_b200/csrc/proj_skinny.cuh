@@ -96,12 +96,15 @@ __global__ void __launch_bounds__(kSkThreads, 1) proj_skinny_kernel(const Skinny
     auto request_pass = [&](int pass) {
         const int c_begin = pass * p.pass_chunks;
         const int pc = min(p.pass_chunks, p.k_chunks - c_begin);
-        const int total = p.cols * pc;
-        for (int i = threadIdx.x; i < total; i += kSkThreads) {
-            const int n = i / pc, cc = i % pc;
+        // row by row, the whole CTA on one row at a time (4 KB contiguous per sweep streams better from
+        // DRAM than eight rows at once); no index division
+        for (int n = 0; n < p.cols; ++n) {
             const bool real = n0 + n < p.n_cols;
-            const __nv_bfloat16* src = p.w + (real ? static_cast<long long>(n0 + n) * p.k_chunks * 8 + (c_begin + cc) * 8 : 0);
-            cp_async_16(w_base + (n * p.pass_chunks + (cc ^ (n & 7))) * 16, src, real ? 16 : 0);
+            const __nv_bfloat16* src = p.w + (real ? (static_cast<long long>(n0 + n) * p.k_chunks + c_begin) * 8 : 0);
+            const uint32_t dst = w_base + n * p.pass_chunks * 16;
+            const int sw = n & 7;
+            for (int cc = threadIdx.x; cc < pc; cc += kSkThreads)
+                cp_async_16(dst + ((cc ^ sw) << 4), src + (real ? cc * 8 : 0), real ? 16 : 0);
         }
         cp_async_commit();
     };
