@@ -308,7 +308,7 @@ def projections_extra(dev, stream_ptr):
 
     ms = timed(all_qkv, 4) / len(qkv_ops)
     gbs = (qd + 2 * kd) * hidden * 2 / ms / 1e6
-    out["qkv_decode_step"] = {"kernel": "proj_skinny_kernel + qk_norm_rope_append_kernel", "rows": 1, "us": ms * 1e3,
+    out["qkv_decode_step"] = {"kernel": "proj_skinny_kernel (head norm, rotation and cache write inside)", "rows": 1, "us": ms * 1e3,
                               "weight_gbs": gbs, "frac_of_measured_hbm": gbs / peak}
     ms = timed(all_out, 4) / len(out_ops)
     gbs = hidden * qd * 2 / ms / 1e6
