@@ -301,3 +301,37 @@ def test_matmul3_decode_fusion_equals_two_kernels(one_matrix):
         assert np.array_equal(a, b)
     assert outs[0][0][0, :batch - 1].any() and not outs[0][0][0, batch - 1:].any()   # the dead slot stays untouched
     assert outs[0][3] == (1 if one_matrix else 3)
+
+
+def test_smallest_k_and_plain_state_buffers():
+    """One 64-wide k-block; and K / V landing in plain [rows x Nkv] state buffers like the reference's
+    k_state / v_state: the cache strides [Nkv, 128, max_batch * Nkv, 1] with position_index 0 express that."""
+    _matmul_add(61, interval=200, max_batch=1, batch=1, n=384, k=64, residual=True)
+    _matmul_add(62, interval=1, max_batch=3, batch=3, n=384, k=64, residual=True)
+    g = torch.Generator().manual_seed(63)
+    interval, mb, hq, hkv, hidden = 40, 2, 4, 2, 128
+    m, nkv = interval * mb, hkv * 128
+    x = torch.randn(m, hidden, generator=g).to(torch.bfloat16)
+    wq = (torch.randn(hq * 128, hidden, generator=g) * 0.05).to(torch.bfloat16)
+    wk = (torch.randn(nkv, hidden, generator=g) * 0.05).to(torch.bfloat16)
+    wv = (torch.randn(nkv, hidden, generator=g) * 0.05).to(torch.bfloat16)
+    rope = ellm_b200.precompute_freqs_cis(128, interval, 1e6)
+    k_state = torch.zeros(m, nkv, dtype=torch.bfloat16, device=DEV)
+    v_state = torch.zeros_like(k_state)
+    q = torch.zeros(interval, mb, hq, 128, dtype=torch.bfloat16, device=DEV)
+    op = MatMul3.new(x.to(DEV), wq.to(DEV), q, wk.to(DEV), k_state, wv.to(DEV), v_state, torch.from_numpy(rope).to(DEV), 128, m,
+                     hidden, hq * 128, nkv, kv_strides=[nkv, 128, mb * nkv, 1], max_batch=mb, max_seq=interval,
+                     rope_rows=interval)
+    op.run(0, interval, mb)
+    want_v = oracle.matmul_nt_bf16(bits(x), bits(wv))
+    _close(bits(v_state), want_v, 0.99, atol=2e-5 * np.sqrt(hidden))
+    # K rows: norm + rotation of the projected rows, row m = (chunk row r, sequence b) rotated at position r
+    pk = oracle.matmul_nt_bf16(bits(x), bits(wk)).reshape(interval, mb, hkv, 128)
+    pq = oracle.matmul_nt_bf16(bits(x), bits(wq)).reshape(interval, mb, hq, 128)
+    ck = np.zeros((m, nkv), np.uint16)
+    cv = np.zeros((m, nkv), np.uint16)
+    oracle.qk_norm_rope_append_bf16(pq, pk, want_v.reshape(interval, mb, hkv, 128), ck, cv, rope, [nkv, 128, mb * nkv, 1], hq, hkv,
+                                    0, interval, mb, 1e-6, max_batch=mb)
+    assert np.array_equal(cv, want_v)
+    _close_rotated(bits(k_state), ck)
+    op.close()
