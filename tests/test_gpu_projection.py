@@ -168,6 +168,13 @@ def test_matmul3_two_row_chunk_of_one_sequence():
              one_matrix=True)
 
 
+def test_matmul3_chunk_with_per_sequence_starts():
+    # a prompt chunk of three sequences that start at different positions (tensor-memory kernel, both forms)
+    for pairing in (0, 1):
+        _matmul3(18, interval=60, max_batch=3, batch=3, q_heads=4, kv_heads=2, hidden=192, max_seq=128,
+                 positions=[0, 17, 64], pairing=pairing)
+
+
 def test_matmul3_model_shape():
     # the benchmark stack's layer shape on a short chunk: 40 heads of columns, 32 k-blocks
     _matmul3(14, interval=384, max_batch=1, batch=1, q_heads=32, kv_heads=4, hidden=2048, max_seq=512,
