@@ -483,7 +483,9 @@ def main():
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": config_dict(lens),
         "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": ms_e2e, "entry": "ellm_attn_run_host"},
+                "ms_per_step": ms_e2e, "entry": "ellm_attn_run_host",
+                "transfer": "inside the timed call: one kernel fetches Q, new K/V rows and positions from the pinned host "
+                            "buffers over PCIe, the merge kernel stores O and LSE into the pinned host buffers; no copy nodes"},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "decode_splitkv_kernel", "achieved": achieved, "peak": peak,
