@@ -233,3 +233,27 @@ def test_run_host_replays_its_graph_with_new_contents():
         ph += 1
     assert np.array_equal(bits(dck), ref_k) and np.array_equal(bits(dcv), ref_v)
     assert op.kernel_stats()["decode_splitkv"][0] == 3
+
+
+@pytest.mark.parametrize("ctas", [1, 37, 148])
+def test_decode_grid_size_option(ctas):
+    """The decode kernel splits its tile list over any number of CTAs up to 2 x SMs (option
+    "decode_ctas"); the result does not depend on the split beyond the merge's rounding."""
+    import oracle
+    from helpers import O_MAX_ABS, LSE_MAX_ABS
+    dev = torch.device("cuda:0")
+    case = Case(seed=31, interval=1, batch=3, q_heads=8, kv_heads=2, max_seq=3000, positions=[2999, 65, 1500])
+    want_k, want_v, want_o, want_l = case.oracle()
+    q, ck, cv = case.q.to(dev), case.cache_k.to(dev), case.cache_v.to(dev)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(1, case.max_batch, case.q_heads, dtype=torch.float32, device=dev)
+    op = ellm_b200.Attention.new(q, ck, cv, out, case.max_batch, case.q_heads, case.kv_heads, 128, case.strides, case.scale,
+                                 max_seq=case.max_seq, lse=lse, k_new=case.k_new.to(dev), v_new=case.v_new.to(dev))
+    op.set_option("decode_ctas", ctas)
+    op.run_ragged(torch.from_numpy(case.positions).to(dev), 1, case.batch)
+    assert np.array_equal(bits(ck), want_k) and np.array_equal(bits(cv), want_v)
+    assert np.abs(out.float().cpu().numpy() - oracle.bf16_bits_to_f32(want_o))[:, :case.batch].max() <= O_MAX_ABS
+    assert np.abs(lse.cpu().numpy() - want_l)[:, :case.batch].max() <= LSE_MAX_ABS
+    with pytest.raises(ellm_b200.EllmError):
+        op.set_option("decode_ctas", 100000)
+    op.close()
