@@ -44,7 +44,7 @@ struct DecodeParams {
     const __nv_bfloat16* v_cache;
     float* part_o;                 // [slots, 16, 128]
     float* part_lse;               // [slots, 16]
-    int* prefix_out;               // [max_batch + 1]: block 0 publishes the tile prefix table for the merge
+    int* prefix_out;               // [max_batch + 1]: unused (the merge rebuilds the tile table from the positions); kept for the layout of the workspace
     const int32_t* positions;      // device int32[batch] or nullptr
     long long uniform_len;         // keys per sequence when positions == nullptr
     long long len_cap;             // no sequence is read past this many keys (cache rows / window end)
@@ -125,14 +125,13 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t warp_smem = smem_u32(smem) + warp * kDecStages * kDecWarpStageBytes;
 
-    // let a dependent grid (the merge) be set up while this one runs; under a programmatic
-    // dependent launch of this grid itself, wait here for the kernel before it (it wrote the
-    // positions, the queries and the newest cache row); a no-op for an ordinary launch
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // Under a programmatic dependent launch of this grid, wait here for the kernel before it (it
+    // wrote the positions, the queries and the newest cache row); a no-op for an ordinary launch.
+    // Only then let the dependent grid (the merge) be set up: whatever it does before its own wait
+    // - it rebuilds the tile table from the positions - then sees everything this grid sees.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     dec_build_prefix(p, prefix, lens);
-    if (blockIdx.x == 0)
-        for (int i = threadIdx.x; i <= p.batch; i += kDecThreads) p.prefix_out[i] = prefix[i];
     const long long segs_per_seq = static_cast<long long>(p.kv_heads) * p.gtiles;
     const long long total = static_cast<long long>(prefix[p.batch]) * segs_per_seq;
     long long t_begin, t_end;

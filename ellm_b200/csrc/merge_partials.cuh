@@ -40,23 +40,38 @@ template <typename OutT>
 __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const DecodeParams p, OutT* out, float* lse) {
     // a following kernel launched as a programmatic dependent may start its own prologue now
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // under a programmatic dependent launch: wait until the decode grid's writes are visible
-    // (a no-op for an ordinary launch)
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float s_l[kMergeMaxPieces];
     __shared__ float s_red[kMergeThreads / 32];
     __shared__ float4 s_acc[kMergeThreads / 32][32];
+    __shared__ int s_prefix[kDecMaxBatch + 1];
+    __shared__ int s_lens[kDecMaxBatch];
     constexpr int kWarps = kMergeThreads / 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // Where this row's pieces are follows from the positions alone, which are older than the decode
+    // grid (it lets this grid start only after its own wait): the tile table is rebuilt here, before
+    // the wait for the decode grid's results, instead of being read from it afterwards.
+    dec_build_prefix(p, s_prefix, s_lens);
     const long long row = blockIdx.x;
     const int b = static_cast<int>(row / p.q_heads), qh = static_cast<int>(row % p.q_heads);
     const int kvh = qh / p.group, g = qh % p.group, gt = g / 16, r = g % 16;
     const long long segs_per_seq = static_cast<long long>(p.kv_heads) * p.gtiles;
     const int seg_in_seq = kvh * p.gtiles + gt;
     const long long segment = b * segs_per_seq + seg_in_seq;
-    const int tiles_b = p.prefix_out[b + 1] - p.prefix_out[b];
-    const long long total = static_cast<long long>(p.prefix_out[p.batch]) * segs_per_seq;
+    const int tiles_b = s_prefix[b + 1] - s_prefix[b];
+    const long long total = static_cast<long long>(s_prefix[p.batch]) * segs_per_seq;
     OutT* orow = out + row * kHeadDim + lane * 4;
+    long long c_first = 0, c_last = -1;
+    if (tiles_b > 0) {
+        const long long t0 = static_cast<long long>(s_prefix[b]) * segs_per_seq + static_cast<long long>(seg_in_seq) * tiles_b;
+        c_first = cta_of_tile(total, p.num_ctas, t0);
+        c_last = cta_of_tile(total, p.num_ctas, t0 + tiles_b - 1);
+    }
+    const int pieces = static_cast<int>(c_last - c_first + 1);
+    const float* lse_base = p.part_lse + (c_first + segment) * 16 + r;            // piece i at + i * 16
+    const float* o_base = p.part_o + ((c_first + segment) * 16 + r) * kHeadDim + lane * 4;   // piece i at + i * 16 * 128
+    // under a programmatic dependent launch: wait until the decode grid's writes are visible
+    // (a no-op for an ordinary launch)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tiles_b == 0) {  // no key in range for this sequence
         if (warp == 0) {
             store_row4<OutT>(orow, make_float4(0.f, 0.f, 0.f, 0.f));
@@ -64,13 +79,6 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Decod
         }
         return;
     }
-    const long long t0 = static_cast<long long>(p.prefix_out[b]) * segs_per_seq +
-                         static_cast<long long>(seg_in_seq) * tiles_b;
-    const long long c_first = cta_of_tile(total, p.num_ctas, t0);
-    const long long c_last = cta_of_tile(total, p.num_ctas, t0 + tiles_b - 1);
-    const int pieces = static_cast<int>(c_last - c_first + 1);
-    const float* lse_base = p.part_lse + (c_first + segment) * 16 + r;            // piece i at + i * 16
-    const float* o_base = p.part_o + ((c_first + segment) * 16 + r) * kHeadDim + lane * 4;   // piece i at + i * 16 * 128
 
     // The pieces' rows do not depend on their weights, so a warp requests the rows of its first
     // kMergeAhead pieces before anything else: they travel while the log-sum-exps are fetched and
