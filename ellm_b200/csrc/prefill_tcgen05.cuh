@@ -46,6 +46,7 @@ constexpr int kTcSmemRing = kTcSmemQ + kTcTiles * kTcTileBytes;
 constexpr int kTcSmemBar = kTcSmemRing + kTcStages * kTcTileBytes;
 constexpr int kTcSmemBytes = kTcSmemBar + 256 + 1024;       // barriers + slack to align the base to 1024
 constexpr float kTcRescaleThreshold = 8.0f;                 // log2 units
+constexpr float kTcSumTrigger = 65536.0f;                   // a fast-path step whose row sum reaches this is redone with a rescale
 #ifndef ELLM_TC_SPLIT_P
 #define ELLM_TC_SPLIT_P 0   // hand the first 64 keys of P to the MMA issuer before the rest is computed
 #endif
@@ -394,17 +395,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const bool edge = key0 + kTcKeys - 1 > tile_min_lim;   // the causal edge crosses this tile
             const long long dlim = lim - key0;                     // last column this row may see
             const int rel = dlim < 0 ? -1 : (dlim > 127 ? 127 : static_cast<int>(dlim));
-            // Fast path (every step but the first, unless the row maximum jumps): exponentiate
-            // against the maximum already in use and track the new maximum in the same pass.  P is
-            // held in registers until the maximum is known to have moved by at most 2^8 - then it is
-            // consistent with O and l as they stand and goes to tensor memory as is.  Otherwise S_t is
-            // still intact and the two-pass slow path below redoes the step with a rescale of O_t.
+            // Fast path (every step but the first, unless a score leaps far above the maximum in use):
+            // exponentiate against the maximum already in use, in one pass.  P is held in registers
+            // until the step's row sum has shown that nothing leapt - then it is consistent with O
+            // and l as they stand and goes to tensor memory as is.  Otherwise S_t is still intact and
+            // the two-pass slow path below redoes the step with a rescale of O_t.
             bool slow = (j == 0) || edge;
             if (!slow) {
                 const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_used, -m_used);
                 uint64_t sum_a = pack2(0.0f, 0.0f), sum_b = sum_a;
                 uint32_t pk[64];
-                float mxa = -INFINITY, mxb = -INFINITY;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     float s[64];
@@ -414,7 +414,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                     for (int cc = 0; cc < 32; ++cc) {
                         const int c = half * 32 + cc;
-                        if (cc & 1) mxb = max3(mxb, s[2 * cc], s[2 * cc + 1]); else mxa = max3(mxa, s[2 * cc], s[2 * cc + 1]);
                         const uint64_t x2 = fma2(pack2(s[2 * cc], s[2 * cc + 1]), scale2, negm2);
                         uint64_t p2;
                         if (kTcPolyEvery > 0 && (c % kTcPolyEvery) == kTcPolyEvery - 1) {
@@ -430,12 +429,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         pk[c] = pack_bf16(p0, p1);
                     }
                 }
-                const float m_new = fmaxf(mxa, mxb) * p.scale_log2;
-                slow = __any_sync(0xffffffffu, m_new - m_used > kTcRescaleThreshold);
+                // No row maximum is tracked here.  A score far above the maximum in use shows up as a huge
+                // term of this step's sum (2^16 and more: one key 16 octaves above, or infinity); then the
+                // step is redone the slow way, which finds the true maximum and rescales.  Below that, P
+                // (bf16) and the fp32 accumulators take the larger terms as they are.
+                float sa, sb;
+                unpack2(add2(sum_a, sum_b), sa, sb);
+                const float step_sum = sa + sb;
+                slow = __any_sync(0xffffffffu, !(step_sum < kTcSumTrigger));
                 if (!slow) {
-                    float sa, sb;
-                    unpack2(add2(sum_a, sum_b), sa, sb);
-                    l += sa + sb;
+                    l += step_sum;
                     tmem_st32u(tS, pk);
                     tmem_st32u(tS + 32, pk + 32);
                     tmem_wait_st();

@@ -144,3 +144,19 @@ def test_device_wait_timeout_is_reported_and_the_context_stays_usable():
     assert_attention_close(case, bits(out), lse.cpu().numpy(), want_o, want_l)
     with pytest.raises(ellm_b200.EllmError):
         op.set_option("no_such_option", 1)
+
+
+@pytest.mark.parametrize("boost", [6.0, 40.0, 300.0])
+def test_scores_that_leap_above_the_running_maximum(boost):
+    """Keys whose scores lie far above everything before them (mildly: within the range the fast path
+    absorbs; strongly: tens of octaves, which must send the step down the rescaling path; and so far that
+    the exponentials overflow before the rescale) - deep inside the sequence, in the middle of a key tile
+    and at tile starts, so that steps after the first one meet them."""
+    case = Case(seed=61, interval=1536, batch=1, q_heads=4, kv_heads=1, max_seq=1536, position_index=0)
+    for key in (300, 301, 640, 1024, 1400):
+        case.k_new[key] = (case.k_new[key].float() * boost).to(torch.bfloat16)
+    want_k, want_v, want_o, want_l = case.oracle()
+    got_k, got_v, got_o, got_l = case.gpu(prefill_kernel=L.PREFILL_TCGEN05)
+    assert case.last_stats["prefill_tcgen05"][0] == 1
+    assert_cache_bit_exact(got_k, got_v, want_k, want_v)
+    assert_attention_close(case, got_o, got_l, want_o, want_l)
