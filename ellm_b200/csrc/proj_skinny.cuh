@@ -109,6 +109,9 @@ __global__ void __launch_bounds__(kSkThreads, 1) proj_skinny_kernel(const Skinny
         cp_async_commit();
     };
     request_pass(0);
+    // fused head epilogue: a CTA's shared memory may be written by its cluster peers only once it runs;
+    // every CTA says so here and checks the others just before the exchange
+    if (p.heads != 0) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     // the next kernel of the stream may start its own prologue now
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // activations (and the residual) are the previous kernels' output: wait for them
@@ -213,6 +216,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) proj_skinny_kernel(const Skinny
         if (head >= p.mat_q_heads + p.mat_k_heads) { kind = 2; head -= p.mat_q_heads + p.mat_k_heads; }
         else if (head >= p.mat_q_heads) { kind = 1; head -= p.mat_q_heads; }
         float x[4] = {0.f, 0.f, 0.f, 0.f};
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // every CTA of the head has started
         if (mine) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
