@@ -239,6 +239,8 @@ def test_invalid_arguments():
     with pytest.raises(ellm_b200.EllmError):   # more rows than the buffers hold
         op.run(0, 33, 4)
     op.run(0, 32, 4, cpu_num=8, thread_id=3)   # a worker that is not thread 0 launches nothing
+    op.run(0, 0, 4)                            # an empty chunk and an empty batch are no work, not errors
+    op.run(0, 1, 0)
     assert op.kernel_stats()[0] == 0
     op.close()
 
