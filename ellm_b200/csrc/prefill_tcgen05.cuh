@@ -54,6 +54,7 @@ constexpr float kTcSumTrigger = 65536.0f;                   // a fast-path step 
 #define ELLM_TC_POLY_EVERY 0
 #endif
 constexpr int kTcPolyEvery = ELLM_TC_POLY_EVERY;            // every n-th pair of a row uses the polynomial exp2 (0 = none)
+constexpr int kTcPolyDiv = kTcPolyEvery > 0 ? kTcPolyEvery : 1;   // the divisor the selection below may use
 
 struct Tcgen05Plan {
     bool ready = false;
@@ -358,7 +359,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int total_rows = p.interval * p.group;
     int steps[kTcTiles];
-#pragma unroll
     // where this sequence's chunk starts and where its keys end
     const long long base = p.positions ? static_cast<long long>(p.positions[b]) : p.base;
     const long long key_end = p.positions ? min(base + p.interval, p.max_seq) : p.key_end;
@@ -416,7 +416,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         const int c = half * 32 + cc;
                         const uint64_t x2 = fma2(pack2(s[2 * cc], s[2 * cc + 1]), scale2, negm2);
                         uint64_t p2;
-                        if (kTcPolyEvery > 0 && (c % kTcPolyEvery) == kTcPolyEvery - 1) {
+                        if (kTcPolyEvery > 0 && (c % kTcPolyDiv) == kTcPolyDiv - 1) {
                             p2 = exp2_poly2(x2);
                         } else {
                             float x0, x1;
@@ -525,7 +525,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                             const int c = half * 32 + cc;
                             const uint64_t x2 = fma2(pack2(s[2 * cc], s[2 * cc + 1]), scale2, negm2);
                             uint64_t p2;
-                            if (kTcPolyEvery > 0 && (c % kTcPolyEvery) == kTcPolyEvery - 1) {
+                            if (kTcPolyEvery > 0 && (c % kTcPolyDiv) == kTcPolyDiv - 1) {
                                 p2 = exp2_poly2(x2);
                             } else {
                                 float x0, x1;
