@@ -47,9 +47,6 @@ constexpr int kTcSmemBar = kTcSmemRing + kTcStages * kTcTileBytes;
 constexpr int kTcSmemBytes = kTcSmemBar + 256 + 1024;       // barriers + slack to align the base to 1024
 constexpr float kTcRescaleThreshold = 8.0f;                 // log2 units
 constexpr float kTcSumTrigger = 65536.0f;                   // a fast-path step whose row sum reaches this is redone with a rescale
-#ifndef ELLM_TC_SPLIT_P
-#define ELLM_TC_SPLIT_P 0   // hand the first 64 keys of P to the MMA issuer before the rest is computed
-#endif
 #ifndef ELLM_TC_POLY_EVERY
 #define ELLM_TC_POLY_EVERY 0
 #endif
@@ -305,9 +302,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     auto bar_s_full = [&](int t) { return bar0 + 8u * (2 + 2 * kTcStages + t); };
     auto bar_p_full = [&](int t) { return bar0 + 8u * (4 + 2 * kTcStages + t); };
     auto bar_pv_done = [&](int t) { return bar0 + 8u * (6 + 2 * kTcStages + t); };
-    auto bar_p_half = [&](int t) { return bar0 + 8u * (8 + 2 * kTcStages + t); };
-    const uint32_t bar_tail = bar0 + 8u * (10 + 2 * kTcStages);
-    constexpr int kNumBars = 11 + 2 * kTcStages;
+    const uint32_t bar_tail = bar0 + 8u * (8 + 2 * kTcStages);
+    constexpr int kNumBars = 9 + 2 * kTcStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kTcSmemBar + 8 * kNumBars);
     volatile int* abort_word = reinterpret_cast<volatile int*>(smem + kTcSmemBar + 8 * kNumBars + 8);
 
@@ -333,7 +329,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(bar_q(t), 1);
             mbar_init(bar_s_full(t), 1);
             mbar_init(bar_p_full(t), kTcTileRows / 32);   // one arrival per softmax warp
-            mbar_init(bar_p_half(t), kTcTileRows / 32);
             mbar_init(bar_pv_done(t), 1);
         }
         for (int s = 0; s < kTcStages; ++s) {
@@ -541,11 +536,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         tmem_wait_st();
                         tc_fence_before();
                         __syncwarp();
-#if ELLM_TC_SPLIT_P
-                        if (lane == 0) mbar_arrive(half == 0 ? bar_p_half(t) : bar_p_full(t));
-#else
                         if (half == 1 && lane == 0) mbar_arrive(bar_p_full(t));
-#endif
                     }
                     float sa, sb;
                     unpack2(add2(sum_a, sum_b), sa, sb);
@@ -684,11 +675,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 bool have_v = false, have_k = false;
                 for (int t = 0; t < kTcTiles && ok; ++t) {
                     if (j >= steps[t]) continue;
-#if ELLM_TC_SPLIT_P
-                    ok = mbar_wait(bar_p_half(t), j & 1, abort_word, p.status, kTcWaitPFull, p.wait_timeout_ns);
-#else
                     ok = mbar_wait(bar_p_full(t), j & 1, abort_word, p.status, kTcWaitPFull, p.wait_timeout_ns);
-#endif
                     if (!ok) break;
                     if (!have_v) {
                         ok = wait_item(item_v);
@@ -697,11 +684,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     }
                     tc_fence_after();
                     issue_pv_half(t, slot_v, j == 0, 0);
-#if ELLM_TC_SPLIT_P
-                    ok = mbar_wait(bar_p_full(t), j & 1, abort_word, p.status, kTcWaitPFull, p.wait_timeout_ns);
-                    if (!ok) break;
-                    tc_fence_after();
-#endif
                     issue_pv_half(t, slot_v, j == 0, 1);
                     if (j + 1 < steps[t]) {
                         if (!have_k) {
