@@ -35,19 +35,51 @@ struct StageIn {
     int n;
 };
 
+// The ranges form one flat list of 16-byte chunks; a thread requests all of its chunks (two per
+// round, normally one in all: the launch sizes the grid to the list) and its tail words before it
+// stores any of them, so a step pays one round trip over PCIe, not one per range.
 __global__ void __launch_bounds__(256) stage_in_kernel(const StageIn s) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const unsigned long long tid = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     const unsigned long long step = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
-    for (int i = 0; i < s.n; ++i) {
-        const unsigned long long chunks = s.bytes[i] / 16, words = (s.bytes[i] % 16) / 4;
-        const uint4* src = static_cast<const uint4*>(s.src[i]);
-        uint4* dst = static_cast<uint4*>(s.dst[i]);
-        for (unsigned long long c = tid; c < chunks; c += step) dst[c] = src[c];
-        if (tid < words)
-            static_cast<unsigned*>(s.dst[i])[chunks * 4 + tid] = static_cast<const unsigned*>(s.src[i])[chunks * 4 + tid];
+    unsigned long long first[5];
+    first[0] = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) first[k + 1] = first[k] + (k < s.n ? s.bytes[k] / 16 : 0);
+    auto locate = [&](unsigned long long f, const uint4*& src, uint4*& dst) {
+        src = static_cast<const uint4*>(s.src[0]) + f;
+        dst = static_cast<uint4*>(s.dst[0]) + f;
+#pragma unroll
+        for (int k = 1; k < 4; ++k)
+            if (k < s.n && f >= first[k]) {
+                src = static_cast<const uint4*>(s.src[k]) + (f - first[k]);
+                dst = static_cast<uint4*>(s.dst[k]) + (f - first[k]);
+            }
+    };
+    // tail words of ranges whose size is not a multiple of 16 bytes
+    unsigned tail[4];
+    bool has_tail[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        has_tail[k] = k < s.n && tid < (s.bytes[k] % 16) / 4;
+        if (has_tail[k]) tail[k] = static_cast<const unsigned*>(s.src[k])[(s.bytes[k] / 16) * 4 + tid];
     }
+    for (unsigned long long f = tid; f < first[4]; f += 2 * step) {
+        const uint4 *src_a, *src_b;
+        uint4 *dst_a, *dst_b;
+        locate(f, src_a, dst_a);
+        const bool two = f + step < first[4];
+        if (two) locate(f + step, src_b, dst_b);
+        const uint4 a = *src_a;
+        uint4 b = make_uint4(0u, 0u, 0u, 0u);
+        if (two) b = *src_b;
+        *dst_a = a;
+        if (two) *dst_b = b;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        if (has_tail[k]) static_cast<unsigned*>(s.dst[k])[(s.bytes[k] / 16) * 4 + tid] = tail[k];
 }
 
 }  // namespace ellm
@@ -567,7 +599,10 @@ int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
         add(h->d.q, dq, q_width);
         if (k_new_host) { add(h->d.k_new, dk, kv_width); add(h->d.v_new, dv, kv_width); }
         add(h->positions_dev, dp, batch_size * sizeof(int32_t));
-        ellm::stage_in_kernel<<<32, 256, 0, stream>>>(si);
+        unsigned long long stage_chunks = 0;
+        for (int i = 0; i < si.n; ++i) stage_chunks += si.bytes[i] / 16;
+        const unsigned stage_blocks = static_cast<unsigned>(std::min<unsigned long long>(std::max<unsigned long long>((stage_chunks + 255) / 256, 1), 1184));
+        ellm::stage_in_kernel<<<stage_blocks, 256, 0, stream>>>(si);
         ELLM_CUDA(cudaGetLastError());
         return run_impl(h, h->positions_dev, position_index, 1, batch_size, 0, INT64_MAX, nullptr,
                         lse_host ? static_cast<float*>(dlse) : h->d.lse, k_new_host != nullptr, /*enqueue_only=*/1, &stream, dout);
