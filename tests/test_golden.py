@@ -34,8 +34,8 @@ def test_oracle_reproduces_golden(name):
 @pytest.mark.parametrize("name", sorted(CASES))
 def test_gpu_matches_golden(name, kernel):
     case = Case(**CASES[name])
-    if kernel == 1 and (case.interval == 1 or case.positions is not None):
-        pytest.skip("the tcgen05 kernel serves uniform prefill chunks only")
+    if kernel != 0 and case.interval == 1:
+        pytest.skip("a decode step never reaches a prefill kernel; the choice of one changes nothing")
     gk, gv, go, gl = case.gpu(prefill_kernel=kernel)
     assert np.array_equal(_rows(gk, case), GOLD[name + "/k_rows"])   # bit-exact cache writes
     assert np.array_equal(_rows(gv, case), GOLD[name + "/v_rows"])
