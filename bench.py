@@ -12,9 +12,15 @@ and the appended rows.  Every step reads ~0.55 GB, far more than the 126 MB L2.
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 With N > 1 (under torchrun) every rank runs the same workload on its own 16
-sequences (independent sequences, no data-path collective): weak scaling.
-`--impl reference` times the CPU restatement of the reference's AVX-512-FP16
-attention kernel on all host cores instead (rank 0 only).
+sequences (independent sequences, no data-path collective): weak scaling of the
+headline `value`.  The two shardings of ONE problem ride along in `extra.sharded`
+at every N: the long causal prefill of BASELINE configs[2] split by KV-head group
+(no collective) and, the 1M-token prefill of configs[4] split into zig-zag
+sequence chunks with the NCCL exchange of (O, LSE) partials - strong scaling,
+each with a parity stamp: sampled query rows recomputed by the CPU oracle on
+rank 0, outside every timed region.  `--impl reference` times the CPU restatement
+of the reference's AVX-512-FP16 attention kernel on all host cores instead (rank 0
+only).
 """
 import argparse
 import json
@@ -76,7 +82,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -187,6 +193,8 @@ def run_reference(args, lens):
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample, **cpu_info()},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "reference_scope": "one workload (16 sequences) on rank 0's host cores at every N; the GPU arm's value at N ranks "
+                           "is the rate over N such workloads, so above N = 1 the ratio compares N GPUs with one host",
     }
     print(json.dumps(line))
 
@@ -335,11 +343,14 @@ def prefill_extra(dev, stream_ptr, steps, warmup):
     op = Attention.new(q, ck, cv, out, 1, H, H, D, [H * 4096 * D, 4096 * D, D, 1], SCALE, max_seq=4096,
                        max_interval=S, lse=lse, k_new=kn, v_new=vn, device=dev.index, stream=stream_ptr, async_=True)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    runs = 0
     for _ in range(max(3, warmup)):
         op.run(0, S, 1, 1, 0)
+        runs += 1
     torch.cuda.synchronize(dev)
     times = []
     for _ in range(max(5, min(steps, 20))):
+        runs += 1
         flush.zero_()  # write a buffer larger than L2 between timed iterations
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(); op.run(0, S, 1, 1, 0); e1.record()
@@ -350,8 +361,91 @@ def prefill_extra(dev, stream_ptr, steps, warmup):
     stats = op.kernel_stats()
     kernel = "prefill_tcgen05" if stats["prefill_tcgen05"][0] else "prefill_warp_mma"
     op.close()
+    burst, sustained, src = measured_tensor_peaks()
+    tf = flops / ms / 1e9
     return {"workload": "causal prefill, seq 2048, 32/32 heads (BASELINE configs[0]), KV append included, L2 flushed between iterations",
-            "ttft_ms": ms, "tflops": flops / ms / 1e9, "kernel": kernel}
+            "ttft_ms": ms, "tflops": tf, "kernel": kernel, "launches_per_step": sum(v[0] for v in stats.values()) // max(1, runs),
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": burst, "unit": "TFLOP/s", "frac": tf / burst,
+                         "frac_of_nominal_2250": tf / 2250.0, "flops": flops,
+                         "peak_source": src + " bf16_tflops (burst: the kernel is timed alone)"}}
+
+
+def parity_stamp(sample, what):
+    """Sampled query rows of a sharded run against the oracle's row kernel (the restatement of
+    src/kernel/generic/flash_attention.rs:60-89) over all their keys; rank 0, outside any timed
+    region.  `sample` comes from ellm_b200.multi_gpu (inputs and results of the rows)."""
+    from concurrent.futures import ThreadPoolExecutor
+    import oracle
+    if sample is None:
+        return None
+    k, v = np.ascontiguousarray(sample["k"]), np.ascontiguousarray(sample["v"])
+
+    def one(row):
+        o = np.zeros(D, np.float32)
+        want_l = oracle.flash_attention_f32(np.ascontiguousarray(row["q"], dtype=np.float32), k, v, o, float(SCALE), row["pos"])
+        d = np.abs(row["out"] - o)
+        return float(d.max()), float(d.mean()), abs(row["lse"] - want_l)
+
+    with ThreadPoolExecutor(min(16, os.cpu_count() or 1)) as pool:
+        res = list(pool.map(one, sample["rows"]))
+    mx, mean, lse = max(r[0] for r in res), float(np.mean([r[1] for r in res])), max(r[2] for r in res)
+    return {"rows": len(res), "max_abs": mx, "mean_abs": mean, "lse_max_abs": lse,
+            "tolerance": {"max_abs": 2e-2, "mean_abs": 2e-3, "lse_max_abs": 1e-3},
+            "ok": bool(mx <= 2e-2 and mean <= 2e-3 and lse <= 1e-3),
+            "positions": [min(r["pos"] for r in sample["rows"]), max(r["pos"] for r in sample["rows"])],
+            "checker": "CPU oracle row kernel (fp32 recurrence) over keys 0..=position, " + what}
+
+
+def sharded_extra(rank, world, dev):
+    """The two shardings of ONE problem (strong scaling), at this N."""
+    from ellm_b200 import multi_gpu
+    burst, sustained, src = measured_tensor_peaks()
+    out = {}
+    # (i) BASELINE configs[2]: seq 131072, 64 q / 8 kv heads, one KV-head group per GPU at N = 8
+    S, Hq, Hkv = 131072, 64, 8
+    n_rows = 64
+    rng = np.random.default_rng(11)
+    pos = [0, 1, 127, 128, 129, 255, 256, 4095, 4096, 65535, 65536, S - 129, S - 128, S - 2, S - 1]
+    pos += [int(x) for x in rng.integers(0, S, n_rows - len(pos))]
+    res, sample = multi_gpu.heads_prefill(S, Hq, Hkv, rank, world, dev, steps=2, warmup=1, seed=2, sample_positions=pos)
+    if rank == 0:
+        res["workload"] = ("BASELINE configs[2]: causal prefill, seq 131072, 64 q / 8 kv heads, KV-head groups sharded over the "
+                           "ranks, no collective; strong scaling (fixed problem)")
+        res["frac_of_n_x_sustained_peak"] = res["tflops"] / (min(world, Hkv) * sustained)
+        res["parity"] = parity_stamp(sample, "rows of rank 0's first KV head, seed 2")
+        out["head_groups"] = res
+    del sample
+    torch.cuda.empty_cache()
+    # (ii) BASELINE configs[4]: seq 1048576, 32 q / 4 kv heads, zig-zag sequence chunks + partial exchange
+    S, Hq, Hkv = 1048576, 32, 4
+    pos = multi_gpu.owned_sample_positions(S, world, 64)
+    res, sample = multi_gpu.seq_prefill(S, Hq, Hkv, rank, world, dev, steps=1, warmup=1 if world > 1 else 0, seed=4,
+                                        sample_positions=pos)
+    if rank == 0:
+        res["workload"] = ("BASELINE configs[4]: causal prefill, seq 1048576, 32 q / 4 kv heads, 2N zig-zag sequence chunks; "
+                           "Q all-gather + fp32 (O, LSE) partials over NCCL, merged by the owner; strong scaling"
+                           + ("" if world > 1 else " (one rank: both chunks local, the window + merge path without the exchange; no warm-up step)"))
+        res["frac_of_n_x_sustained_peak"] = res["tflops"] / (world * sustained)
+        res["parity"] = parity_stamp(sample, "rows inside the 65536-token prefix and in rank 0's last chunk, seed 4")
+        out["sequence_chunks"] = res
+    del sample
+    torch.cuda.empty_cache()
+    if rank == 0:
+        out["peaks"] = {"bf16_tflops_sustained": sustained, "bf16_tflops_burst": burst, "source": src}
+    return out
+
+
+def stack_extra(dev):
+    """BASELINE configs[3]: 48-layer attention-only stack, 32768-token prefill then 256 decode steps."""
+    from ellm_b200 import stack
+    res = stack.measure(device=f"cuda:{dev.index}")
+    burst, sustained, src = measured_tensor_peaks()
+    hbm, hsrc = measured_peaks()
+    res["prefill_frac_of_sustained_peak"] = res["prefill_tflops"] / sustained
+    res["prefill_frac_of_burst_peak"] = res["prefill_tflops"] / burst
+    res["decode_frac_of_measured_hbm"] = res["decode_gbs"] / hbm
+    res["peaks"] = {"bf16_tflops_sustained": sustained, "bf16_tflops_burst": burst, "hbm_gbs": hbm, "source": src}
+    return res
 
 
 def main():
@@ -362,6 +456,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
+    ap.add_argument("--no-sharded", action="store_true")
+    ap.add_argument("--min-seconds", type=float, default=1.5, help="the timed rounds together last at least this long")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     lens = workload_lens()
@@ -409,6 +505,7 @@ def main():
         torch.cuda.synchronize(dev)
 
     def timed(fn, n):
+        """n calls of fn between two events, a barrier and a synchronise on both sides; maximum over ranks."""
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
@@ -423,30 +520,40 @@ def main():
             ms = float(t.item())
         return ms
 
+    def timed_rounds(fn, n, min_seconds, min_rounds, max_rounds=1000):
+        """Rounds of exactly n steps each, until at least min_rounds rounds and min_seconds of timed work
+        (the same count on every rank: it is fixed from the first round's maximum over ranks)."""
+        first = timed(fn, n)
+        rounds = int(min(max_rounds, max(min_rounds, np.ceil(min_seconds * 1e3 / max(first, 1e-3)))))
+        return [first] + [timed(fn, n) for _ in range(rounds - 1)]
+
     for _ in range(args.warmup):
         step()
+    op.check()
     before = op.kernel_stats()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.25)
-    ms = timed(step, args.steps)
+        time.sleep(0.3)
+        warm_samples = len(sampler.rows)
+    rounds = timed_rounds(step, args.steps, args.min_seconds, 25)
+    if rank == 0:
+        time.sleep(0.06)
+        timed_samples = len(sampler.rows) - warm_samples
+        sampler.rows = sampler.rows[warm_samples:]     # only what was sampled while the timed rounds ran
     after = op.kernel_stats()
-    # keep the device under the same load a little longer so that the clock sampler sees it
-    t_end = time.time() + 1.0
-    while rank == 0 and time.time() < t_end and len(sampler.rows) < 5:
-        for _ in range(50):
-            step()
-        torch.cuda.synchronize(dev)
+    op.check()
     clocks = sampler.stop() if rank == 0 else None
     launches = sum(after[k][0] - before[k][0] for k in after) if rank == 0 else 0
-    ms_per_step = ms / args.steps
+    ms_per_step = statistics.median(rounds) / args.steps
     value = world * total_bytes / (ms_per_step * 1e-3) / 1e9
 
-    # dominant kernel alone: CUDA events around each split-KV decode launch
+    # dominant kernel alone: CUDA events around each split-KV decode launch (a separate pass: the
+    # events between the launches take away the overlap of a kernel's start with its predecessor's end)
     op.set_profiling(True)
     p0 = op.kernel_stats()["decode_splitkv"]
-    timed(step, args.steps)
+    for _ in range(5):
+        timed(step, args.steps)
     p1 = op.kernel_stats()["decode_splitkv"]
     op.set_profiling(False)
     k_ms = (p1[2] - p0[2]) / max(1, p1[1] - p0[1])
@@ -464,12 +571,21 @@ def main():
 
     for _ in range(args.warmup):
         step_host()
-    ms_e2e = timed(step_host, args.steps) / args.steps
+    rounds_e2e = timed_rounds(step_host, args.steps, 0.5, 10)
+    ms_e2e = statistics.median(rounds_e2e) / args.steps
     e2e = world * total_bytes / (ms_e2e * 1e-3) / 1e9
     h2d = qh.numel() * 2 + knh.numel() * 2 + vnh.numel() * 2 + ph.numel() * 4
     d2h = oh.numel() * 2 + lh.numel() * 4
     if not torch.isfinite(oh.float()).all():
         raise SystemExit("bench: non-finite attention output")
+    op.close()
+    del op, q, k_new, v_new, out, lse
+    cache.close()
+    torch.cuda.empty_cache()
+
+    extra = {}
+    if not args.no_extra and not args.no_sharded:
+        extra["sharded"] = sharded_extra(rank, world, dev)
 
     if rank != 0:
         if world > 1:
@@ -480,18 +596,25 @@ def main():
     line = {
         "metric": "decode attn HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "rounds": {"count": len(rounds), "steps_per_round": args.steps, "ms_per_step_median": ms_per_step,
+                   "ms_per_step_min": min(rounds) / args.steps, "ms_per_step_max": max(rounds) / args.steps,
+                   "timed_ms_total": sum(rounds),
+                   "how": "every round times exactly --steps steps between CUDA events with a barrier and a synchronise on "
+                          "both sides, maximum over ranks; ms_per_step is the median round"},
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": config_dict(lens),
         "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": ms_e2e, "entry": "ellm_attn_run_host",
+                "ms_per_step": ms_e2e, "rounds": len(rounds_e2e), "entry": "ellm_attn_run_host",
                 "transfer": "inside the timed call: one kernel fetches Q, new K/V rows and positions from the pinned host "
                             "buffers over PCIe, the merge kernel stores O and LSE into the pinned host buffers; no copy nodes"},
         "gpu_launches": launches,
-        "clocks": clocks,
+        "clocks": dict(clocks, sampled="during the timed rounds only, every 50 ms", samples_in_timed_rounds=timed_samples),
         "roofline": {"bound": "hbm", "kernel": "decode_splitkv_kernel", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                      "frac_of_nominal_8tbs": achieved / 8000.0, "kernel_ms": k_ms,
-                     "algorithmic_bytes_per_launch": kernel_bytes, "traffic": TRAFFIC_BYTES_PER_LAUNCH},
+                     "kernel_ms_source": "separate pass of 5 rounds with CUDA events around each launch of this kernel",
+                     "algorithmic_bytes_per_launch": kernel_bytes, "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+                     "traffic_source": TRAFFIC_SOURCE},
         "tpot_attn_ms": ms_per_step,
     }
     if world == 1 and not args.no_cpu_baseline:
@@ -499,18 +622,25 @@ def main():
         line["cpu_baseline"] = {"value": leg[0], "unit": "GB/s", "cores": leg[1], "kind": "port",
                                 "sample": leg[2], "ms_per_step": leg[3], **cpu_info()}
     if world == 1 and not args.no_extra:
-        line["extra"] = {"prefill": prefill_extra(dev, stream.cuda_stream, args.steps, args.warmup),
-                         "prefill_long": prefill_long(dev, stream.cuda_stream),
-                         "projections": projections_extra(dev, stream.cuda_stream)}
+        extra["prefill"] = prefill_extra(dev, stream.cuda_stream, args.steps, args.warmup)
+        extra["prefill_long"] = prefill_long(dev, stream.cuda_stream)
+        extra["projections"] = projections_extra(dev, stream.cuda_stream)
+        torch.cuda.empty_cache()
+        extra["stack"] = stack_extra(dev)
+    if extra:
+        line["extra"] = extra
     print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode_splitkv_kernel launch on this
-# workload, from the ncu capture summarised in profiles/decode_splitkv_bench_workload.md.
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_splitkv_kernel launch on this workload
+# (609.89 MB read + 4.09 MB written), from an `ncu --set full --clock-control none -k
+# regex:decode_splitkv -c 2` capture of `python bench.py --steps 2 --warmup 3 --no-cpu-baseline
+# --no-extra` on a B200.  A constant of that capture, not measured by this run.
 TRAFFIC_BYTES_PER_LAUNCH = 613.95e6
+TRAFFIC_SOURCE = "ncu capture of this workload (dram__bytes_read.sum + dram__bytes_write.sum, one launch); a recorded constant"
 
 if __name__ == "__main__":
     main()

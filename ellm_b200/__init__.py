@@ -8,7 +8,9 @@ calling them without libellm_attn.so and a B200 raises.
 from ._lib import (  # noqa: F401
     EllmError, PREFILL_AUTO, PREFILL_TCGEN05, PREFILL_WARP_MMA, header_symbols, load,
 )
-from .attention import Attention, decode_noalloc, kv_append, merge_partials, qk_norm_rope_append, rms_norm  # noqa: F401
+from .attention import (  # noqa: F401
+    Attention, decode_noalloc, kv_append, merge_partials, merge_partials_list, qk_norm_rope_append, rms_norm,
+)
 from .kv_cache import StaticKVCache  # noqa: F401
 from .projection import MatMul3, MatMulAdd  # noqa: F401
 from .rope import precompute_freqs_cis  # noqa: F401

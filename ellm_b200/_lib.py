@@ -67,12 +67,18 @@ _SIGNATURES = {
     "ellm_attn_run_host": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _SZ, _SZ, _SZ]),
     "ellm_device_alloc": (_I, [_I, _SZ, C.POINTER(_VP)]),
     "ellm_device_free": (_I, [_I, _VP]),
+    "ellm_kv_cache_create": (_I, [_I, _SZ, _SZ, _SZ, _SZ, _SZ, C.POINTER(_VP)]),
+    "ellm_kv_cache_destroy": (_I, [_VP]),
+    "ellm_kv_cache_layer": (_I, [_VP, _SZ, C.POINTER(_VP), C.POINTER(_VP), C.POINTER(_SZ)]),
     "ellm_kv_append": (_I, [_VP, _VP, C.POINTER(_SZ), _SZ, _SZ, _SZ, _SZ, _SZ, _VP, _SZ, _SZ, _I, _VP]),
     "ellm_qk_norm_rope_append": (_I, [_VP] * 9 + [_SZ, C.POINTER(_SZ)] + [_SZ] * 6 + [_VP, _SZ, _SZ, C.c_float, _SZ, _SZ, _I, _VP]),
     "ellm_rms_norm": (_I, [_VP, _VP, _SZ, _SZ, C.c_float, _I, _VP]),
     "ellm_attn_merge_partials": (_I, [_VP, _VP, _SZ, _SZ, _SZ, _VP, _VP, _I, _VP]),
     "ellm_attn_merge_partials_f32": (_I, [_VP, _VP, _SZ, _SZ, _SZ, _VP, _VP, _I, _VP]),
     "ellm_attn_run_window": (_I, [_VP, _SZ, _SZ, _SZ, _SZ, _SZ, _VP, _VP]),
+    "ellm_attn_run_window_q": (_I, [_VP, _VP, _SZ, _SZ, _SZ, _SZ, _SZ, _VP, _VP]),
+    "ellm_attn_merge_partials_list": (_I, [C.POINTER(_VP), C.POINTER(_VP), _SZ, _SZ, _SZ, _VP, _I, _VP, _I, _VP]),
+    "ellm_attn_check": (_I, [_VP]),
     "ellm_attn_decode_noalloc": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _SZ, _SZ, _SZ, _SZ, _SZ, C.POINTER(_SZ), _SZ, C.c_float, _I, _VP]),
     "ellm_attn_set_option": (_I, [_VP, C.c_char_p, C.c_longlong]),
     "ellm_attn_set_profiling": (_I, [_VP, _I]),

@@ -64,6 +64,18 @@ class Attention:
                                                batch_size, key_begin, key_end, _ptr(o_part),
                                                _ptr(lse_part)))
 
+    def run_window_q(self, q, position_index, position_interval, batch_size, key_begin, key_end,
+                     o_part, lse_part):
+        """run_window with the queries read from `q` (same shape as the bound q buffer)."""
+        L.check(self._lib.ellm_attn_run_window_q(self._h, _ptr(q), position_index, position_interval,
+                                                 batch_size, key_begin, key_end, _ptr(o_part),
+                                                 _ptr(lse_part)))
+
+    def check(self):
+        """Waits for the handle's stream; raises EllmError(ERR_DEVICE_TIMEOUT) if a bounded
+        device-side wait of a kernel enqueued since the last check ran out (async handles)."""
+        L.check(self._lib.ellm_attn_check(self._h))
+
     def run_host(self, q_host, out_host, position_index, position_interval, batch_size, *,
                  k_new_host=None, v_new_host=None, lse_host=None, positions_host=None):
         L.check(self._lib.ellm_attn_run_host(self._h, _ptr(q_host), _ptr(k_new_host),
@@ -112,6 +124,17 @@ def merge_partials(o_parts, lse_parts, out, lse_out=None, device=0, stream=None,
     parts, rows, d = o_parts.shape
     fn = L.load().ellm_attn_merge_partials_f32 if out_f32 else L.load().ellm_attn_merge_partials
     L.check(fn(_ptr(o_parts), _ptr(lse_parts), parts, rows, d, _ptr(out), _ptr(lse_out), device, stream))
+
+
+def merge_partials_list(o_parts, lse_parts, out, lse_out=None, device=0, stream=None, out_f32=False):
+    """Combine of parts held in separate buffers: o_parts a list of [rows, 128] fp32 tensors,
+    lse_parts the matching [rows] fp32 tensors (at most 16); out [rows, 128] bf16 or fp32."""
+    n = len(o_parts)
+    rows = o_parts[0].numel() // 128
+    po = (C.c_void_p * n)(*[_ptr(t) for t in o_parts])
+    pl = (C.c_void_p * n)(*[_ptr(t) for t in lse_parts])
+    L.check(L.load().ellm_attn_merge_partials_list(po, pl, n, rows, 128, _ptr(out), 1 if out_f32 else 0,
+                                                   _ptr(lse_out), device, stream))
 
 
 def decode_noalloc(q, k_cache, v_cache, out, batch_size, q_heads, kv_heads, head_size, kv_strides,

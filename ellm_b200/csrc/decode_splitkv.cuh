@@ -44,7 +44,6 @@ struct DecodeParams {
     const __nv_bfloat16* v_cache;
     float* part_o;                 // [slots, 16, 128]
     float* part_lse;               // [slots, 16]
-    int* prefix_out;               // [max_batch + 1]: unused (the merge rebuilds the tile table from the positions); kept for the layout of the workspace
     const int32_t* positions;      // device int32[batch] or nullptr
     long long uniform_len;         // keys per sequence when positions == nullptr
     long long len_cap;             // no sequence is read past this many keys (cache rows / window end)

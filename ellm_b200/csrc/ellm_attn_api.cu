@@ -150,7 +150,6 @@ struct ellm_attn {
     size_t slots = 0;
     float* part_o = nullptr;
     float* part_lse = nullptr;
-    int* prefix = nullptr;
     int32_t* positions_dev = nullptr;  // staging for ellm_attn_run_host
     int* status_dev = nullptr;         // bounded-wait status word written by the tcgen05 kernel
     int* status_host = nullptr;        // pinned mirror
@@ -268,7 +267,6 @@ int launch_decode(ellm_attn* h, const int32_t* positions, size_t position_index,
     p.v_cache = static_cast<const __nv_bfloat16*>(h->d.v_cache);
     p.part_o = h->part_o;
     p.part_lse = h->part_lse;
-    p.prefix_out = h->prefix;
     p.positions = positions;
     long long len = static_cast<long long>(position_index) + 1;
     if (len > key_end) len = key_end;
@@ -381,7 +379,7 @@ int finish(ellm_attn* h, bool enqueue_only) {
 int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size_t interval,
              size_t batch, long long key_begin, long long key_end, float* out_f32, float* lse_out,
              bool append, int enqueue_only = -1, const cudaStream_t* stream_override = nullptr,
-             void* decode_out_override = nullptr) {
+             void* decode_out_override = nullptr, const void* q_override = nullptr) {
     if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL");
     if (interval == 0 || batch == 0) return ELLM_OK;  // nothing to do, as an empty assign() range
     if (batch > h->d.max_batch) return fail(ELLM_ERR_INVALID_ARG, "batch_size %zu > max_batch %zu", batch, h->d.max_batch);
@@ -403,6 +401,14 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
         StreamSwap(ellm_attn* h_, const cudaStream_t* o) : h(h_), saved(h_->stream) { if (o) h->stream = *o; }
         ~StreamSwap() { h->stream = saved; }
     } swap(h, stream_override);
+    // a windowed call may read its queries from another buffer of the same shape (the gathered
+    // query chunks of a sharded sequence): the handle's q is put back before the lock is released
+    struct QuerySwap {
+        ellm_attn* h;
+        const void* saved;
+        QuerySwap(ellm_attn* h_, const void* q) : h(h_), saved(h_->d.q) { if (q) h->d.q = q; }
+        ~QuerySwap() { h->d.q = saved; }
+    } qswap(h, q_override);
     const bool no_sync = enqueue_only < 0 ? h->d.async != 0 : enqueue_only != 0;
     int rc;
     const bool do_append = append && h->d.k_new;
@@ -490,7 +496,6 @@ int ellm_attn_create(const ellm_attn_desc* desc, ellm_attn** out) {
     };
     if (cudaMalloc(&h->part_o, h->slots * 16 * ellm::kHeadDim * sizeof(float)) != cudaSuccess ||
         cudaMalloc(&h->part_lse, h->slots * 16 * sizeof(float)) != cudaSuccess ||
-        cudaMalloc(&h->prefix, (desc->max_batch + 1) * sizeof(int)) != cudaSuccess ||
         cudaMalloc(&h->positions_dev, desc->max_batch * sizeof(int32_t)) != cudaSuccess ||
         cudaMalloc(&h->status_dev, sizeof(int)) != cudaSuccess ||
         cudaMallocHost(&h->status_host, sizeof(int)) != cudaSuccess) {
@@ -525,7 +530,6 @@ int ellm_attn_destroy(ellm_attn* h) {
     if (h->graph_stream) cudaStreamDestroy(h->graph_stream);
     cudaFree(h->part_o);
     cudaFree(h->part_lse);
-    cudaFree(h->prefix);
     cudaFree(h->positions_dev);
     cudaFree(h->status_dev);
     if (h->status_host) cudaFreeHost(h->status_host);
@@ -556,6 +560,25 @@ int ellm_attn_run_window(ellm_attn* h, size_t position_index, size_t position_in
     if (!o_part || !lse_part) return fail(ELLM_ERR_INVALID_ARG, "o_part and lse_part must be non-NULL");
     return run_impl(h, nullptr, position_index, position_interval, batch_size, static_cast<long long>(key_begin),
                     static_cast<long long>(key_end > static_cast<size_t>(INT64_MAX) ? INT64_MAX : key_end), o_part, lse_part, false);
+}
+
+int ellm_attn_run_window_q(ellm_attn* h, const void* q, size_t position_index, size_t position_interval,
+                           size_t batch_size, size_t key_begin, size_t key_end, float* o_part, float* lse_part) {
+    if (!o_part || !lse_part) return fail(ELLM_ERR_INVALID_ARG, "o_part and lse_part must be non-NULL");
+    if (q && !aligned16(q)) return fail(ELLM_ERR_INVALID_ARG, "q must be 16-byte aligned");
+    return run_impl(h, nullptr, position_index, position_interval, batch_size, static_cast<long long>(key_begin),
+                    static_cast<long long>(key_end > static_cast<size_t>(INT64_MAX) ? INT64_MAX : key_end), o_part, lse_part, false,
+                    -1, nullptr, nullptr, q);
+}
+
+int ellm_attn_check(ellm_attn* h) {
+    if (!h) return fail(ELLM_ERR_INVALID_ARG, "handle is NULL");
+    DeviceGuard guard(h->d.device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", h->d.device);
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->status_dev)
+        ELLM_CUDA(cudaMemcpyAsync(h->status_host, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
+    return finish(h, false);
 }
 
 int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host, const void* v_new_host,
@@ -741,6 +764,62 @@ int ellm_device_free(int device, void* ptr) {
     return ELLM_OK;
 }
 
+// The static KV cache as an object of the library: one zero-filled allocation for K and one for V,
+// [layer, sequence, kv_head, position, head_size], never resized.
+struct ellm_kv_cache {
+    int device = 0;
+    size_t layers = 0, max_batch = 0, kv_heads = 0, max_seq = 0, head_size = 0;
+    size_t layer_elems = 0;
+    void* k = nullptr;
+    void* v = nullptr;
+};
+
+int ellm_kv_cache_create(int device, size_t layers, size_t max_batch, size_t kv_heads, size_t max_seq,
+                         size_t head_size, ellm_kv_cache** out) {
+    if (!out) return fail(ELLM_ERR_INVALID_ARG, "out is NULL");
+    *out = nullptr;
+    if (layers == 0 || max_batch == 0 || kv_heads == 0 || max_seq == 0)
+        return fail(ELLM_ERR_INVALID_ARG, "layers, max_batch, kv_heads and max_seq must be > 0");
+    if (head_size != static_cast<size_t>(ellm::kHeadDim)) return fail(ELLM_ERR_UNSUPPORTED, "head_size %zu: only 128", head_size);
+    ellm_kv_cache* c = new (std::nothrow) ellm_kv_cache();
+    if (!c) return fail(ELLM_ERR_NO_MEMORY, "host allocation failed");
+    c->device = device;
+    c->layers = layers; c->max_batch = max_batch; c->kv_heads = kv_heads; c->max_seq = max_seq; c->head_size = head_size;
+    c->layer_elems = max_batch * kv_heads * max_seq * head_size;
+    const size_t bytes = layers * c->layer_elems * 2;
+    int rc = ellm_device_alloc(device, bytes, &c->k);
+    if (rc == ELLM_OK) rc = ellm_device_alloc(device, bytes, &c->v);
+    if (rc != ELLM_OK) {
+        ellm_device_free(device, c->k);
+        delete c;
+        return rc;
+    }
+    *out = c;
+    return ELLM_OK;
+}
+
+int ellm_kv_cache_destroy(ellm_kv_cache* c) {
+    if (!c) return ELLM_OK;
+    ellm_device_free(c->device, c->k);
+    ellm_device_free(c->device, c->v);
+    delete c;
+    return ELLM_OK;
+}
+
+int ellm_kv_cache_layer(const ellm_kv_cache* c, size_t layer, void** k, void** v, size_t kv_strides[4]) {
+    if (!c) return fail(ELLM_ERR_INVALID_ARG, "cache is NULL");
+    if (layer >= c->layers) return fail(ELLM_ERR_INVALID_ARG, "layer %zu outside [0, %zu)", layer, c->layers);
+    if (k) *k = static_cast<unsigned char*>(c->k) + layer * c->layer_elems * 2;
+    if (v) *v = static_cast<unsigned char*>(c->v) + layer * c->layer_elems * 2;
+    if (kv_strides) {
+        kv_strides[0] = c->kv_heads * c->max_seq * c->head_size;
+        kv_strides[1] = c->max_seq * c->head_size;
+        kv_strides[2] = c->head_size;
+        kv_strides[3] = 1;
+    }
+    return ELLM_OK;
+}
+
 int ellm_kv_append(void* cache, const void* src, const size_t kv_strides[4], size_t max_batch,
                    size_t kv_heads, size_t head_size, size_t max_seq, size_t position_index,
                    const int32_t* positions, size_t position_interval, size_t batch_size, int device,
@@ -864,6 +943,37 @@ int ellm_attn_merge_partials_f32(const float* o_parts, const float* lse_parts, s
     return merge_partials_impl(o_parts, lse_parts, parts, rows, head_size, out, true, lse_out, device, stream);
 }
 
+int ellm_attn_merge_partials_list(const float* const* o_parts, const float* const* lse_parts, size_t parts,
+                                  size_t rows, size_t head_size, void* out, int out_is_f32, float* lse_out,
+                                  int device, void* stream) {
+    if (!o_parts || !lse_parts || !out) return fail(ELLM_ERR_INVALID_ARG, "o_parts, lse_parts and out must be non-NULL");
+    if (head_size != static_cast<size_t>(ellm::kHeadDim)) return fail(ELLM_ERR_UNSUPPORTED, "head_size %zu: only 128", head_size);
+    if (parts == 0 || parts > static_cast<size_t>(ellm::kMergeListMax))
+        return fail(ELLM_ERR_INVALID_ARG, "parts %zu outside [1, %d]", parts, ellm::kMergeListMax);
+    if (!aligned16(out)) return fail(ELLM_ERR_INVALID_ARG, "out must be 16-byte aligned");
+    ellm::MergeList m{};
+    m.parts = static_cast<int>(parts);
+    for (size_t i = 0; i < parts; ++i) {
+        if (!o_parts[i] || !lse_parts[i]) return fail(ELLM_ERR_INVALID_ARG, "part %zu is NULL", i);
+        if (!aligned16(o_parts[i])) return fail(ELLM_ERR_INVALID_ARG, "part %zu must be 16-byte aligned", i);
+        m.o[i] = o_parts[i];
+        m.lse[i] = lse_parts[i];
+    }
+    if (rows == 0) return ELLM_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    const unsigned long long blocks = (rows + 3) / 4;
+    if (blocks > 0x7fffffffull) return fail(ELLM_ERR_UNSUPPORTED, "too many rows for one launch");
+    if (out_is_f32)
+        ellm::merge_partials_list_kernel<float><<<static_cast<unsigned>(blocks), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+            m, static_cast<long long>(rows), static_cast<float*>(out), lse_out);
+    else
+        ellm::merge_partials_list_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+            m, static_cast<long long>(rows), static_cast<__nv_bfloat16*>(out), lse_out);
+    ELLM_CUDA(cudaGetLastError());
+    return ELLM_OK;
+}
+
 int ellm_attn_set_option(ellm_attn* h, const char* name, long long value) {
     if (!h || !name) return fail(ELLM_ERR_INVALID_ARG, "handle and name must be non-NULL");
     std::lock_guard<std::mutex> lock(h->mu);
@@ -932,8 +1042,7 @@ namespace {
 
 constexpr size_t kNoAllocPartOBytes = static_cast<size_t>(ELLM_NOALLOC_MAX_SLOTS) * 16 * ellm::kHeadDim * sizeof(float);
 constexpr size_t kNoAllocPartLseBytes = static_cast<size_t>(ELLM_NOALLOC_MAX_SLOTS) * 16 * sizeof(float);
-constexpr size_t kNoAllocPrefixBytes = ((static_cast<size_t>(ELLM_NOALLOC_MAX_BATCH) + 1) * sizeof(int) + 255) / 256 * 256;
-constexpr size_t kNoAllocBytes = kNoAllocPartOBytes + kNoAllocPartLseBytes + kNoAllocPrefixBytes;
+constexpr size_t kNoAllocBytes = kNoAllocPartOBytes + kNoAllocPartLseBytes;
 static_assert(ELLM_NOALLOC_MAX_BATCH <= ellm::kDecMaxBatch, "the decode kernel's prefix table bounds the batch");
 
 // In host code this name is only a stand-in for the symbol, never a device address:
@@ -955,7 +1064,15 @@ int noalloc_setup(int device, NoAllocDevice** out) {
     NoAllocDevice& nd = g_noalloc_dev[device];
     if (!nd.ready) {
         void* ptr = nullptr;
-        ELLM_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        // The look-up can be what loads this library's device image, and with it the array: if
+        // another allocator already holds the GPU's memory, this is where that shows.
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e == cudaErrorMemoryAllocation) {
+            cudaGetLastError();
+            return fail(ELLM_ERR_NO_MEMORY, "no device memory left for the library image and its %zu-byte scratch array on device %d; "
+                        "make the first call on a device before another allocator takes its memory", kNoAllocBytes, device);
+        }
+        ELLM_CUDA(e);
         if (!ptr) return fail(ELLM_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
         ELLM_CUDA(cudaDeviceGetAttribute(&nd.sm_count, cudaDevAttrMultiProcessorCount, device));
         int major = 0;
@@ -987,6 +1104,7 @@ extern "C" int ellm_attn_decode_noalloc(const void* q, const void* k_cache, cons
             return fail(ELLM_ERR_INVALID_ARG, "kv_strides[%d] must be a non-zero multiple of 8 elements", i);
     if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out))
         return fail(ELLM_ERR_INVALID_ARG, "device buffers must be 16-byte aligned");
+    if (lse && (reinterpret_cast<uintptr_t>(lse) & 3u)) return fail(ELLM_ERR_INVALID_ARG, "lse misaligned");
     if (!(scale > 0.0f) || !std::isfinite(scale)) return fail(ELLM_ERR_INVALID_ARG, "scale must be finite and > 0");
     if (max_seq == 0) return fail(ELLM_ERR_INVALID_ARG, "max_seq must be > 0");
     if (!positions && position_index + 1 > max_seq)
@@ -1015,7 +1133,6 @@ extern "C" int ellm_attn_decode_noalloc(const void* q, const void* k_cache, cons
     p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
     p.part_o = reinterpret_cast<float*>(nd->scratch);
     p.part_lse = reinterpret_cast<float*>(nd->scratch + kNoAllocPartOBytes);
-    p.prefix_out = reinterpret_cast<int*>(nd->scratch + kNoAllocPartOBytes + kNoAllocPartLseBytes);
     p.positions = positions;
     p.uniform_len = static_cast<long long>(position_index) + 1;
     p.len_cap = static_cast<long long>(max_seq);

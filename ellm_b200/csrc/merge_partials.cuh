@@ -181,4 +181,49 @@ __global__ void __launch_bounds__(128) merge_partials_kernel(const float* __rest
     if (lse && lane == 0) lse[row] = mmax + logf(wsum);
 }
 
+// The same combine over parts that live in separate buffers (each [rows, 128] fp32 with its
+// [rows] log-sum-exps): the partials of a sharded sequence as they were computed or received,
+// combined where they lie instead of being gathered into one array first.
+constexpr int kMergeListMax = 16;
+struct MergeList {
+    const float* o[kMergeListMax];
+    const float* lse[kMergeListMax];
+    int parts;
+};
+
+template <typename OutT>
+__global__ void __launch_bounds__(128) merge_partials_list_kernel(const MergeList m, long long rows, OutT* out, float* lse) {
+    const int lane = threadIdx.x & 31;
+    const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    float l[kMergeListMax];
+    float mmax = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kMergeListMax; ++i) {
+        l[i] = i < m.parts ? m.lse[i][row] : -INFINITY;
+        mmax = fmaxf(mmax, l[i]);
+    }
+    OutT* orow = out + row * kHeadDim + lane * 4;
+    if (mmax == -INFINITY) {
+        store_row4<OutT>(orow, make_float4(0.f, 0.f, 0.f, 0.f));
+        if (lse && lane == 0) lse[row] = -INFINITY;
+        return;
+    }
+    float wsum = 0.0f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < kMergeListMax; ++i) {
+        if (i < m.parts && l[i] != -INFINITY) {
+            const float w = expf(l[i] - mmax);
+            const float4 x = *reinterpret_cast<const float4*>(m.o[i] + row * kHeadDim + lane * 4);
+            wsum += w;
+            acc.x += w * x.x; acc.y += w * x.y; acc.z += w * x.z; acc.w += w * x.w;
+        }
+    }
+    const float inv = 1.0f / wsum;
+    acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+    store_row4<OutT>(orow, acc);
+    if (lse && lane == 0) lse[row] = mmax + logf(wsum);
+}
+
 }  // namespace ellm

@@ -62,6 +62,7 @@ struct Tcgen05Plan {
     CUtensorMap map_q, map_k, map_v;
     size_t cached_interval = 0, cached_batch = 0;
     long long cached_kv_rows = -1;
+    const void* cached_q = nullptr;
     unsigned long long wait_timeout_ns = 2000000000ull;   // ellm_attn_set_option("tc_wait_timeout_ns")
     int debug_skip_item = -1;                              // ellm_attn_set_option("tc_debug_skip_kv_item")
 };
@@ -776,7 +777,8 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
     CUtensorMap& map_k = plan.map_k;
     CUtensorMap& map_v = plan.map_v;
     // the buffers, head counts and strides are fixed for the handle: the maps depend only on these
-    const bool reuse = plan.cached_kv_rows == kv_rows && plan.cached_interval == interval && plan.cached_batch == batch;
+    const bool reuse = plan.cached_kv_rows == kv_rows && plan.cached_interval == interval && plan.cached_batch == batch &&
+                       plan.cached_q == d.q;
     plan.cached_kv_rows = -1;
     if (!reuse) {
         // q viewed as [head_dim, g, chunk row, kv head, sequence]; a box is 64 x G x (128/G) packed rows
@@ -806,6 +808,7 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
     plan.cached_kv_rows = kv_rows;
     plan.cached_interval = interval;
     plan.cached_batch = batch;
+    plan.cached_q = d.q;
     TcParams p;
     p.out = out_f32 ? static_cast<void*>(out_f32) : d.out;
     p.key_end = kv_rows;

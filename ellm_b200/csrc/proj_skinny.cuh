@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) proj_skinny_kernel(const Skinny
             const long long pos = (p.positions ? static_cast<long long>(p.positions[b]) : p.position_index) + m / p.max_batch;
             const int ch = (n0 & 127) + quad * 4;   // channel of x[0] inside the head
             if (kind == 2) {
-                if (pos >= 0 && pos < p.max_seq) {
+                if (pos >= 0 && pos < p.max_seq && pos < p.rope_rows) {   // as K: no rotation row, no cache write
                     uint2 v;
                     v.x = pack_bf16(x[0], x[1]);
                     v.y = pack_bf16(x[2], x[3]);

@@ -156,7 +156,7 @@ __device__ __forceinline__ void proj_head_epilogue(const ProjParams& p, uint32_t
     __syncwarp();
     bool store = live;
     if (kind != 0 && (pos < 0 || pos >= p.max_seq)) store = false;
-    if (kind != 2 && (pos < 0 || pos >= p.rope_rows)) store = false;   // no rotation row: leave the output untouched
+    if (pos < 0 || pos >= p.rope_rows) store = false;   // no rotation row: leave Q and the token's whole cache line (K and V) untouched
     __nv_bfloat16* dst = kind == 0 ? p.q_out + (m * p.q_heads + head) * kHeadDim
                                    : (kind == 1 ? p.k_cache : p.v_cache) + b * p.s0 + head * p.s1 + pos * p.s2;
     if (kind == 2) {   // V: the projected row as it is

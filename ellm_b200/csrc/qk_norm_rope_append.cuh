@@ -52,7 +52,9 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(const NormRope
 
     if (head >= p.q_heads + p.kv_heads) {  // V: plain row copy into the cache
         const int kvh = head - p.q_heads - p.kv_heads;
-        if (pos < 0 || pos >= p.max_seq) return;
+        // a position without a rotation row leaves the token's whole cache line untouched (its K row
+        // is skipped below for the same reason), never a new V beside a stale K
+        if (pos < 0 || pos >= p.max_seq || pos >= p.rope_rows) return;
         const uint2 v = *reinterpret_cast<const uint2*>(p.v_in + row * p.kv_in_stride + kvh * kHeadDim + lane * 4);
         *reinterpret_cast<uint2*>(p.v_cache + b * p.s0 + kvh * p.s1 + pos * p.s2 + lane * 4) = v;
         return;

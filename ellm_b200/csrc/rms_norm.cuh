@@ -46,7 +46,7 @@ __device__ __forceinline__ uint4 scale_piece(uint4 v, float rrms) {
     return o;
 }
 
-__global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+__global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* x, __nv_bfloat16* y,   // x and y may be the same buffer: no __restrict__
                                                        long long rows, int length, float eps) {
     __shared__ float warp_sums[8];
     __shared__ float s_rrms;

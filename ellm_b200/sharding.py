@@ -86,7 +86,31 @@ class SequenceChunkPlan:
         return sorted({self.owner(k) for k in range(q_chunk + 1)})
 
 
-def sequence_chunk_attention(plan, rank, q_chunks, compute_partial, merge, dist=None, empty_like=None):
+def local_partials(plan, rank, compute_partial, merge):
+    """Step 1 of the sharded prefill on `rank`: the partial of every (query chunk i, key chunk k)
+    pair it computes, pre-merged per query chunk.  Returns {i: (o, lse)}."""
+    local = {}
+    for i, k in plan.pairs_of(rank):
+        local.setdefault(i, []).append(compute_partial(i, k))
+    return {i: (parts[0] if len(parts) == 1 else merge(parts)) for i, parts in local.items()}
+
+
+def final_merge(plan, rank, local, received, merge):
+    """Step 3: the owner combines its own partial of each owned query chunk with the ones it
+    received ({i: [(o, lse), ...]}).  Returns {owned chunk index: (o, lse)}."""
+    result = {}
+    for i in plan.chunks_of(rank):
+        parts = ([local[i]] if i in local else []) + list(received.get(i, []))
+        result[i] = parts[0] if len(parts) == 1 else merge(parts)
+    return result
+
+
+class ExchangeTimeout(RuntimeError):
+    """A peer did not deliver (or take) a partial within the bound: it has left or is stuck."""
+
+
+def sequence_chunk_attention(plan, rank, q_chunks, compute_partial, merge, dist=None, empty_like=None, mark=None,
+                             timeout_s=None):
     """Runs the sequence-chunk sharded prefill for `rank`.
 
     q_chunks: {chunk index: Q rows of that chunk} for EVERY chunk (the caller all-gathers Q
@@ -95,18 +119,22 @@ def sequence_chunk_attention(plan, rank, q_chunks, compute_partial, merge, dist=
       (k owned by this rank); k == i is causal inside the chunk, k < i sees the whole chunk.
     merge(list of (o, lse)) -> (o, lse): log-sum-exp combine (fp32 in, fp32 out).
     dist: torch.distributed (or None for world 1).  empty_like(o) allocates a receive buffer.
+    mark(name): optional, called after the local chunk pairs ("local_done") and after the
+      exchange ("exchanged") so that a caller can time the phases.
+    timeout_s: bound of every wait of the exchange step.  A peer that left before its sends
+      would otherwise block this rank for the process group's own timeout (minutes); with a bound
+      the wait raises ExchangeTimeout and the caller can rebuild the group without that rank.
+      None = wait as the backend does (on NCCL a wait only orders the stream).
     Returns {owned chunk index: (o, lse)} merged over all key chunks.
     """
-    # 1. local partials, pre-merged per query chunk
-    local = {}
-    for i, k in plan.pairs_of(rank):
-        local.setdefault(i, []).append(compute_partial(i, k))
-    local = {i: (parts[0] if len(parts) == 1 else merge(parts)) for i, parts in local.items()}
+    mark = mark or (lambda name: None)
+    local = local_partials(plan, rank, compute_partial, merge)
+    mark("local_done")
 
-    # 2. one exchange step: every partial goes to the owner of its query chunk
+    # one exchange step: every partial goes to the owner of its query chunk
     mine = plan.chunks_of(rank)
     received = {i: [] for i in mine}
-    ops, keep = [], []
+    ops = []
     if plan.world > 1:
         for i in range(plan.n_chunks):
             dst = plan.owner(i)
@@ -123,17 +151,23 @@ def sequence_chunk_attention(plan, rank, q_chunks, compute_partial, merge, dist=
                     ops.append(dist.P2POp(dist.irecv, o, src))
                     ops.append(dist.P2POp(dist.irecv, lse, src))
                     received[i].append((o, lse))
-                    keep.append((o, lse))
         if ops:
-            for req in dist.batch_isend_irecv(ops):
-                req.wait()
-
-    # 3. the owner combines its own partial with the received ones
-    result = {}
-    for i in mine:
-        parts = ([local[i]] if i in local else []) + received[i]
-        result[i] = parts[0] if len(parts) == 1 else merge(parts)
-    return result
+            reqs = dist.batch_isend_irecv(ops)
+            if timeout_s is None:
+                for req in reqs:
+                    req.wait()
+            else:
+                import datetime
+                bound = datetime.timedelta(seconds=timeout_s)
+                for req in reqs:
+                    try:
+                        done = req.wait(bound)
+                    except RuntimeError as e:   # the backend's own text for a wait that ran out or a closed peer
+                        raise ExchangeTimeout(f"rank {rank}: exchange of partials failed: {e}") from e
+                    if done is False:
+                        raise ExchangeTimeout(f"rank {rank}: a partial did not arrive within {timeout_s} s")
+    mark("exchanged")
+    return final_merge(plan, rank, local, received, merge)
 
 
 def sequence_chunk_attention_p2p(plan, rank, compute_partial_into, merge_into, inbox_of, barrier, finish):

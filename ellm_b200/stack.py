@@ -152,16 +152,86 @@ class AttentionStack:
             self.positions.add_(1)
         return graph, out
 
+    def check(self):
+        """Waits for the stream and raises if a bounded device-side wait of any operator's kernels
+        ran out since the last check (the operators only enqueue)."""
+        for op in self.ops + self.qkv_ops + self.out_ops:
+            op.check()
+
     def close(self):
         for op in self.ops + self.qkv_ops + self.out_ops:
             op.close()
+        self.cache.close()
+
+
+def measure(layers=48, hidden=2048, q_heads=32, kv_heads=4, prefill=32768, decode=256, graph=True,
+            projections="tcgen05", device="cuda:0"):
+    """TTFT / TPOT of the attention path on the attention-only stack (BASELINE configs[3] by
+    default): one timed prefill pass of `prefill` tokens over all layers after a warm-up pass, then
+    `decode` single-token steps (a CUDA graph replayed per step unless graph=False).  Returns a dict."""
+    dev = torch.device(device)
+    torch.cuda.set_device(dev)
+    stream = torch.cuda.Stream(dev)
+    S = prefill
+    max_seq = S + decode + 8
+    stack = AttentionStack(layers, hidden, q_heads, kv_heads, max_seq, S, stream=stream, projections=projections,
+                           device=device)
+    g = torch.Generator(device=dev).manual_seed(3)
+    x0 = torch.randn(S, 1, hidden, device=dev, generator=g).to(torch.bfloat16)
+    with torch.cuda.stream(stream):
+        stack.forward(x0, 0)            # warm-up pass (also fills the cache)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        y = stack.forward(x0, 0)
+        e1.record(stream)
+    stream.synchronize()
+    stack.check()
+    ttft = e0.elapsed_time(e1)
+    flops_attn = 4 * 128 * q_heads * S * (S + 1) / 2 * layers
+    flops_proj = 2 * S * hidden * (q_heads * 128 * 2 + kv_heads * 128 * 2) * layers
+    # decode: positions start at S; the graph advances them
+    x1 = y[-1:].clone()
+    stack.positions.fill_(S)
+    times = []
+    with torch.cuda.stream(stream):
+        if not graph:
+            for _ in range(decode):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                x1 = stack.forward(x1, 0, ragged=True)
+                stack.positions.add_(1)
+                e1.record(stream)
+                stream.synchronize()
+                times.append(e0.elapsed_time(e1))
+        else:
+            cuda_graph, out = stack.capture_decode_step(x1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(decode):
+                cuda_graph.replay()
+                x1.copy_(out)
+            e1.record(stream)
+            stream.synchronize()
+            times = [e0.elapsed_time(e1) / decode]
+    stack.check()
+    tpot = float(np.mean(times))
+    kv_bytes = 2 * kv_heads * 128 * 2 * (S + decode / 2) * layers
+    w_bytes = 2 * hidden * (q_heads * 128 * 2 + kv_heads * 128 * 2) * layers
+    res = {
+        "workload": f"{layers}-layer attention-only stack, hidden {hidden}, {q_heads} q / {kv_heads} kv heads, "
+                    f"prefill {S} then {decode} decode steps, 1 sequence, synthetic weights and activations",
+        "ttft_ms": ttft, "prefill_tflops": (flops_attn + flops_proj) / ttft / 1e9,
+        "prefill_attention_flops_share": flops_attn / (flops_attn + flops_proj),
+        "prefill_projections": projections, "tpot_ms": tpot, "decode_gbs": (kv_bytes + w_bytes) / tpot / 1e6,
+        "decode_bytes_per_step": kv_bytes + w_bytes, "decode_cuda_graph": graph,
+        "launches_per_decode_step": 4 * layers if projections == "tcgen05" else None,
+        "final_positions": int(stack.positions[0]), "finite": bool(torch.isfinite(x1.float()).all())}
+    stack.close()
+    return res
 
 
 def main():
-    """TTFT / TPOT of the attention path on the 48-layer stack (BASELINE configs[3] by default):
-
-        python -m ellm_b200.stack --layers 48 --prefill 32768 --decode 256
-    """
+    """python -m ellm_b200.stack --layers 48 --prefill 32768 --decode 256"""
     import argparse
     import json
     ap = argparse.ArgumentParser()
@@ -174,60 +244,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--projections", choices=["tcgen05", "library"], default="tcgen05")
     args = ap.parse_args()
-    dev = torch.device("cuda:0")
-    torch.cuda.set_device(dev)
-    stream = torch.cuda.Stream(dev)
-    S = args.prefill
-    max_seq = S + args.decode + 8
-    stack = AttentionStack(args.layers, args.hidden, args.q_heads, args.kv_heads, max_seq, S, stream=stream,
-                           projections=args.projections)
-    g = torch.Generator(device=dev).manual_seed(3)
-    x0 = torch.randn(S, 1, args.hidden, device=dev, generator=g).to(torch.bfloat16)
-    with torch.cuda.stream(stream):
-        stack.forward(x0, 0)            # warm-up pass (also fills the cache)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        y = stack.forward(x0, 0)
-        e1.record(stream)
-    stream.synchronize()
-    ttft = e0.elapsed_time(e1)
-    flops_attn = 4 * 128 * args.q_heads * S * (S + 1) / 2 * args.layers
-    flops_proj = 2 * S * args.hidden * (args.q_heads * 128 * 2 + args.kv_heads * 128 * 2) * args.layers
-    # decode: positions start at S; the graph advances them
-    x1 = y[-1:].clone()
-    stack.positions.fill_(S)
-    times = []
-    with torch.cuda.stream(stream):
-        if args.no_graph:
-            for _ in range(args.decode):
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                x1 = stack.forward(x1, 0, ragged=True)
-                stack.positions.add_(1)
-                e1.record(stream)
-                stream.synchronize()
-                times.append(e0.elapsed_time(e1))
-        else:
-            graph, out = stack.capture_decode_step(x1)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for _ in range(args.decode):
-                graph.replay()
-                x1.copy_(out)
-            e1.record(stream)
-            stream.synchronize()
-            times = [e0.elapsed_time(e1) / args.decode]
-    tpot = float(np.mean(times))
-    kv_bytes = 2 * args.kv_heads * 128 * 2 * (S + args.decode / 2) * args.layers
-    w_bytes = 2 * args.hidden * (args.q_heads * 128 * 2 + args.kv_heads * 128 * 2) * args.layers
-    print(json.dumps({
-        "workload": f"{args.layers}-layer attention-only stack, hidden {args.hidden}, {args.q_heads} q / {args.kv_heads} kv heads, "
-                    f"prefill {S} then {args.decode} decode steps, 1 sequence, synthetic weights and activations",
-        "ttft_ms": ttft, "prefill_tflops": (flops_attn + flops_proj) / ttft / 1e9,
-        "prefill_attention_flops_share": flops_attn / (flops_attn + flops_proj),
-        "prefill_projections": args.projections, "tpot_ms": tpot, "decode_gbs": (kv_bytes + w_bytes) / tpot / 1e6, "decode_cuda_graph": not args.no_graph,
-        "final_positions": int(stack.positions[0]), "finite": bool(torch.isfinite(x1.float()).all())}))
-    stack.close()
+    print(json.dumps(measure(args.layers, args.hidden, args.q_heads, args.kv_heads, args.prefill, args.decode,
+                             not args.no_graph, args.projections)))
 
 
 if __name__ == "__main__":

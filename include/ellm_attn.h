@@ -125,6 +125,20 @@ int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
 int ellm_device_alloc(int device, size_t bytes, void** out);
 int ellm_device_free(int device, void* ptr);
 
+/* The static, non-paged KV cache as one object: K and V as [layer, sequence, kv_head,
+ * position, head_size] bf16 in device memory, allocated once at their maximum shape, zero-
+ * filled and never resized - the reference's max-shape, never-freed K/V buffers
+ * (src/memory/allocator.rs:16-27; one private buffer per layer by name,
+ * src/memory/cache.rs:69-75).  ellm_kv_cache_layer hands out a layer's K and V base pointers and
+ * the stride vector an ellm_attn_desc takes (sequence, kv_head, position, head_size - a KV
+ * head's rows are contiguous 256-byte lines).  Any of k, v, kv_strides may be NULL. */
+typedef struct ellm_kv_cache ellm_kv_cache;
+int ellm_kv_cache_create(int device, size_t layers, size_t max_batch, size_t kv_heads,
+                         size_t max_seq, size_t head_size, ellm_kv_cache** out);
+int ellm_kv_cache_destroy(ellm_kv_cache* cache);
+int ellm_kv_cache_layer(const ellm_kv_cache* cache, size_t layer, void** k, void** v,
+                        size_t kv_strides[4]);
+
 /* The KV-append step alone (complex_zip.rs:92-98 semantics): rows
  * src[(r*max_batch + b)*kv_heads + kvh][head_size] -> cache row
  * (b, kvh, position_b + r).  positions NULL = position_index for every b. */
@@ -186,6 +200,30 @@ int ellm_attn_run_window(ellm_attn* h, size_t position_index, size_t position_in
                          size_t batch_size, size_t key_begin, size_t key_end, float* o_part,
                          float* lse_part);
 
+/* ellm_attn_run_window with the queries read from `q` instead of the handle's bound q buffer
+ * (same shape and strides; NULL = the bound buffer).  Sequence-chunk sharding gathers every
+ * rank's query chunks into one buffer and runs each (query chunk, key chunk) pair straight from
+ * it.  No counterpart in the reference (src/compiler/mul/attention.rs:41-67 binds q once). */
+int ellm_attn_run_window_q(ellm_attn* h, const void* q, size_t position_index,
+                           size_t position_interval, size_t batch_size, size_t key_begin,
+                           size_t key_end, float* o_part, float* lse_part);
+
+/* ellm_attn_merge_partials over parts that live in separate buffers: o_parts[i] [rows,
+ * head_size] fp32 and lse_parts[i] [rows] fp32 are device pointers held in HOST arrays of
+ * `parts` <= 16 entries; out is fp32 when out_is_f32 != 0, else bf16.  Lets partial results be
+ * combined where they were computed or received, without gathering them first. */
+int ellm_attn_merge_partials_list(const float* const* o_parts, const float* const* lse_parts,
+                                  size_t parts, size_t rows, size_t head_size, void* out,
+                                  int out_is_f32, float* lse_out, int device, void* stream);
+
+/* For handles created with async = 1, whose run calls only enqueue: waits for the handle's
+ * stream and returns ELLM_ERR_DEVICE_TIMEOUT if a bounded device-side wait of any kernel
+ * launched since the last check ran out (the results of those calls are then invalid), else
+ * ELLM_OK.  The counterpart of the executor's barrier after an operator
+ * (src/serving/start.rs:69-73) for callers that synchronise once per step instead of once per
+ * operator; same role as ellm_matmul_check for the projections. */
+int ellm_attn_check(ellm_attn* h);
+
 /* Counters for the benchmark: kernels launched by this handle since creation, and
  * per-kernel device time when profiling is on (events around each launch). */
 typedef enum ellm_kernel_id {
@@ -224,7 +262,11 @@ int ellm_attn_kernel_stats(ellm_attn* h, int kernel_id, uint64_t* launches,
  *
  * The first call on a device looks the array's device address up and sets the
  * kernel's shared-memory attribute for that device; make that first call before any
- * stream capture begins.  All calls on one device share the array, and it keeps
+ * stream capture begins.  That look-up (or any earlier call into this library on the
+ * device) is also the moment the library's device image, array included, is loaded:
+ * it is the one place where this entry point depends on free device memory, so make
+ * the first call before another allocator takes the GPU's memory.  If none is left it
+ * returns ELLM_ERR_NO_MEMORY.  All calls on one device share the array, and it keeps
  * whatever the previous call left in it.  Nothing in it has to start at zero - each
  * call writes every slot before reading it - so sequential calls on one stream are
  * independent of one another, but two calls whose kernels overlap on the GPU (two
@@ -246,8 +288,9 @@ int ellm_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_c
 /* Named options of a handle.
  *   "tc_wait_timeout_ns"    bound of every device-side wait of the tcgen05 prefill kernel
  *                           (default 2 000 000 000); when one runs out the kernel sets a status
- *                           word, releases its resources and returns, and the call that launched
- *                           it (or the next synchronising call) returns ELLM_ERR_DEVICE_TIMEOUT.
+ *                           word, releases its resources and returns; the call that launched it
+ *                           returns ELLM_ERR_DEVICE_TIMEOUT when the handle synchronises
+ *                           (async = 0), and ellm_attn_check reports it for async = 1 handles.
  *   "tc_debug_skip_kv_item" test hook for that path: the kernel's loader never fetches ring item
  *                           N (0 = first K tile, 1 = first V tile, ...) so the wait on it runs
  *                           out; -1 (default) = off.  The context stays usable afterwards.

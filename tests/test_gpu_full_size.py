@@ -80,6 +80,86 @@ def test_config5_one_head_group_seq_1048576_sampled_rows():
     _sampled_rows_check(S, 8, [0, 255, 256, 65535, 524287, 524288, 1000003, S - 1], seed=4)
 
 
+def test_config5_prefix_65536_through_the_chunk_window_and_merge_path():
+    """BASELINE configs[4]'s own check: the first 65536 tokens of the seed-4 sequence (one KV-head
+    group, 8 query heads / 1 KV head; the tensors are generated at the full 1048576 length and
+    sliced), cut into 8 zig-zag chunks over 4 emulated ranks and pushed through the steps of
+    sharding.sequence_chunk_attention one rank after the other on one GPU - ellm_attn_run_window_q
+    per (query chunk, key chunk) pair on a chunk-local cache, the local pre-merge, the hand-over of
+    the partials to the chunk's owner, the final ellm_attn_merge_partials_list - and 576 sampled
+    rows, spread over every chunk and on both sides of every chunk edge, are recomputed by the
+    oracle's row kernel over all their keys."""
+    from concurrent.futures import ThreadPoolExecutor
+    from ellm_b200 import merge_partials_list, sharding
+    dev = torch.device("cuda:0")
+    S_full, S, G, world = 1048576, 65536, 8, 4
+    gen = torch.Generator(device=dev).manual_seed(4)
+    q = torch.randn(S_full, 1, G, 128, device=dev, generator=gen).to(torch.bfloat16)[:S].contiguous()
+    k = torch.randn(1, 1, S_full, 128, device=dev, generator=gen).to(torch.bfloat16)[:, :, :S].contiguous()
+    v = torch.randn(1, 1, S_full, 128, device=dev, generator=gen).to(torch.bfloat16)[:, :, :S].contiguous()
+    scale = 1.0 / np.sqrt(128.0)
+    plan = sharding.SequenceChunkPlan(seq_len=S, world=world, zigzag=True)
+    Lc, n = plan.chunk_len, plan.n_chunks
+    q_all = q.view(n, Lc, 1, G, 128)
+    dummy = torch.empty(Lc, 1, G, 128, dtype=torch.bfloat16, device=dev)
+    ops = {}
+    for c in range(n):   # every chunk's K/V rows as their owner holds them: a chunk-local cache
+        kc, vc = k[:, :, c * Lc:(c + 1) * Lc].contiguous(), v[:, :, c * Lc:(c + 1) * Lc].contiguous()
+        ops[c] = (ellm_b200.Attention.new(q_all[0], kc, vc, dummy, 1, G, 1, 128, [Lc * 128, Lc * 128, 128, 1], scale,
+                                          max_seq=Lc, max_interval=Lc, async_=True), kc, vc)
+
+    def new_partial():
+        return (torch.empty(Lc, 1, G, 128, dtype=torch.float32, device=dev),
+                torch.empty(Lc, 1, G, dtype=torch.float32, device=dev))
+
+    def compute_partial(i, kc):
+        o, lse = new_partial()
+        ops[kc][0].run_window_q(q_all[i], (i - kc) * Lc, Lc, 1, 0, Lc, o, lse)
+        return o, lse
+
+    def merge(parts):
+        o, lse = new_partial()
+        merge_partials_list([p[0] for p in parts], [p[1] for p in parts], o, lse, out_f32=True)
+        return o, lse
+
+    local = {r: sharding.local_partials(plan, r, compute_partial, merge) for r in range(world)}
+    result = {}
+    for r in range(world):
+        received = {i: [local[src][i] for src in plan.sources_of(i) if src != r] for i in plan.chunks_of(r)}
+        result.update(sharding.final_merge(plan, r, local[r], received, merge))
+    for op, _, _ in ops.values():
+        op.check()
+    assert sorted(result) == list(range(n))
+    assert sum(len(plan.sources_of(i)) > 1 for i in range(n)) >= n - 1   # all but chunk 0 pass through the merge
+
+    rng = np.random.default_rng(65536)
+    rows = set()
+    for c in range(n):
+        rows.update([c * Lc, c * Lc + 1, c * Lc + 127, c * Lc + 128, (c + 1) * Lc - 129, (c + 1) * Lc - 2, (c + 1) * Lc - 1])
+        rows.update(int(x) for x in rng.integers(c * Lc, (c + 1) * Lc, 65))
+    rows = sorted(rows)
+    assert len(rows) >= 512
+    kf, vf = k[0, 0].float().cpu().numpy(), v[0, 0].float().cpu().numpy()
+    got = {}
+    for idx, r in enumerate(rows):
+        c, rr, h = r // Lc, r % Lc, idx % G
+        got[r] = (q[r, 0, h].float().cpu().numpy(), result[c][0][rr, 0, h].cpu().numpy(), float(result[c][1][rr, 0, h]), h)
+
+    def one(r):
+        qf, go, gl, h = got[r]
+        o = np.zeros(128, np.float32)
+        want_l = oracle.flash_attention_f32(qf, kf, vf, o, scale, r)
+        return float(np.abs(go - o).max()), float(np.abs(go - o).mean()), abs(gl - want_l)
+
+    with ThreadPoolExecutor(8) as pool:
+        res = list(pool.map(one, rows))
+    assert max(x[0] for x in res) <= O_MAX_ABS, max(x[0] for x in res)
+    assert np.mean([x[1] for x in res]) <= O_MEAN_ABS
+    assert max(x[2] for x in res) <= LSE_MAX_ABS, max(x[2] for x in res)
+    for op, _, _ in ops.values():
+        op.close()
+
+
 def test_tcgen05_and_warp_mma_kernels_agree_on_every_row_at_32768():
     dev = torch.device("cuda:0")
     S, G = 32768, 8

@@ -125,3 +125,37 @@ def test_inputs_as_column_blocks_of_one_projection_output():
     for a, b in zip(*outs):
         assert torch.equal(a, b)
     assert outs[0][1].abs().sum() > 0
+
+
+def test_positions_past_the_rope_table_leave_q_k_and_v_untouched():
+    """Per-sequence device positions cannot be validated on the host: a position that is inside the
+    cache but has no row in the rotation table must leave the token's whole cache line (K and V)
+    and its Q output as they were, never a new V beside a stale K.  In-place x == y of the
+    row norm gives the bits of the out-of-place call."""
+    dev = torch.device("cuda:0")
+    B, Hq, Hkv, max_seq, rope_rows = 3, 4, 2, 64, 16
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(1, B, Hq, 128, generator=g).to(torch.bfloat16).to(dev)
+    k = torch.randn(1, B, Hkv, 128, generator=g).to(torch.bfloat16).to(dev)
+    v = torch.randn(1, B, Hkv, 128, generator=g).to(torch.bfloat16).to(dev)
+    rope = torch.from_numpy(ellm_b200.precompute_freqs_cis(128, rope_rows, 1e6)).to(dev)
+    strides = [Hkv * max_seq * 128, max_seq * 128, 128, 1]
+    ck = torch.full((B, Hkv, max_seq, 128), 7.0, dtype=torch.bfloat16, device=dev)
+    cv = torch.full_like(ck, 9.0)
+    q_out = torch.full_like(q, 5.0)
+    pos = torch.tensor([3, 40, 15], dtype=torch.int32, device=dev)   # sequence 1 lies past the 16 table rows
+    ellm_b200.qk_norm_rope_append(q, k, v, q_out, ck, cv, rope, strides, B, Hq, Hkv, 128, max_seq, 0, 1, B, 1e-6,
+                                  positions=pos)
+    torch.cuda.synchronize()
+    assert (ck[1] == 7.0).all() and (cv[1] == 9.0).all() and (q_out[0, 1] == 5.0).all()
+    for b, p_ in ((0, 3), (2, 15)):
+        assert torch.equal(cv[b, :, p_], v[0, b]) and not (ck[b, :, p_] == 7.0).all() and not (q_out[0, b] == 5.0).all()
+        untouched = torch.ones(max_seq, dtype=torch.bool, device=dev)
+        untouched[p_] = False
+        assert (ck[b][:, untouched] == 7.0).all() and (cv[b][:, untouched] == 9.0).all()
+    x = (torch.randn(6, 512, generator=g) * 2).to(torch.bfloat16).to(dev)
+    y = torch.zeros_like(x)
+    ellm_b200.rms_norm(x, y, 1e-6)
+    ellm_b200.rms_norm(x, x, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(x, y)

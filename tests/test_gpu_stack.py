@@ -2,7 +2,8 @@
 projection with residual) on a small configuration against a CPU restatement (B200 only).
 
 The prefill chunk runs the projections on the tcgen05 kernel (fused epilogues), the decode steps on
-cuBLAS; both sum in another order than the CPU, so a projected value may land one bf16 step away
+the weight-streaming kernel (head norm, rotation and cache write inside); both sum in another order
+than the CPU, so a projected value may land one bf16 step away
 and the deviation grows a little through the layers; the tolerances here are for the whole stack,
 the per-kernel parity bars are in the kernels' own tests."""
 import numpy as np

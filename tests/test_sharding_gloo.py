@@ -105,3 +105,62 @@ def test_sequence_chunk_exchange_two_gloo_ranks(zigzag):
         chunks, worst_o, worst_l = ret[rank]
         assert chunks == sorted(plan.chunks_of(rank))
         assert worst_o < 8e-3 and worst_l < 1e-4   # oracle O is bf16-rounded; merged partials are fp32
+
+
+def _failing_rank_main(rank, world, port_a, port_b, ret):
+    """Step 1: rank 1 leaves before its sends (it never enters the exchange); rank 0 must come
+    back with ExchangeTimeout inside the bound instead of hanging.  Step 2: both ranks form a
+    fresh group and the same exchange passes."""
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    plan = sharding.SequenceChunkPlan(seq_len=8, world=world, zigzag=True)
+    L = plan.chunk_len
+
+    def compute_partial(i, kc):   # the value of a partial is its (query chunk, key chunk) pair
+        return torch.full((L, 128), float(10 * i + kc)), torch.zeros(L)
+
+    def merge(parts):             # every partial starts with log-sum-exp 0, so the full merge is the mean
+        mo, ml = oracle.merge_partials(np.stack([p[0].numpy() for p in parts]), np.stack([p[1].numpy() for p in parts]))
+        return torch.from_numpy(mo), torch.from_numpy(ml)
+
+    os.environ["MASTER_PORT"] = str(port_a)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    t0 = time.time()
+    outcome = "left"
+    if rank == 0:
+        try:
+            sharding.sequence_chunk_attention(plan, rank, None, compute_partial, merge, dist=dist,
+                                              empty_like=torch.empty_like, timeout_s=2.0)
+            outcome = "no error"
+        except sharding.ExchangeTimeout:
+            outcome = "timeout"
+    elapsed = time.time() - t0
+    # the survivor tells the host side (here: the rendezvous store) before anybody launches again
+    store = dist.distributed_c10d._get_default_store()
+    store.set(f"step1_rank{rank}", outcome)
+    store.wait([f"step1_rank{r}" for r in range(world)], datetime.timedelta(seconds=30))
+    dist.destroy_process_group()
+
+    os.environ["MASTER_PORT"] = str(port_b)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        got = sharding.sequence_chunk_attention(plan, rank, None, compute_partial, merge, dist=dist,
+                                                empty_like=torch.empty_like, timeout_s=20.0)
+        ok = sorted(got) == sorted(plan.chunks_of(rank))
+        for i, (o, _) in got.items():
+            want = np.mean([10 * i + kc for kc in range(i + 1)])
+            ok = ok and bool(torch.allclose(o, torch.full_like(o, float(want)), atol=1e-4))
+        ret[rank] = (outcome, elapsed, ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_a_rank_that_leaves_before_its_sends_is_reported_within_the_bound():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_failing_rank_main, args=(world, _free_port(), _free_port(), ret), nprocs=world, join=True)
+    outcome, elapsed, ok = ret[0]
+    assert outcome == "timeout" and elapsed < 15.0
+    assert ok and ret[1][2]      # the step on the fresh group gave the right result on both ranks

@@ -63,6 +63,33 @@ def test_noalloc_decode_matches_handle_decode_twice_in_a_row():
         assert np.abs(lse_b[:, live].cpu().numpy() - want_l[:, live]).max() <= LSE_MAX_ABS
 
 
+def test_noalloc_decode_leaves_free_device_memory_unchanged():
+    """What the entry point's name promises: once the first call on the device is behind it (that
+    call is where the library image with its fixed array gets loaded), further calls take no
+    device memory - free memory as the driver reports it is the same before and after."""
+    dev = torch.device("cuda:0")
+    case = Case(seed=303, interval=1, batch=4, q_heads=32, kv_heads=4, max_seq=1024, positions=[1000, 17, 512, 63])
+    pos = torch.from_numpy(case.positions).to(dev)
+    q, ck, cv = case.q.to(dev), case.cache_k.to(dev), case.cache_v.to(dev)
+    ck[:, :, :1024] = torch.nan_to_num(ck[:, :, :1024])   # the rows at the positions themselves are read
+    cv[:, :, :1024] = torch.nan_to_num(cv[:, :, :1024])
+    out = torch.zeros_like(q)
+    lse = torch.zeros(1, case.max_batch, case.q_heads, dtype=torch.float32, device=dev)
+
+    def call():
+        ellm_b200.decode_noalloc(q, ck, cv, out, case.batch, case.q_heads, case.kv_heads, 128, case.strides, case.scale,
+                                 max_seq=case.max_seq, positions=pos, lse=lse)
+    call()                                  # warm: symbol look-up, module load
+    torch.cuda.synchronize(dev)
+    free_before, _ = torch.cuda.mem_get_info(dev)
+    for _ in range(8):
+        call()
+    torch.cuda.synchronize(dev)
+    free_after, _ = torch.cuda.mem_get_info(dev)
+    assert free_after == free_before
+    assert torch.isfinite(out[:, :case.batch].float()).all()
+
+
 def test_noalloc_decode_rejects_sizes_beyond_its_scratch():
     dev = torch.device("cuda:0")
     lib = ellm_b200.load()
