@@ -5,6 +5,7 @@
 
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstdarg>
@@ -422,17 +423,15 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
                            decode_out_override);
     } else {
         bool use_tc = false;
-        if (key_begin == 0) {
-            if (h->d.prefill_kernel == ELLM_PREFILL_TCGEN05) use_tc = true;
-            else if (h->d.prefill_kernel == ELLM_PREFILL_AUTO) use_tc = ellm::tcgen05_prefers(h->tc, interval, h->group);
-        }
+        if (h->d.prefill_kernel == ELLM_PREFILL_TCGEN05) use_tc = true;
+        else if (h->d.prefill_kernel == ELLM_PREFILL_AUTO) use_tc = ellm::tcgen05_prefers(h->tc, interval, h->group);
         if (use_tc) {
             if (!h->tc.ready)
                 return fail(ELLM_ERR_UNSUPPORTED, "tcgen05 prefill unavailable for this handle: %s", h->tc.why);
             {
                 LaunchScope ls(h, ELLM_KERNEL_PREFILL_TCGEN05);
-                rc = ellm::launch_prefill_tcgen05(h->tc, h->d, positions, position_index, interval, batch, key_end, out_f32,
-                                                  lse_out, h->status_dev, h->stream);
+                rc = ellm::launch_prefill_tcgen05(h->tc, h->d, positions, position_index, interval, batch, key_begin, key_end,
+                                                  out_f32, lse_out, h->status_dev, h->stream);
             }
             if (rc == ELLM_ERR_UNSUPPORTED) return fail(rc, "tcgen05 prefill: %s", h->tc.why);
             if (rc) return fail(rc, "tcgen05 prefill launch failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -987,6 +986,10 @@ int ellm_attn_set_option(ellm_attn* h, const char* name, long long value) {
         h->dec_ctas = static_cast<int>(value);
         return ELLM_OK;
     }
+    if (std::strcmp(name, "tc_persistent") == 0) {
+        h->tc.persistent = value < 0 ? -1 : (value != 0);
+        return ELLM_OK;
+    }
     if (std::strcmp(name, "tc_debug_skip_kv_item") == 0) {
         h->tc.debug_skip_item = value < 0 ? -1 : static_cast<int>(value);
         return ELLM_OK;
@@ -1154,5 +1157,11 @@ extern "C" int ellm_attn_decode_noalloc(const void* q, const void* k_cache, cons
     return ELLM_OK;
 }
 
+
+#ifdef ELLM_TC_TRACE
+extern "C" int ellm_debug_read_tc_trace(long long* host, size_t count) {
+    return cudaMemcpyFromSymbol(host, ellm::g_tc_trace, count * sizeof(long long)) == cudaSuccess ? 0 : 2;
+}
+#endif
 
 #include "ellm_proj_api.cuh"

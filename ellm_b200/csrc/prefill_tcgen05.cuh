@@ -65,6 +65,7 @@ struct Tcgen05Plan {
     const void* cached_q = nullptr;
     unsigned long long wait_timeout_ns = 2000000000ull;   // ellm_attn_set_option("tc_wait_timeout_ns")
     int debug_skip_item = -1;                              // ellm_attn_set_option("tc_debug_skip_kv_item")
+    int persistent = -1;                                   // ellm_attn_set_option("tc_persistent"): -1 auto, 0 one CTA per item, 1 one CTA per SM
 };
 
 struct TcParams {
@@ -74,7 +75,9 @@ struct TcParams {
     int* status;            // device word: non-zero = a bounded wait ran out
     const int32_t* positions;  // per-sequence position of chunk row 0, or nullptr (then `base` for all)
     long long base;         // position of chunk row 0
-    long long key_end;      // rows attend keys [0, min(position + 1, key_end)); uniform chunk start only
+    long long key_begin;    // rows attend keys [key_begin, min(position + 1, key_end)); key_end for a uniform chunk start only
+    long long key_end;
+    long long n_items;      // 256-row work items of the launch = pair_tiles * kv_heads * batch
     long long max_seq;      // rows per (sequence, kv head) in the cache
     int interval, batch, max_batch;
     int q_heads, kv_heads, group;
@@ -268,16 +271,95 @@ __device__ __forceinline__ uint64_t exp2_poly2(uint64_t x2) {
     return pack2(y0, y1);
 }
 
-// Status codes written by a wait that ran out (which wait gave up).
-enum { kTcWaitQ = 1, kTcWaitKvFull = 2, kTcWaitKvEmpty = 3, kTcWaitSFull = 4, kTcWaitPFull = 5, kTcWaitPvDone = 6 };
+// Optional per-CTA time stamps for tuning (compiled in only with -DELLM_TC_TRACE): slot -> SM clock.
+#ifdef ELLM_TC_TRACE
+__device__ long long g_tc_trace[1024 * 64];
+#define TC_TRACE(slot)                                                                   \
+    do {                                                                                 \
+        if (blockIdx.x < 1024 && (slot) < 64) g_tc_trace[blockIdx.x * 64 + (slot)] = clock64(); \
+    } while (0)
+#define TC_TRACE_NS(slot)                                                                \
+    do {                                                                                 \
+        if (blockIdx.x < 1024 && (slot) < 64) g_tc_trace[blockIdx.x * 64 + (slot)] = static_cast<long long>(global_timer_ns()); \
+    } while (0)
+#else
+#define TC_TRACE(slot) do {} while (0)
+#define TC_TRACE_NS(slot) do {} while (0)
+#endif
 
-// Key tiles row tile t of this CTA needs (0 when the tile has no valid row).
-__device__ __forceinline__ int tc_tile_steps(const TcParams& p, int rho0, int total_rows, long long base, long long key_end) {
-    if (rho0 >= total_rows) return 0;
-    const int rho_last = min(rho0 + kTcTileRows, total_rows) - 1;
-    long long kend = base + rho_last / p.group + 1;
-    if (kend > key_end) kend = key_end;
-    return static_cast<int>((kend + kTcKeys - 1) / kTcKeys);
+// Status codes written by a wait that ran out (which wait gave up).
+enum { kTcWaitQ = 1, kTcWaitKvFull = 2, kTcWaitKvEmpty = 3, kTcWaitSFull = 4, kTcWaitPFull = 5, kTcWaitPvDone = 6,
+       kTcWaitQEmpty = 7 };
+
+// One work item: 256 packed rows (two 128-row tiles) of one (sequence, KV head).
+struct TcItem {
+    int pair, kvh, b;
+    long long base;      // position of the sequence's chunk row 0
+    long long key_end;   // rows attend keys [key_begin, min(position + 1, key_end))
+    int j0;              // first 128-key tile of the window
+    int lo;              // first visible column of that tile (key_begin - 128 * j0)
+    int steps[kTcTiles]; // key tiles row tile t needs (0: no valid row, or no key of the window in reach)
+    int nsteps;
+    bool zero_tail;
+};
+
+// The items are numbered heaviest first: later row tiles have more keys.  When all heads' K/V fit
+// in L2 together the order is heaviest-first over the whole launch, else head by head so that one
+// head's K/V stays resident while its row tiles are worked off.  A CTA takes item
+// round * gridDim.x + (its index, counted from the other end in odd rounds): with weights that fall
+// along the list the two directions even out, and a grid as large as the list gives every CTA one item.
+__device__ __forceinline__ bool tc_item(const TcParams& p, int round, TcItem& it) {
+    const long long grid = gridDim.x;
+    const long long idx = static_cast<long long>(round) * grid +
+                          ((round & 1) ? grid - 1 - static_cast<long long>(blockIdx.x) : static_cast<long long>(blockIdx.x));
+    if (idx >= p.n_items) return false;
+    const int heads = p.kv_heads * p.batch;
+    int head;
+    if (p.pair_major) {
+        it.pair = p.pair_tiles - 1 - static_cast<int>(idx / heads);
+        head = static_cast<int>(idx % heads);
+    } else {
+        head = static_cast<int>(idx / p.pair_tiles);
+        it.pair = p.pair_tiles - 1 - static_cast<int>(idx % p.pair_tiles);
+    }
+    it.kvh = head % p.kv_heads;
+    it.b = head / p.kv_heads;
+    // where this sequence's chunk starts and where its keys end
+    it.base = p.positions ? static_cast<long long>(p.positions[it.b]) : p.base;
+    it.key_end = p.positions ? min(it.base + p.interval, p.max_seq) : p.key_end;
+    it.j0 = static_cast<int>(p.key_begin / kTcKeys);
+    it.lo = static_cast<int>(p.key_begin - static_cast<long long>(it.j0) * kTcKeys);
+    const int total_rows = p.interval * p.group;
+    it.nsteps = 0;
+#pragma unroll
+    for (int t = 0; t < kTcTiles; ++t) {
+        const int rho0 = (it.pair * kTcTiles + t) * kTcTileRows;
+        int s = 0;
+        if (rho0 < total_rows) {
+            const int rho_last = min(rho0 + kTcTileRows, total_rows) - 1;
+            long long kend = it.base + rho_last / p.group + 1;
+            if (kend > it.key_end) kend = it.key_end;
+            s = static_cast<int>((kend + kTcKeys - 1) / kTcKeys) - it.j0;
+            if (s < 0) s = 0;
+        }
+        it.steps[t] = s;
+        it.nsteps = max(it.nsteps, s);
+    }
+    // With per-sequence chunk starts the K/V tensor maps are bounded by the cache, not by this
+    // sequence's end, so the last V tile may carry rows past key_end that hold anything; their P
+    // is 0 but 0 * NaN is NaN, so the producer zeroes them before the MMA may read the tile.
+    it.zero_tail = p.positions != nullptr && static_cast<long long>(it.j0 + it.nsteps) * kTcKeys > it.key_end;
+    return true;
+}
+
+// A wait of the teardown: bounded, sets no status.
+__device__ __noinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity, unsigned long long timeout_ns) {
+    const unsigned long long t0 = global_timer_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > timeout_ns) return false;
+    }
 }
 
 template <typename OutT>
@@ -288,6 +370,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) { TC_TRACE_NS(0); TC_TRACE(1); }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == (kTcTiles * 4) * 32) {   // the producer thread fetches the three descriptors ahead of its first copy
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -303,31 +386,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     auto bar_s_full = [&](int t) { return bar0 + 8u * (2 + 2 * kTcStages + t); };
     auto bar_p_full = [&](int t) { return bar0 + 8u * (4 + 2 * kTcStages + t); };
     auto bar_pv_done = [&](int t) { return bar0 + 8u * (6 + 2 * kTcStages + t); };
-    const uint32_t bar_tail = bar0 + 8u * (8 + 2 * kTcStages);
-    constexpr int kNumBars = 9 + 2 * kTcStages;
+    auto bar_q_empty = [&](int t) { return bar0 + 8u * (8 + 2 * kTcStages + t); };
+    const uint32_t bar_tail = bar0 + 8u * (10 + 2 * kTcStages);
+    const uint32_t bar_final = bar0 + 8u * (11 + 2 * kTcStages);
+    constexpr int kNumBars = 12 + 2 * kTcStages;
+    static_assert(8 * kNumBars + 16 <= 256, "the barrier block is 256 bytes");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kTcSmemBar + 8 * kNumBars);
     volatile int* abort_word = reinterpret_cast<volatile int*>(smem + kTcSmemBar + 8 * kNumBars + 8);
 
-    // CTAs are taken in block-index order.  Later row tiles have more keys, so they go first; when
-    // all heads' K/V fit in L2 together the order is heaviest-first over the whole grid, else
-    // head by head so that one head's K/V stays resident while its row tiles are worked off.
-    int pair, kvh, b;
-    {
-        const int heads = p.kv_heads * p.batch;
-        int head;
-        if (p.pair_major) {
-            pair = p.pair_tiles - 1 - static_cast<int>(blockIdx.x / heads);
-            head = static_cast<int>(blockIdx.x % heads);
-        } else {
-            head = static_cast<int>(blockIdx.x / p.pair_tiles);
-            pair = p.pair_tiles - 1 - static_cast<int>(blockIdx.x % p.pair_tiles);
-        }
-        kvh = head % p.kv_heads;
-        b = head / p.kv_heads;
-    }
     if (threadIdx.x == 0) {
         for (int t = 0; t < kTcTiles; ++t) {
             mbar_init(bar_q(t), 1);
+            mbar_init(bar_q_empty(t), 1);
             mbar_init(bar_s_full(t), 1);
             mbar_init(bar_p_full(t), kTcTileRows / 32);   // one arrival per softmax warp
             mbar_init(bar_pv_done(t), 1);
@@ -337,6 +407,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(bar_kv_empty(s), 1);
         }
         mbar_init(bar_tail, 1);
+        mbar_init(bar_final, 1);
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -353,19 +424,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // Launched as a programmatic dependent, the set-up above ran while the stream's previous kernel
     // was still at work; everything below reads or writes what that kernel may have touched.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) TC_TRACE(2);
     const int total_rows = p.interval * p.group;
-    int steps[kTcTiles];
-    // where this sequence's chunk starts and where its keys end
-    const long long base = p.positions ? static_cast<long long>(p.positions[b]) : p.base;
-    const long long key_end = p.positions ? min(base + p.interval, p.max_seq) : p.key_end;
-    for (int t = 0; t < kTcTiles; ++t) steps[t] = tc_tile_steps(p, (pair * kTcTiles + t) * kTcTileRows, total_rows, base, key_end);
-    const int nsteps = max(steps[0], steps[1]);
-    // With per-sequence chunk starts the K/V tensor maps are bounded by the cache, not by this
-    // sequence's end, so the last V tile may carry rows past key_end that hold anything; their P
-    // is 0 but 0 * NaN is NaN, so the producer zeroes them before the MMA may read the tile.
-    const bool zero_tail = p.positions != nullptr && static_cast<long long>(nsteps) * kTcKeys > key_end;
+    const int rounds = static_cast<int>((p.n_items + gridDim.x - 1) / gridDim.x);
 
-
+    // Every role walks the same list of items.  What carries over from one item to the next are the
+    // barriers' phases, so each role counts what it has pushed through them so far: ring items,
+    // key steps per row tile, Q loads per row tile, tail clean-ups.
     if (warp < kTcTiles * 4) {
         // =============================== softmax / correction / epilogue ===============================
         const int t = warp >> 2;
@@ -373,149 +438,50 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t tS = tmem + lane_base + t * 128;
         const uint32_t tO = tmem + lane_base + 256 + t * 128;
-        const int rho = (pair * kTcTiles + t) * kTcTileRows + row;
-        const bool valid = rho < total_rows;
-        const int pos = valid ? rho / p.group : 0, g = valid ? rho % p.group : 0;
-        const long long lim = valid ? min(base + pos, key_end - 1) : -1;   // last key this row may see
-        const long long tile_min_lim = min(base + ((pair * kTcTiles + t) * kTcTileRows) / p.group, key_end - 1);
-        const int my_steps = steps[t];
-        float m_used = -INFINITY, l = 0.0f;
+        int steps_done = 0;     // key steps of this row tile over all items so far
         bool ok = true;
-        for (int j = 0; j < my_steps && ok; ++j) {
-            // lane 0 polls the barrier, the warp follows (32 pollers per warp only add shared-memory traffic)
-            ok = lane == 0 ? mbar_wait(bar_s_full(t), j & 1, abort_word, p.status, kTcWaitSFull, p.wait_timeout_ns) : true;
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-            const long long key0 = static_cast<long long>(j) * kTcKeys;
-            const bool edge = key0 + kTcKeys - 1 > tile_min_lim;   // the causal edge crosses this tile
-            const long long dlim = lim - key0;                     // last column this row may see
-            const int rel = dlim < 0 ? -1 : (dlim > 127 ? 127 : static_cast<int>(dlim));
-            // Fast path (every step but the first, unless a score leaps far above the maximum in use):
-            // exponentiate against the maximum already in use, in one pass.  P is held in registers
-            // until the step's row sum has shown that nothing leapt - then it is consistent with O
-            // and l as they stand and goes to tensor memory as is.  Otherwise S_t is still intact and
-            // the two-pass slow path below redoes the step with a rescale of O_t.
-            bool slow = (j == 0) || edge;
-            if (!slow) {
-                const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_used, -m_used);
-                uint64_t sum_a = pack2(0.0f, 0.0f), sum_b = sum_a;
-                uint32_t pk[64];
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    float s[64];
-                    tmem_ld32(tS + half * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
-                    tmem_ld32(tS + half * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int cc = 0; cc < 32; ++cc) {
-                        const int c = half * 32 + cc;
-                        const uint64_t x2 = fma2(pack2(s[2 * cc], s[2 * cc + 1]), scale2, negm2);
-                        uint64_t p2;
-                        if (kTcPolyEvery > 0 && (c % kTcPolyDiv) == kTcPolyDiv - 1) {
-                            p2 = exp2_poly2(x2);
-                        } else {
-                            float x0, x1;
-                            unpack2(x2, x0, x1);
-                            p2 = pack2(fast_exp2(x0), fast_exp2(x1));
-                        }
-                        if (c & 1) sum_b = add2(sum_b, p2); else sum_a = add2(sum_a, p2);
-                        float p0, p1;
-                        unpack2(p2, p0, p1);
-                        pk[c] = pack_bf16(p0, p1);
-                    }
-                }
-                // No row maximum is tracked here.  A score far above the maximum in use shows up as a huge
-                // term of this step's sum (2^16 and more: one key 16 octaves above, or infinity); then the
-                // step is redone the slow way, which finds the true maximum and rescales.  Below that, P
-                // (bf16) and the fp32 accumulators take the larger terms as they are.
-                float sa, sb;
-                unpack2(add2(sum_a, sum_b), sa, sb);
-                const float step_sum = sa + sb;
-                slow = __any_sync(0xffffffffu, !(step_sum < kTcSumTrigger));
+        TcItem it;
+        int n_traced = 0;
+        for (int round = 0; round < rounds && ok; ++round) {
+            if (!tc_item(p, round, it)) continue;
+            const int tr = 8 + 8 * n_traced + 4 * t;   // trace slots of this item and tile
+            ++n_traced;
+            const int rho = (it.pair * kTcTiles + t) * kTcTileRows + row;
+            const bool valid = rho < total_rows;
+            const int pos = valid ? rho / p.group : 0, g = valid ? rho % p.group : 0;
+            const long long lim = valid ? min(it.base + pos, it.key_end - 1) : -1;   // last key this row may see
+            const long long tile_min_lim = min(it.base + ((it.pair * kTcTiles + t) * kTcTileRows) / p.group, it.key_end - 1);
+            const int my_steps = it.steps[t];
+            const long long row_index = (static_cast<long long>(pos) * p.max_batch + it.b) * p.q_heads + it.kvh * p.group + g;
+            float m_used = -INFINITY, l = 0.0f;
+            for (int j = 0; j < my_steps && ok; ++j) {
+                // lane 0 polls the barrier, the warp follows (32 pollers per warp only add shared-memory traffic)
+                ok = lane == 0 ? mbar_wait(bar_s_full(t), (steps_done + j) & 1, abort_word, p.status, kTcWaitSFull, p.wait_timeout_ns) : true;
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (j == 0 && (warp & 3) == 0 && lane == 0) TC_TRACE(tr);
+                tc_fence_after();
+                const long long key0 = static_cast<long long>(it.j0 + j) * kTcKeys;
+                const int lo = j == 0 ? it.lo : 0;                     // columns below it lie before the key window
+                const bool edge = key0 + kTcKeys - 1 > tile_min_lim || lo > 0;   // the causal edge (or the window's start) crosses this tile
+                const long long dlim = lim - key0;                     // last column this row may see
+                const int rel = dlim < 0 ? -1 : (dlim > 127 ? 127 : static_cast<int>(dlim));
+                // Fast path (every step but the first, unless a score leaps far above the maximum in use):
+                // exponentiate against the maximum already in use, in one pass.  P is held in registers
+                // until the step's row sum has shown that nothing leapt - then it is consistent with O
+                // and l as they stand and goes to tensor memory as is.  Otherwise S_t is still intact and
+                // the two-pass slow path below redoes the step with a rescale of O_t.
+                bool slow = (j == 0) || edge;
                 if (!slow) {
-                    l += step_sum;
-                    tmem_st32u(tS, pk);
-                    tmem_st32u(tS + 32, pk + 32);
-                    tmem_wait_st();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_p_full(t));
-                }
-            }
-            if (slow) {
-                // pass 1 over S_t: row maximum (3-input max, two chains per 32-column chunk).  The
-                // scores are read again in pass 2 rather than kept: tensor-memory reads are cheap and
-                // 128 live registers per thread are not.
-                float mx = -INFINITY;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    float s[64];
-                    tmem_ld32(tS + h * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
-                    tmem_ld32(tS + h * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
-                    tmem_wait_ld();
-                    if (edge) {
-#pragma unroll
-                        for (int c = 0; c < 64; ++c) s[c] = (h * 64 + c <= rel) ? s[c] : -INFINITY;
-                    }
-                    float m0 = max3(s[0], s[1], s[2]), m1 = max3(s[3], s[4], s[5]);
-                    float m2 = max3(s[6], s[7], s[8]), m3 = max3(s[9], s[10], s[11]);
-#pragma unroll
-                    for (int c = 12; c < 60; c += 8) {
-                        m0 = max3(m0, s[c], s[c + 1]);
-                        m1 = max3(m1, s[c + 2], s[c + 3]);
-                        m2 = max3(m2, s[c + 4], s[c + 5]);
-                        m3 = max3(m3, s[c + 6], s[c + 7]);
-                    }
-                    m0 = max3(m0, s[60], s[61]);
-                    m1 = max3(m1, s[62], s[63]);
-                    mx = max3(mx, fmaxf(m0, m1), fmaxf(m2, m3));
-                }
-                const float m_new = fmaxf(m_used, mx * p.scale_log2);
-                // rescale O only when the maximum moved far enough to matter; otherwise keep
-                // exponentiating against the stale maximum (O and l stay consistent with it)
-                const bool need = (m_new - m_used > kTcRescaleThreshold) || (m_used == -INFINITY && m_new != -INFINITY);
-                const bool rescale = __any_sync(0xffffffffu, need);
-                float corr = 1.0f;
-                if (rescale) {
-                    corr = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
-                    m_used = m_new;
-                }
-                const float msub = (m_used == -INFINITY) ? 0.0f : m_used;
-                // S_t(j) complete implies P.V(t, j-1) complete (MMAs of one thread finish in issue
-                // order), so O_t can be rescaled and the columns of S_t can take P_t right away.
-                if (rescale && j > 0) {   // before any P.V of this step may start
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        float o[32];
-                        tmem_ld32(tO + c * 32, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] *= corr;
-                        tmem_st32(tO + c * 32, o);
-                    }
-                }
-                // pass 2: p = exp2(s * scale - m) on packed pairs (a fixed share of the pairs may take
-                // the polynomial route on the FMA pipe instead of the 16-per-clock exp2 unit);
-                // P row -> tensor memory as bf16 pairs (k, k+1) per 32-bit column, 64 columns, over
-                // the first half of S_t.  The first 64 keys' P is handed to the MMA warp before the
-                // second half is computed.
-                {
-                    const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-msub, -msub);
+                    const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_used, -m_used);
                     uint64_t sum_a = pack2(0.0f, 0.0f), sum_b = sum_a;
+                    uint32_t pk[64];
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
-                        // keys [64*half, 64*half+64) of S sit in columns [64*half, +64); their P goes to
-                        // columns [32*half, +32), which never overlap a half of S not yet read
                         float s[64];
                         tmem_ld32(tS + half * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
                         tmem_ld32(tS + half * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
                         tmem_wait_ld();
-                        if (edge) {
-#pragma unroll
-                            for (int c = 0; c < 64; ++c) s[c] = (half * 64 + c <= rel) ? s[c] : -INFINITY;
-                        }
-                        uint32_t pk[32];
 #pragma unroll
                         for (int cc = 0; cc < 32; ++cc) {
                             const int c = half * 32 + cc;
@@ -531,98 +497,247 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                             if (c & 1) sum_b = add2(sum_b, p2); else sum_a = add2(sum_a, p2);
                             float p0, p1;
                             unpack2(p2, p0, p1);
-                            pk[cc] = pack_bf16(p0, p1);
+                            pk[c] = pack_bf16(p0, p1);
                         }
-                        tmem_st32u(tS + half * 32, pk);
+                    }
+                    // No row maximum is tracked here.  A score far above the maximum in use shows up as a huge
+                    // term of this step's sum (2^16 and more: one key 16 octaves above, or infinity); then the
+                    // step is redone the slow way, which finds the true maximum and rescales.  Below that, P
+                    // (bf16) and the fp32 accumulators take the larger terms as they are.
+                    float sa, sb;
+                    unpack2(add2(sum_a, sum_b), sa, sb);
+                    const float step_sum = sa + sb;
+                    slow = __any_sync(0xffffffffu, !(step_sum < kTcSumTrigger));
+                    if (!slow) {
+                        l += step_sum;
+                        tmem_st32u(tS, pk);
+                        tmem_st32u(tS + 32, pk + 32);
                         tmem_wait_st();
                         tc_fence_before();
                         __syncwarp();
-                        if (half == 1 && lane == 0) mbar_arrive(bar_p_full(t));
+                        if (lane == 0) mbar_arrive(bar_p_full(t));
                     }
-                    float sa, sb;
-                    unpack2(add2(sum_a, sum_b), sa, sb);
-                    l = l * corr + (sa + sb);
+                }
+                if (slow) {
+                    // pass 1 over S_t: row maximum (3-input max, two chains per 32-column chunk).  The
+                    // scores are read again in pass 2 rather than kept: tensor-memory reads are cheap and
+                    // 128 live registers per thread are not.
+                    float mx = -INFINITY;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        float s[64];
+                        tmem_ld32(tS + h * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
+                        tmem_ld32(tS + h * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+                        tmem_wait_ld();
+                        if (edge) {
+#pragma unroll
+                            for (int c = 0; c < 64; ++c) s[c] = (h * 64 + c <= rel && h * 64 + c >= lo) ? s[c] : -INFINITY;
+                        }
+                        float m0 = max3(s[0], s[1], s[2]), m1 = max3(s[3], s[4], s[5]);
+                        float m2 = max3(s[6], s[7], s[8]), m3 = max3(s[9], s[10], s[11]);
+#pragma unroll
+                        for (int c = 12; c < 60; c += 8) {
+                            m0 = max3(m0, s[c], s[c + 1]);
+                            m1 = max3(m1, s[c + 2], s[c + 3]);
+                            m2 = max3(m2, s[c + 4], s[c + 5]);
+                            m3 = max3(m3, s[c + 6], s[c + 7]);
+                        }
+                        m0 = max3(m0, s[60], s[61]);
+                        m1 = max3(m1, s[62], s[63]);
+                        mx = max3(mx, fmaxf(m0, m1), fmaxf(m2, m3));
+                    }
+                    const float m_new = fmaxf(m_used, mx * p.scale_log2);
+                    // rescale O only when the maximum moved far enough to matter; otherwise keep
+                    // exponentiating against the stale maximum (O and l stay consistent with it)
+                    const bool need = (m_new - m_used > kTcRescaleThreshold) || (m_used == -INFINITY && m_new != -INFINITY);
+                    const bool rescale = __any_sync(0xffffffffu, need);
+                    float corr = 1.0f;
+                    if (rescale) {
+                        corr = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
+                        m_used = m_new;
+                    }
+                    const float msub = (m_used == -INFINITY) ? 0.0f : m_used;
+                    // S_t(j) complete implies P.V(t, j-1) complete (MMAs of one thread finish in issue
+                    // order), so O_t can be rescaled and the columns of S_t can take P_t right away.
+                    if (rescale && j > 0) {   // before any P.V of this step may start
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            float o[32];
+                            tmem_ld32(tO + c * 32, o);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] *= corr;
+                            tmem_st32(tO + c * 32, o);
+                        }
+                    }
+                    // pass 2: p = exp2(s * scale - m) on packed pairs; P row -> tensor memory as bf16
+                    // pairs (k, k+1) per 32-bit column, 64 columns, over the first half of S_t.
+                    {
+                        const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-msub, -msub);
+                        uint64_t sum_a = pack2(0.0f, 0.0f), sum_b = sum_a;
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            // keys [64*half, 64*half+64) of S sit in columns [64*half, +64); their P goes to
+                            // columns [32*half, +32), which never overlap a half of S not yet read
+                            float s[64];
+                            tmem_ld32(tS + half * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
+                            tmem_ld32(tS + half * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+                            tmem_wait_ld();
+                            if (edge) {
+#pragma unroll
+                                for (int c = 0; c < 64; ++c) s[c] = (half * 64 + c <= rel && half * 64 + c >= lo) ? s[c] : -INFINITY;
+                            }
+                            uint32_t pk[32];
+#pragma unroll
+                            for (int cc = 0; cc < 32; ++cc) {
+                                const int c = half * 32 + cc;
+                                const uint64_t x2 = fma2(pack2(s[2 * cc], s[2 * cc + 1]), scale2, negm2);
+                                uint64_t p2;
+                                if (kTcPolyEvery > 0 && (c % kTcPolyDiv) == kTcPolyDiv - 1) {
+                                    p2 = exp2_poly2(x2);
+                                } else {
+                                    float x0, x1;
+                                    unpack2(x2, x0, x1);
+                                    p2 = pack2(fast_exp2(x0), fast_exp2(x1));
+                                }
+                                if (c & 1) sum_b = add2(sum_b, p2); else sum_a = add2(sum_a, p2);
+                                float p0, p1;
+                                unpack2(p2, p0, p1);
+                                pk[cc] = pack_bf16(p0, p1);
+                            }
+                            tmem_st32u(tS + half * 32, pk);
+                            tmem_wait_st();
+                            tc_fence_before();
+                            __syncwarp();
+                            if (half == 1 && lane == 0) mbar_arrive(bar_p_full(t));
+                        }
+                        float sa, sb;
+                        unpack2(add2(sum_a, sum_b), sa, sb);
+                        l = l * corr + (sa + sb);
+                    }
                 }
             }
-        }
-        if (ok && my_steps > 0) {
-            ok = mbar_wait(bar_pv_done(t), (my_steps - 1) & 1, abort_word, p.status, kTcWaitPvDone, p.wait_timeout_ns);
-            ok = __all_sync(0xffffffffu, ok);
-        }
-        if (ok && my_steps > 0) {
-            tc_fence_after();
-            const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
-            const long long row_index = (static_cast<long long>(pos) * p.max_batch + b) * p.q_heads + kvh * p.group + g;
+            if ((warp & 3) == 0 && lane == 0) TC_TRACE(tr + 1);
+            if (ok && my_steps > 0) {
+                ok = mbar_wait(bar_pv_done(t), (steps_done + my_steps - 1) & 1, abort_word, p.status, kTcWaitPvDone, p.wait_timeout_ns);
+                ok = __all_sync(0xffffffffu, ok);
+            }
+            if (!ok) break;
+            if ((warp & 3) == 0 && lane == 0) TC_TRACE(tr + 2);
             OutT* orow = reinterpret_cast<OutT*>(p.out) + row_index * kHeadDim;
+            if (my_steps > 0) {
+                tc_fence_after();
+                const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float o[32];
-                tmem_ld32(tO + c * 32, o);
-                tmem_wait_ld();
-                if (valid) {
-                    if constexpr (sizeof(OutT) == 4) {
+                for (int c = 0; c < 4; ++c) {
+                    float o[32];
+                    tmem_ld32(tO + c * 32, o);
+                    tmem_wait_ld();
+                    if (valid) {
+                        if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            *reinterpret_cast<float4*>(orow + c * 32 + i * 4) =
-                                make_float4(o[i * 4 + 0] * inv, o[i * 4 + 1] * inv, o[i * 4 + 2] * inv, o[i * 4 + 3] * inv);
-                    } else {
+                            for (int i = 0; i < 8; ++i)
+                                *reinterpret_cast<float4*>(orow + c * 32 + i * 4) =
+                                    make_float4(o[i * 4 + 0] * inv, o[i * 4 + 1] * inv, o[i * 4 + 2] * inv, o[i * 4 + 3] * inv);
+                        } else {
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            uint4 v;
-                            v.x = pack_bf16(o[i * 8 + 0] * inv, o[i * 8 + 1] * inv);
-                            v.y = pack_bf16(o[i * 8 + 2] * inv, o[i * 8 + 3] * inv);
-                            v.z = pack_bf16(o[i * 8 + 4] * inv, o[i * 8 + 5] * inv);
-                            v.w = pack_bf16(o[i * 8 + 6] * inv, o[i * 8 + 7] * inv);
-                            *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = v;
+                            for (int i = 0; i < 4; ++i) {
+                                uint4 v;
+                                v.x = pack_bf16(o[i * 8 + 0] * inv, o[i * 8 + 1] * inv);
+                                v.y = pack_bf16(o[i * 8 + 2] * inv, o[i * 8 + 3] * inv);
+                                v.z = pack_bf16(o[i * 8 + 4] * inv, o[i * 8 + 5] * inv);
+                                v.w = pack_bf16(o[i * 8 + 6] * inv, o[i * 8 + 7] * inv);
+                                *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = v;
+                            }
                         }
                     }
                 }
+                if (valid && p.lse) p.lse[row_index] = (m_used + log2f(l)) * kLn2;
+                // the next item's first P.V overwrites O_t: its P is only handed over by these same
+                // threads, after the reads above have completed
+                tc_fence_before();
+            } else if (valid) {
+                // no key of the window lies in reach of this tile's rows: an empty partial result
+                if constexpr (sizeof(OutT) == 4) {
+                    for (int i = 0; i < 32; ++i) *reinterpret_cast<float4*>(orow + i * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                } else {
+                    for (int i = 0; i < 16; ++i) *reinterpret_cast<uint4*>(orow + i * 8) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                if (p.lse) p.lse[row_index] = -INFINITY;
             }
-            if (valid && p.lse) p.lse[row_index] = (m_used + log2f(l)) * kLn2;
-            tc_fence_before();
+            steps_done += my_steps;
+            if ((warp & 3) == 0 && lane == 0) TC_TRACE(tr + 3);
         }
     } else if (warp == kTcTiles * 4) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
             bool ok = true;
-            for (int t = 0; t < kTcTiles; ++t) {
-                if (steps[t] == 0) continue;
-                const int rho0 = (pair * kTcTiles + t) * kTcTileRows;
-                mbar_arrive_expect_tx(bar_q(t), kTcTileBytes);
-                for (int h = 0; h < 2; ++h)
-                    tma_load_5d(smem_base + kTcSmemQ + t * kTcTileBytes + h * kTcHalfBytes, &map_q, bar_q(t), h * 64, 0,
-                                rho0 / p.group, kvh, b);
-            }
-            for (int item = 0; item < 2 * nsteps && ok; ++item) {  // K_0, V_0, K_1, V_1, ...
-                const int slot = item % kTcStages, round = item / kTcStages;
-                ok = mbar_wait(bar_kv_empty(slot), (round & 1) ^ 1, abort_word, p.status, kTcWaitKvEmpty, p.wait_timeout_ns);
-                if (!ok) break;
-                if (item == p.debug_skip_item) continue;   // test hook: this item's barrier is never signalled
-                const CUtensorMap* map = (item & 1) ? &map_v : &map_k;
-                const int key0 = (item >> 1) * kTcKeys;
-                mbar_arrive_expect_tx(bar_kv_full(slot), kTcTileBytes);
-                for (int h = 0; h < 2; ++h)
-                    tma_load_4d(smem_base + kTcSmemRing + slot * kTcTileBytes + h * kTcHalfBytes, map, bar_kv_full(slot),
-                                h * 64, key0, kvh, b);
-            }
-            if (ok && zero_tail) {
-                const int item = 2 * nsteps - 1, slot = item % kTcStages;   // the last V tile
-                ok = mbar_wait(bar_kv_full(slot), (item / kTcStages) & 1, abort_word, p.status, kTcWaitKvFull, p.wait_timeout_ns);
-                if (ok) {
-                    // a 128-byte row of either half holds one key; the swizzle only permutes inside a row
-                    const int first = static_cast<int>(key_end - static_cast<long long>(nsteps - 1) * kTcKeys);
-                    unsigned char* tile = smem + kTcSmemRing + slot * kTcTileBytes;
-                    for (int r = first; r < kTcKeys; ++r)
-                        for (int h = 0; h < 2; ++h) {
-                            uint4* row = reinterpret_cast<uint4*>(tile + h * kTcHalfBytes + r * 128);
+            long long ring_n = 0;                   // ring items requested so far (K_0, V_0, K_1, ... of every item)
+            int q_loads[kTcTiles] = {0, 0};
+            int tails = 0;
+            TcItem it;
+            for (int round = 0; round < rounds && ok; ++round) {
+                if (!tc_item(p, round, it)) continue;
+                for (int t = 0; t < kTcTiles && ok; ++t) {
+                    if (it.steps[t] == 0) continue;
+                    // the previous item's last Q.K^T of this row tile has finished with the Q tile
+                    ok = mbar_wait(bar_q_empty(t), (q_loads[t] & 1) ^ 1, abort_word, p.status, kTcWaitQEmpty, p.wait_timeout_ns);
+                    if (!ok) break;
+                    const int rho0 = (it.pair * kTcTiles + t) * kTcTileRows;
+                    mbar_arrive_expect_tx(bar_q(t), kTcTileBytes);
+                    for (int h = 0; h < 2; ++h)
+                        tma_load_5d(smem_base + kTcSmemQ + t * kTcTileBytes + h * kTcHalfBytes, &map_q, bar_q(t), h * 64, 0,
+                                    rho0 / p.group, it.kvh, it.b);
+                    ++q_loads[t];
+                }
+                for (int item = 0; item < 2 * it.nsteps && ok; ++item, ++ring_n) {  // K_0, V_0, K_1, V_1, ...
+                    const int slot = static_cast<int>(ring_n % kTcStages);
+                    const uint32_t round_par = static_cast<uint32_t>((ring_n / kTcStages) & 1);
+                    ok = mbar_wait(bar_kv_empty(slot), round_par ^ 1, abort_word, p.status, kTcWaitKvEmpty, p.wait_timeout_ns);
+                    if (!ok) break;
+                    if (ring_n == p.debug_skip_item) continue;   // test hook: this item's barrier is never signalled
+                    const CUtensorMap* map = (item & 1) ? &map_v : &map_k;
+                    const int key0 = (it.j0 + (item >> 1)) * kTcKeys;
+                    mbar_arrive_expect_tx(bar_kv_full(slot), kTcTileBytes);
+                    for (int h = 0; h < 2; ++h)
+                        tma_load_4d(smem_base + kTcSmemRing + slot * kTcTileBytes + h * kTcHalfBytes, map, bar_kv_full(slot),
+                                    h * 64, key0, it.kvh, it.b);
+                }
+                if (ok && it.zero_tail && it.nsteps > 0) {
+                    const long long last = ring_n - 1;   // the last V tile
+                    const int slot = static_cast<int>(last % kTcStages);
+                    ok = mbar_wait(bar_kv_full(slot), static_cast<uint32_t>((last / kTcStages) & 1), abort_word, p.status, kTcWaitKvFull,
+                                   p.wait_timeout_ns);
+                    if (ok) {
+                        // a 128-byte row of either half holds one key; the swizzle only permutes inside a row
+                        const int first = static_cast<int>(it.key_end - static_cast<long long>(it.j0 + it.nsteps - 1) * kTcKeys);
+                        unsigned char* tile = smem + kTcSmemRing + slot * kTcTileBytes;
+                        for (int r = first; r < kTcKeys; ++r)
+                            for (int h = 0; h < 2; ++h) {
+                                uint4* rowp = reinterpret_cast<uint4*>(tile + h * kTcHalfBytes + r * 128);
 #pragma unroll
-                            for (int c = 0; c < 8; ++c) row[c] = make_uint4(0u, 0u, 0u, 0u);
-                        }
-                    fence_async_smem();
-                    mbar_arrive(bar_tail);
+                                for (int c = 0; c < 8; ++c) rowp[c] = make_uint4(0u, 0u, 0u, 0u);
+                            }
+                        fence_async_smem();
+                        mbar_arrive(bar_tail);
+                        ++tails;
+                    }
                 }
             }
+            if (*abort_word) {
+                // a wait ran out somewhere: copies this thread requested may still be on their way into
+                // shared memory.  Wait (bounded, quietly) for the barrier of every slot it armed last.
+                for (int s = 0; s < kTcStages; ++s) {
+                    const long long last = ring_n - 1 - ((ring_n - 1 - s) % kTcStages + kTcStages) % kTcStages;   // last item of slot s
+                    if (last >= 0 && last != p.debug_skip_item)
+                        mbar_wait_quiet(bar_kv_full(s), static_cast<uint32_t>((last / kTcStages) & 1), 200000ull);
+                }
+                for (int t = 0; t < kTcTiles; ++t)
+                    if (q_loads[t] > 0) mbar_wait_quiet(bar_q(t), static_cast<uint32_t>((q_loads[t] - 1) & 1), 200000ull);
+            }
+            (void)tails;
         }
+        __syncwarp();
     } else {
         // =============================== MMA issuer ===============================
         // One thread issues every MMA, one GEMM after the other: two issuing threads were tried and
@@ -653,53 +768,80 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
                 if (half == 1) umma_commit(bar_pv_done(t));
             };
-            // item i of the ring: K_(i/2) for even i, V_(i/2) for odd i
-            auto wait_item = [&](int item) {
-                if (zero_tail && item == 2 * nsteps - 1)   // the last V tile is released by the producer's clean-up
-                    return mbar_wait(bar_tail, 0, abort_word, p.status, kTcWaitKvFull, p.wait_timeout_ns);
-                return mbar_wait(bar_kv_full(item % kTcStages), (item / kTcStages) & 1, abort_word, p.status, kTcWaitKvFull, p.wait_timeout_ns);
-            };
-            for (int t = 0; t < kTcTiles && ok; ++t)
-                if (steps[t] > 0) ok = mbar_wait(bar_q(t), 0, abort_word, p.status, kTcWaitQ, p.wait_timeout_ns);
-            if (ok && nsteps > 0) {
-                ok = wait_item(0);
-                if (ok) {
-                    tc_fence_after();
-                    for (int t = 0; t < kTcTiles; ++t)
-                        if (steps[t] > 0) issue_qk(t, 0);
-                    umma_commit(bar_kv_empty(0));
+            long long ring_c = 0;                  // ring items of all earlier work items
+            int steps_done[kTcTiles] = {0, 0};
+            int q_loads[kTcTiles] = {0, 0};
+            int tails = 0;
+            TcItem it;
+            for (int round = 0; round < rounds && ok; ++round) {
+                if (!tc_item(p, round, it)) continue;
+                const int nsteps = it.nsteps;
+                // ring item i of this work item: K_(i/2) for even i, V_(i/2) for odd i
+                auto wait_item = [&](int item) {
+                    const long long r = ring_c + item;
+                    if (it.zero_tail && item == 2 * nsteps - 1)   // the last V tile is released by the producer's clean-up
+                        return mbar_wait(bar_tail, static_cast<uint32_t>(tails & 1), abort_word, p.status, kTcWaitKvFull, p.wait_timeout_ns);
+                    return mbar_wait(bar_kv_full(static_cast<int>(r % kTcStages)), static_cast<uint32_t>((r / kTcStages) & 1), abort_word,
+                                     p.status, kTcWaitKvFull, p.wait_timeout_ns);
+                };
+                auto slot_of = [&](int item) { return static_cast<int>((ring_c + item) % kTcStages); };
+                for (int t = 0; t < kTcTiles && ok; ++t)
+                    if (it.steps[t] > 0) ok = mbar_wait(bar_q(t), static_cast<uint32_t>(q_loads[t] & 1), abort_word, p.status, kTcWaitQ, p.wait_timeout_ns);
+                if (ok && nsteps > 0) {
+                    ok = wait_item(0);
+                    if (ok) {
+                        tc_fence_after();
+                        for (int t = 0; t < kTcTiles; ++t)
+                            if (it.steps[t] > 0) {
+                                issue_qk(t, slot_of(0));
+                                if (it.steps[t] == 1) umma_commit(bar_q_empty(t));   // this item reads Q_t no more
+                            }
+                        umma_commit(bar_kv_empty(slot_of(0)));
+                    }
                 }
-            }
-            for (int j = 0; j < nsteps && ok; ++j) {
-                const int item_v = 2 * j + 1, slot_v = item_v % kTcStages;
-                const int item_k = 2 * j + 2, slot_k = item_k % kTcStages;
-                bool have_v = false, have_k = false;
-                for (int t = 0; t < kTcTiles && ok; ++t) {
-                    if (j >= steps[t]) continue;
-                    ok = mbar_wait(bar_p_full(t), j & 1, abort_word, p.status, kTcWaitPFull, p.wait_timeout_ns);
-                    if (!ok) break;
-                    if (!have_v) {
-                        ok = wait_item(item_v);
+                for (int j = 0; j < nsteps && ok; ++j) {
+                    const int item_v = 2 * j + 1, slot_v = slot_of(item_v);
+                    const int item_k = 2 * j + 2, slot_k = slot_of(item_k);
+                    bool have_v = false, have_k = false;
+                    for (int t = 0; t < kTcTiles && ok; ++t) {
+                        if (j >= it.steps[t]) continue;
+                        ok = mbar_wait(bar_p_full(t), static_cast<uint32_t>((steps_done[t] + j) & 1), abort_word, p.status, kTcWaitPFull,
+                                       p.wait_timeout_ns);
                         if (!ok) break;
-                        have_v = true;
-                    }
-                    tc_fence_after();
-                    issue_pv_half(t, slot_v, j == 0, 0);
-                    issue_pv_half(t, slot_v, j == 0, 1);
-                    if (j + 1 < steps[t]) {
-                        if (!have_k) {
-                            ok = wait_item(item_k);
+                        if (!have_v) {
+                            ok = wait_item(item_v);
                             if (!ok) break;
-                            have_k = true;
-                            tc_fence_after();
+                            have_v = true;
                         }
-                        issue_qk(t, slot_k);
+                        tc_fence_after();
+                        issue_pv_half(t, slot_v, j == 0, 0);
+                        issue_pv_half(t, slot_v, j == 0, 1);
+                        if (j + 1 < it.steps[t]) {
+                            if (!have_k) {
+                                ok = wait_item(item_k);
+                                if (!ok) break;
+                                have_k = true;
+                                tc_fence_after();
+                            }
+                            issue_qk(t, slot_k);
+                            if (j + 2 == it.steps[t]) umma_commit(bar_q_empty(t));
+                        }
                     }
+                    if (!ok) break;
+                    umma_commit(bar_kv_empty(slot_v));                      // V_j free once every MMA so far is done
+                    if (j + 1 < nsteps) umma_commit(bar_kv_empty(slot_k));  // and K_{j+1}
                 }
                 if (!ok) break;
-                umma_commit(bar_kv_empty(slot_v));                      // V_j free once every MMA so far is done
-                if (j + 1 < nsteps) umma_commit(bar_kv_empty(slot_k));  // and K_{j+1}
+                ring_c += 2 * nsteps;
+                if (it.zero_tail && nsteps > 0) ++tails;
+                for (int t = 0; t < kTcTiles; ++t) {
+                    steps_done[t] += it.steps[t];
+                    if (it.steps[t] > 0) ++q_loads[t];
+                }
             }
+            // every MMA issued above has completed before tensor memory is given back
+            umma_commit(bar_final);
+            mbar_wait_quiet(bar_final, 0, *abort_word ? 2000000ull : p.wait_timeout_ns);
         }
         __syncwarp();
     }
@@ -707,12 +849,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // teardown: every role gets here (all waits are bounded)
     tc_fence_before();
     __syncthreads();
-    if (*abort_word) {
-        // a wait ran out: TMA copies of this CTA may still be in flight towards its shared memory;
-        // give them time to land (they take microseconds) before the CTA and its memory go away
-        for (int i = 0; i < 200; ++i) __nanosleep(1000);
-        __syncthreads();
-    }
+    if (threadIdx.x == 0) { TC_TRACE(3); TC_TRACE_NS(4); }
     if (warp == kTcTiles * 4 + 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
@@ -750,9 +887,10 @@ inline void tcgen05_plan_init(Tcgen05Plan& plan, const ellm_attn_desc& d, int sm
     plan.ready = true;
 }
 
-// AUTO picks this kernel when the chunk fills at least one 256-row CTA.
+// AUTO picks this kernel for every chunk of at least 16 packed rows (rows x query heads of a
+// group); a shorter chunk leaves more than 7/8 of a 128-row tile empty and goes to the warp-level kernel.
 inline bool tcgen05_prefers(const Tcgen05Plan& plan, size_t interval, int group) {
-    return plan.ready && interval * static_cast<size_t>(group) >= 256;
+    return plan.ready && interval * static_cast<size_t>(group) >= 16;
 }
 
 // With a uniform chunk start the K/V tensor maps are bounded at min(position_index + interval,
@@ -760,16 +898,16 @@ inline bool tcgen05_prefers(const Tcgen05Plan& plan, size_t interval, int group)
 // (positions != nullptr) they are bounded by the cache and the kernel zeroes the tail itself.
 // out_f32 != nullptr writes an fp32 partial result there instead of bf16 to d.out.
 inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, const int32_t* positions,
-                                  size_t position_index, size_t interval, size_t batch, long long key_end,
-                                  float* out_f32, float* lse, int* status, cudaStream_t stream) {
+                                  size_t position_index, size_t interval, size_t batch, long long key_begin,
+                                  long long key_end, float* out_f32, float* lse, int* status, cudaStream_t stream) {
     if (!plan.ready) return ELLM_ERR_UNSUPPORTED;
     const int group = static_cast<int>(d.q_heads / d.kv_heads);
     // per-sequence chunk starts: the maps can only be bounded by the cache itself
     long long kv_rows = positions ? static_cast<long long>(d.max_seq) : static_cast<long long>(position_index + interval);
     if (kv_rows > key_end) kv_rows = key_end;
     if (kv_rows > static_cast<long long>(d.max_seq)) kv_rows = static_cast<long long>(d.max_seq);
-    if (kv_rows <= 0) {
-        snprintf(plan.why, sizeof(plan.why), "empty key window");
+    if (kv_rows <= 0 || key_begin < 0 || (positions && key_begin != 0)) {
+        snprintf(plan.why, sizeof(plan.why), "empty key window, or a window start together with per-sequence positions");
         return ELLM_ERR_UNSUPPORTED;
     }
     EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(plan.encode);
@@ -811,6 +949,7 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
     plan.cached_q = d.q;
     TcParams p;
     p.out = out_f32 ? static_cast<void*>(out_f32) : d.out;
+    p.key_begin = key_begin;
     p.key_end = kv_rows;
     p.lse = lse;
     p.status = status;
@@ -827,11 +966,16 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
     p.group = group;
     p.pair_tiles = static_cast<int>((interval * group + kTcTiles * kTcTileRows - 1) / (kTcTiles * kTcTileRows));
     p.scale_log2 = d.scale * kLog2e;
-    const unsigned long long ctas = static_cast<unsigned long long>(p.pair_tiles) * p.kv_heads * p.batch;
-    if (ctas > 0x7fffffffull) {
+    const unsigned long long items = static_cast<unsigned long long>(p.pair_tiles) * p.kv_heads * p.batch;
+    if (items > 0x7fffffffull) {
         snprintf(plan.why, sizeof(plan.why), "too many row tiles for one launch");
         return ELLM_ERR_UNSUPPORTED;
     }
+    p.n_items = static_cast<long long>(items);
+    // One CTA per SM walking the item list (no second wave that starts from nothing, the set-up paid
+    // once), or one CTA per item taken by the hardware in block order.
+    const bool persistent = plan.persistent < 0 ? true : plan.persistent != 0;
+    const unsigned long long ctas = persistent ? std::min<unsigned long long>(items, static_cast<unsigned long long>(plan.sm_count)) : items;
     // K and V rows this launch can touch, all heads and sequences together
     const unsigned long long kv_bytes = 2ull * static_cast<unsigned long long>(kv_rows) * 256ull * d.kv_heads * batch;
     p.pair_major = kv_bytes <= (96ull << 20) ? 1 : 0;

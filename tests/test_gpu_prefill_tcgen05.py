@@ -56,8 +56,11 @@ def test_auto_picks_tcgen05_for_large_chunks_and_warp_mma_for_small():
     big.gpu()
     assert big.last_stats["prefill_tcgen05"][0] == 1
     small = Case(seed=1, interval=16, batch=1, q_heads=2, kv_heads=2, max_seq=32)
-    small.gpu()
-    assert small.last_stats["prefill_warp_mma"][0] == 1
+    small.gpu()   # 16 packed rows per KV head are enough for a tensor-memory tile
+    assert small.last_stats["prefill_tcgen05"][0] == 1 and small.last_stats["prefill_warp_mma"][0] == 0
+    tiny = Case(seed=1, interval=15, batch=1, q_heads=2, kv_heads=2, max_seq=32)
+    tiny.gpu()
+    assert tiny.last_stats["prefill_warp_mma"][0] == 1
     ragged = Case(seed=1, interval=256, batch=2, q_heads=2, kv_heads=2, max_seq=600, positions=[0, 300])
     ragged.gpu()   # per-sequence chunk starts stay on the tcgen05 kernel
     assert ragged.last_stats["prefill_tcgen05"][0] == 1
@@ -119,6 +122,103 @@ def test_tcgen05_prefill_per_sequence_chunk_starts(positions, interval, q_heads,
     case = Case(seed=900 + interval, interval=interval, batch=len(positions), q_heads=q_heads, kv_heads=kv_heads,
                 max_seq=max(positions) + interval + 70, positions=positions, max_batch=len(positions) + 1)
     _check(case)
+
+
+@pytest.mark.parametrize("interval,position_index", [(2, 0), (63, 0), (64, 0), (65, 0), (127, 0), (129, 0), (17, 40), (64, 64)])
+@pytest.mark.parametrize("q_heads,kv_heads", [(4, 4), (8, 1), (16, 2)])
+def test_auto_never_picks_the_warp_level_kernel_from_16_packed_rows_up(interval, position_index, q_heads, kv_heads):
+    """The shape sweep of the warp-level kernel's own test, left to the automatic choice: every chunk
+    with at least 16 packed rows (rows x query heads per KV head) runs on the tensor-memory kernel."""
+    case = Case(seed=200 + interval, interval=interval, batch=2, q_heads=q_heads, kv_heads=kv_heads,
+                max_seq=position_index + interval + 5, position_index=position_index)
+    want_k, want_v, want_o, want_l = case.oracle()
+    got_k, got_v, got_o, got_l = case.gpu()
+    assert_cache_bit_exact(got_k, got_v, want_k, want_v)
+    assert_attention_close(case, got_o, got_l, want_o, want_l)
+    name = "prefill_tcgen05" if interval * (q_heads // kv_heads) >= 16 else "prefill_warp_mma"
+    assert case.last_stats[name][0] == 1
+
+
+@pytest.mark.parametrize("interval,pos", [(40, 300), (300, 1000), (16, 127)])
+def test_key_windows_that_start_past_key_zero(interval, pos):
+    """Windows [0,a), [a,b), [b,inf) with a, b in the middle of 128-key tiles, on the tensor-memory
+    kernel: their merged partials equal the unsplit result; rows that see no key of a window give
+    an empty partial (O = 0, LSE = -inf)."""
+    from helpers import from_bits
+    dev = torch.device("cuda:0")
+    case = Case(seed=70 + interval, interval=interval, batch=2, q_heads=8, kv_heads=2, max_seq=pos + interval,
+                position_index=pos, poison=False)
+    want_k, want_v, want_o, want_l = case.oracle()
+    q = case.q.to(dev)
+    ck = from_bits(want_k).view(2, 2, case.max_seq, 128).to(dev)
+    cv = from_bits(want_v).view(2, 2, case.max_seq, 128).to(dev)
+    out = torch.zeros_like(q)
+    op = ellm_b200.Attention.new(q, ck, cv, out, 2, 8, 2, 128, case.strides, case.scale, max_seq=case.max_seq,
+                                 max_interval=interval, prefill_kernel=L.PREFILL_TCGEN05)
+    windows = [(0, 100), (100, pos + interval // 2), (pos + interval // 2, 1 << 40)]
+    po = torch.full((len(windows), interval, 2, 8, 128), float("nan"), dtype=torch.float32, device=dev)
+    pl = torch.full((len(windows), interval, 2, 8), float("nan"), dtype=torch.float32, device=dev)
+    for i, (a, b) in enumerate(windows):
+        op.run_window(pos, interval, 2, a, b, po[i], pl[i])
+    assert op.kernel_stats()["prefill_tcgen05"][0] == len(windows)
+    # rows before the last window's start see none of its keys
+    empty = interval // 2
+    assert (po[2, :empty] == 0).all() and (pl[2, :empty] == float("-inf")).all()
+    rows = interval * 2 * 8
+    lse = torch.zeros(rows, dtype=torch.float32, device=dev)
+    ellm_b200.merge_partials(po.view(len(windows), rows, 128), pl.view(len(windows), rows), out, lse)
+    torch.cuda.synchronize()
+    assert_attention_close(case, bits(out), lse.view(interval, 2, 8).cpu().numpy(), want_o, want_l)
+
+
+def test_one_cta_per_sm_and_one_cta_per_item_give_the_same_bits():
+    """The work-item list walked by one CTA per SM (several items per CTA, barrier phases carried
+    from item to item) against one CTA per item: 2 sequences x 4 KV heads x 24 row-tile pairs = 192
+    items on 148 SMs, ragged steps per item."""
+    dev = torch.device("cuda:0")
+    S, B, Hq, Hkv = 768, 2, 32, 4
+    g = torch.Generator().manual_seed(123)
+    q = torch.randn(S, B, Hq, 128, generator=g).to(torch.bfloat16).to(dev)
+    k = torch.randn(B, Hkv, S, 128, generator=g).to(torch.bfloat16).to(dev)
+    v = torch.randn(B, Hkv, S, 128, generator=g).to(torch.bfloat16).to(dev)
+    outs = []
+    for mode in (1, 0):
+        out = torch.zeros_like(q)
+        lse = torch.zeros(S, B, Hq, dtype=torch.float32, device=dev)
+        op = ellm_b200.Attention.new(q, k, v, out, B, Hq, Hkv, 128, [Hkv * S * 128, S * 128, 128, 1], 0.088, max_seq=S,
+                                     max_interval=S, lse=lse, prefill_kernel=L.PREFILL_TCGEN05)
+        op.set_option("tc_persistent", mode)
+        op.run(0, S, B, 1, 0)
+        outs.append((out, lse))
+        op.close()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert torch.isfinite(outs[0][0].float()).all()
+
+
+def test_device_wait_timeout_on_an_enqueue_only_handle_shows_in_check():
+    """A handle created with async = 1 only enqueues, so its run call cannot report a device-side
+    wait that ran out; ellm_attn_check does, and clears the condition."""
+    dev = torch.device("cuda:0")
+    case = Case(seed=78, interval=256, batch=1, q_heads=1, kv_heads=1, max_seq=256, position_index=0, poison=False)
+    _, _, want_o, want_l = case.oracle()
+    q, ck, cv = case.q.to(dev), case.cache_k.to(dev), case.cache_v.to(dev)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(256, 1, 1, dtype=torch.float32, device=dev)
+    op = ellm_b200.Attention.new(q, ck, cv, out, 1, 1, 1, 128, case.strides, case.scale, max_seq=256, max_interval=256,
+                                 lse=lse, k_new=case.k_new.to(dev), v_new=case.v_new.to(dev), prefill_kernel=L.PREFILL_TCGEN05,
+                                 async_=True)
+    op.check()                                           # nothing enqueued yet
+    op.set_option("tc_wait_timeout_ns", 200_000_000)
+    op.set_option("tc_debug_skip_kv_item", 0)            # the first K tile never arrives
+    op.run(0, 256, 1, 1, 0)                              # returns at once, no error yet
+    with pytest.raises(ellm_b200.EllmError) as e:
+        op.check()
+    assert e.value.status == L.ERR_DEVICE_TIMEOUT
+    op.set_option("tc_debug_skip_kv_item", -1)
+    op.run(0, 256, 1, 1, 0)
+    op.check()                                           # cleared: the good run passes
+    assert_attention_close(case, bits(out), lse.cpu().numpy(), want_o, want_l)
+    op.close()
 
 
 def test_device_wait_timeout_is_reported_and_the_context_stays_usable():
