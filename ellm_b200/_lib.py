@@ -80,6 +80,15 @@ _SIGNATURES = {
     "ellm_attn_merge_partials_list": (_I, [C.POINTER(_VP), C.POINTER(_VP), _SZ, _SZ, _SZ, _VP, _I, _VP, _I, _VP]),
     "ellm_attn_check": (_I, [_VP]),
     "ellm_attn_decode_noalloc": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _SZ, _SZ, _SZ, _SZ, _SZ, C.POINTER(_SZ), _SZ, C.c_float, _I, _VP]),
+    "ellm_stream_create": (_I, [_I, C.POINTER(_VP)]),
+    "ellm_stream_destroy": (_I, [_I, _VP]),
+    "ellm_stream_synchronize": (_I, [_I, _VP]),
+    "ellm_positions_set": (_I, [_VP, _SZ, C.c_int32, _I, _I, _VP]),
+    "ellm_step_graph_begin": (_I, [_I, _VP]),
+    "ellm_step_graph_end": (_I, [_I, _VP, C.POINTER(_VP)]),
+    "ellm_step_graph_launch": (_I, [_VP, _VP]),
+    "ellm_step_graph_nodes": (_I, [_VP, C.POINTER(_SZ)]),
+    "ellm_step_graph_destroy": (_I, [_VP]),
     "ellm_attn_set_option": (_I, [_VP, C.c_char_p, C.c_longlong]),
     "ellm_attn_set_profiling": (_I, [_VP, _I]),
     "ellm_attn_kernel_stats": (_I, [_VP, _I, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_double)]),

@@ -973,6 +973,117 @@ int ellm_attn_merge_partials_list(const float* const* o_parts, const float* cons
     return ELLM_OK;
 }
 
+// ---- what a host without CUDA bindings needs to run a step asynchronously or as a graph ----
+namespace ellm {
+__global__ void positions_update_kernel(int32_t* positions, int count, int32_t value, int add) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) positions[i] = add ? positions[i] + value : value;
+}
+}  // namespace ellm
+
+struct ellm_step_graph {
+    int device = 0;
+    cudaGraphExec_t exec = nullptr;
+    size_t nodes = 0;
+};
+
+int ellm_stream_create(int device, void** stream) {
+    if (!stream) return fail(ELLM_ERR_INVALID_ARG, "stream is NULL");
+    *stream = nullptr;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    cudaStream_t s = nullptr;
+    ELLM_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *stream = s;
+    return ELLM_OK;
+}
+
+int ellm_stream_destroy(int device, void* stream) {
+    if (!stream) return ELLM_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    ELLM_CUDA(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
+    return ELLM_OK;
+}
+
+int ellm_stream_synchronize(int device, void* stream) {
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    ELLM_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    return ELLM_OK;
+}
+
+int ellm_positions_set(int32_t* positions, size_t count, int32_t value, int add, int device, void* stream) {
+    if (!positions) return fail(ELLM_ERR_INVALID_ARG, "positions is NULL");
+    if (count == 0) return ELLM_OK;
+    if (count > 0x7fffffffull) return fail(ELLM_ERR_INVALID_ARG, "count too large");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    const unsigned blocks = static_cast<unsigned>((count + 127) / 128);
+    ELLM_CUDA(launch_dependent(ellm::positions_update_kernel, blocks, 128, 0, static_cast<cudaStream_t>(stream), positions,
+                               static_cast<int>(count), value, add));
+    return ELLM_OK;
+}
+
+int ellm_step_graph_begin(int device, void* stream) {
+    if (!stream) return fail(ELLM_ERR_INVALID_ARG, "a step can only be captured on a stream made by ellm_stream_create (not the default stream)");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    ELLM_CUDA(cudaStreamBeginCapture(static_cast<cudaStream_t>(stream), cudaStreamCaptureModeThreadLocal));
+    return ELLM_OK;
+}
+
+int ellm_step_graph_end(int device, void* stream, ellm_step_graph** out) {
+    if (!out) return fail(ELLM_ERR_INVALID_ARG, "out is NULL");
+    *out = nullptr;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", device);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(static_cast<cudaStream_t>(stream), &graph);
+    if (e != cudaSuccess || !graph) {
+        cudaGetLastError();
+        return fail(ELLM_ERR_CUDA, "the capture of the step failed: %s (an operator that synchronises or copies "
+                    "inside run() cannot be captured: create the operators with async = 1)", cudaGetErrorString(e));
+    }
+    ellm_step_graph* g = new (std::nothrow) ellm_step_graph();
+    if (!g) { cudaGraphDestroy(graph); return fail(ELLM_ERR_NO_MEMORY, "host allocation failed"); }
+    g->device = device;
+    cudaGraphGetNodes(graph, nullptr, &g->nodes);
+    const cudaError_t ei = cudaGraphInstantiate(&g->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ei != cudaSuccess) {
+        delete g;
+        cudaGetLastError();
+        return fail(ELLM_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(ei));
+    }
+    *out = g;
+    return ELLM_OK;
+}
+
+int ellm_step_graph_launch(ellm_step_graph* g, void* stream) {
+    if (!g || !g->exec) return fail(ELLM_ERR_INVALID_ARG, "graph is NULL");
+    DeviceGuard guard(g->device);
+    if (!guard.ok) return fail(ELLM_ERR_CUDA, "cannot select device %d", g->device);
+    ELLM_CUDA(cudaGraphLaunch(g->exec, static_cast<cudaStream_t>(stream)));
+    return ELLM_OK;
+}
+
+int ellm_step_graph_nodes(const ellm_step_graph* g, size_t* nodes) {
+    if (!g || !nodes) return fail(ELLM_ERR_INVALID_ARG, "graph and nodes must be non-NULL");
+    *nodes = g->nodes;
+    return ELLM_OK;
+}
+
+int ellm_step_graph_destroy(ellm_step_graph* g) {
+    if (!g) return ELLM_OK;
+    DeviceGuard guard(g->device);
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    delete g;
+    return ELLM_OK;
+}
+
 int ellm_attn_set_option(ellm_attn* h, const char* name, long long value) {
     if (!h || !name) return fail(ELLM_ERR_INVALID_ARG, "handle and name must be non-NULL");
     std::lock_guard<std::mutex> lock(h->mu);

@@ -14,6 +14,8 @@
 //   ellm::start(...)                serving::start::start src/serving/start.rs:18-86
 //   ellm::start_generation(...)     the prompt-chunk / decode stepping the reference keeps in
 //                                   src/serving/start copy.rs:84-110 (not compiled there)
+//   ellm::start_generation_async(...) the same stepping with the operators enqueued on one stream,
+//                                   one wait per step, decode steps replayed from a CUDA graph
 //
 // Errors: the reference aborts (panic = "abort"); here a non-zero status becomes a
 // std::runtime_error carrying ellm_last_error().
@@ -123,6 +125,14 @@ class Attention {
         check(ellm_attn_run(handle_, position_index, position_interval, batch_size, cpu_num, thread_id));
     }
 
+    // Extension: sequence b starts its chunk at positions[b] (device int32[batch_size]).
+    void run_ragged(const int32_t* positions, size_t position_interval, size_t batch_size, size_t cpu_num,
+                    size_t thread_id) const {
+        check(ellm_attn_run_ragged(handle_, positions, position_interval, batch_size, cpu_num, thread_id));
+    }
+    // For async operators: waits for the stream and throws if a device-side wait ran out since the last check.
+    void check_device() const { check(ellm_attn_check(handle_)); }
+
     ellm_attn* handle() const { return handle_; }
 
   private:
@@ -204,6 +214,11 @@ class MatMul3 {
     void run(size_t position_index, size_t position_interval, size_t batch_size, size_t cpu_num, size_t thread_id) const {
         check(ellm_matmul3_run(handle_, position_index, position_interval, batch_size, cpu_num, thread_id));
     }
+    void run_ragged(const int32_t* positions, size_t position_interval, size_t batch_size, size_t cpu_num,
+                    size_t thread_id) const {
+        check(ellm_matmul3_run_ragged(handle_, positions, position_interval, batch_size, cpu_num, thread_id));
+    }
+    void check_device() const { check(ellm_matmul_check(handle_, 0)); }
 
   private:
     MatMul3() = default;
@@ -242,6 +257,11 @@ class MatMulAdd {
     void run(size_t position_index, size_t position_interval, size_t batch_size, size_t cpu_num, size_t thread_id) const {
         check(ellm_matmul_add_run(handle_, position_index, position_interval, batch_size, cpu_num, thread_id));
     }
+    // the product does not depend on the positions: the same rows as run()
+    void run_ragged(const int32_t*, size_t position_interval, size_t batch_size, size_t cpu_num, size_t thread_id) const {
+        run(0, position_interval, batch_size, cpu_num, thread_id);
+    }
+    void check_device() const { check(ellm_matmul_check(handle_, 1)); }
 
   private:
     MatMulAdd() = default;
@@ -253,19 +273,37 @@ class MatMulAdd {
 class Operator {
   public:
     using Run = std::function<void(size_t, size_t, size_t, size_t, size_t)>;
+    using RunRagged = std::function<void(const int32_t*, size_t, size_t, size_t, size_t)>;
+    using Check = std::function<void()>;
     explicit Operator(Run run) : run_(std::move(run)) {}
-    // takes ownership of an operator object with a run(position_index, position_interval, batch, cpus, tid)
+    // takes ownership of an operator object with a run(position_index, position_interval, batch, cpus, tid);
+    // the device operators of this header also bring run_ragged (positions in device memory) and
+    // check_device, which the asynchronous executor below needs
     template <class Op>
     static Operator own(Op&& op) {
         auto held = std::make_shared<std::decay_t<Op>>(std::forward<Op>(op));
-        return Operator([held](size_t p, size_t n, size_t b, size_t c, size_t t) { held->run(p, n, b, c, t); });
+        Operator o([held](size_t p, size_t n, size_t b, size_t c, size_t t) { held->run(p, n, b, c, t); });
+        o.run_ragged_ = [held](const int32_t* pos, size_t n, size_t b, size_t c, size_t t) { held->run_ragged(pos, n, b, c, t); };
+        o.check_ = [held] { held->check_device(); };
+        return o;
     }
     void run(size_t position_index, size_t position_interval, size_t batch_size, size_t cpu_num, size_t thread_id) const {
         run_(position_index, position_interval, batch_size, cpu_num, thread_id);
     }
+    bool device_operator() const { return static_cast<bool>(run_ragged_); }
+    void run_ragged(const int32_t* positions, size_t position_interval, size_t batch_size, size_t cpu_num,
+                    size_t thread_id) const {
+        if (!run_ragged_) throw std::logic_error("this operator has no form with positions in device memory");
+        run_ragged_(positions, position_interval, batch_size, cpu_num, thread_id);
+    }
+    void check_device() const {
+        if (check_) check_();
+    }
 
   private:
     Run run_;
+    RunRagged run_ragged_;
+    Check check_;
 };
 
 // Arrival counter + generation word; waiters spin on the generation.
@@ -382,6 +420,111 @@ void start_generation(std::vector<Op>& operator_queue, size_t prompt_length, siz
         }
         for (size_t s = 0; s < decode_steps; ++s) step(position++, 1);
     });
+}
+
+// What the asynchronous executor needs: the one stream every operator of the queue was created on
+// (ellm_stream_create, async = true in the operators' options) and, for graph decode, a device
+// array of `batch_size` int32 positions (ellm_device_alloc) that it owns while it runs.
+struct AsyncOptions {
+    int device = 0;
+    void* stream = nullptr;
+    int32_t* positions = nullptr;   // device int32[batch_size]; required for graph_decode
+    bool graph_decode = true;       // decode steps: capture the operator queue once, replay it per step
+};
+
+// start_generation without a host barrier per operator.  The operators only enqueue on one stream
+// (in queue order, by thread 0; the other threads' run() calls return at once, as always), and the
+// threads meet ONE barrier per step, after thread 0 has waited for the stream and checked every
+// operator's device status - in place of the barrier after each operator of
+// src/serving/start.rs:69-73.  With graph_decode the first decode step runs like that (it also
+// warms every kernel up), then one step's operator queue - every operator in its run_ragged form,
+// reading the sequences' positions from opt.positions, followed by the update positions += 1 - is
+// captured into a CUDA graph, and every further decode step is one launch of that graph.
+// before_step(position, interval) runs on thread 0 before a step is enqueued (stage the step's
+// input), after_step(position, interval) on thread 0 after the step's wait (fetch its output).
+// Every operator of the queue must be a device operator (Operator::own of this header's classes).
+template <class Op, class BeforeStep, class AfterStep>
+void start_generation_async(std::vector<Op>& operator_queue, size_t prompt_length, size_t sequence_chunk_size,
+                            size_t decode_steps, size_t batch_size, BeforeStep before_step, AfterStep after_step,
+                            const AsyncOptions& opt, size_t thread_num = 0) {
+    if (!opt.stream) throw std::invalid_argument("start_generation_async needs a stream from ellm_stream_create");
+    const bool use_graph = opt.graph_decode && decode_steps > 1;
+    if (use_graph && !opt.positions) throw std::invalid_argument("graph decode needs AsyncOptions::positions");
+    for (auto& op : operator_queue)
+        if (!op.device_operator()) throw std::invalid_argument("start_generation_async: host-side operator in the queue");
+    ellm_step_graph* graph = nullptr;
+    try {
+        detail::spmd(thread_num, [&](size_t tid, size_t threads, Barrier& barrier, std::exception_ptr& err) {
+            auto guarded = [&](auto&& f) {
+                try {
+                    if (!err) f();
+                } catch (...) {
+                    err = std::current_exception();
+                }
+            };
+            auto finish = [&](size_t position, size_t interval) {   // one wait and one barrier per step
+                if (tid == 0)
+                    guarded([&] {
+                        check(ellm_stream_synchronize(opt.device, opt.stream));
+                        for (auto& op : operator_queue) op.check_device();
+                        after_step(position, interval);
+                    });
+                barrier.wait();
+            };
+            auto eager_step = [&](size_t position, size_t interval, bool ragged) {
+                if (tid == 0) guarded([&] { before_step(position, interval); });
+                for (auto& op : operator_queue)
+                    guarded([&] {
+                        if (ragged) op.run_ragged(opt.positions, interval, batch_size, threads, tid);
+                        else op.run(position, interval, batch_size, threads, tid);
+                    });
+                finish(position, interval);
+            };
+            size_t position = 0;
+            while (position < prompt_length) {
+                const size_t interval = std::min(sequence_chunk_size, prompt_length - position);
+                eager_step(position, interval, false);
+                position += interval;
+            }
+            if (!use_graph) {
+                for (size_t s = 0; s < decode_steps; ++s) eager_step(position++, 1, false);
+                return;
+            }
+            // first decode step: enqueued operator by operator, positions taken from the device array
+            if (tid == 0)
+                guarded([&] { check(ellm_positions_set(opt.positions, batch_size, static_cast<int32_t>(position), 0, opt.device, opt.stream)); });
+            eager_step(position++, 1, true);
+            if (tid == 0)
+                guarded([&] {
+                    check(ellm_positions_set(opt.positions, batch_size, 1, 1, opt.device, opt.stream));
+                    // record one step; nothing runs until the graph is launched
+                    check(ellm_step_graph_begin(opt.device, opt.stream));
+                    try {
+                        for (auto& op : operator_queue) op.run_ragged(opt.positions, 1, batch_size, 1, 0);
+                        check(ellm_positions_set(opt.positions, batch_size, 1, 1, opt.device, opt.stream));
+                    } catch (...) {
+                        ellm_step_graph* dropped = nullptr;
+                        ellm_step_graph_end(opt.device, opt.stream, &dropped);
+                        ellm_step_graph_destroy(dropped);
+                        throw;
+                    }
+                    check(ellm_step_graph_end(opt.device, opt.stream, &graph));
+                });
+            barrier.wait();
+            for (size_t s = 1; s < decode_steps; ++s, ++position) {
+                if (tid == 0)
+                    guarded([&] {
+                        before_step(position, 1);
+                        check(ellm_step_graph_launch(graph, opt.stream));
+                    });
+                finish(position, 1);
+            }
+        });
+    } catch (...) {
+        ellm_step_graph_destroy(graph);
+        throw;
+    }
+    ellm_step_graph_destroy(graph);
 }
 
 }  // namespace ellm

@@ -224,6 +224,33 @@ int ellm_attn_merge_partials_list(const float* const* o_parts, const float* cons
  * operator; same role as ellm_matmul_check for the projections. */
 int ellm_attn_check(ellm_attn* h);
 
+/* ---- Running a whole step without a host barrier per operator ----------------------------------
+ * The reference's executor meets a barrier after every operator (src/serving/start.rs:69-73).
+ * On a device the operators of a step can instead be enqueued back to back on one stream by
+ * handles created with async = 1, with one wait per step - or, for decode steps, captured once
+ * into a CUDA graph and replayed, every operator taking the sequences' positions from a device
+ * array that the graph itself advances (ellm_attn_run_ragged / ellm_matmul3_run_ragged).  These
+ * entry points give a host that has no CUDA binding of its own what it needs for that: a stream,
+ * the wait, the position array's update, and the capture.  The stepping they serve is the one
+ * the reference keeps in src/serving/start copy.rs:84-110.
+ *
+ * ellm_positions_set: positions[i] = value (add == 0) or positions[i] += value (add != 0) for
+ * i < count, on the stream.  ellm_step_graph_begin .. ellm_step_graph_end bracket the run calls
+ * of one step on `stream` (made by ellm_stream_create; every operator of the step must be an
+ * async = 1 handle on that stream and must have run at least once before, outside a capture);
+ * nothing executes in between, the calls are recorded.  ellm_step_graph_launch replays them. */
+typedef struct ellm_step_graph ellm_step_graph;
+int ellm_stream_create(int device, void** stream);
+int ellm_stream_destroy(int device, void* stream);
+int ellm_stream_synchronize(int device, void* stream);
+int ellm_positions_set(int32_t* positions, size_t count, int32_t value, int add, int device,
+                       void* stream);
+int ellm_step_graph_begin(int device, void* stream);
+int ellm_step_graph_end(int device, void* stream, ellm_step_graph** out);
+int ellm_step_graph_launch(ellm_step_graph* graph, void* stream);
+int ellm_step_graph_nodes(const ellm_step_graph* graph, size_t* nodes);   /* kernels recorded */
+int ellm_step_graph_destroy(ellm_step_graph* graph);
+
 /* Counters for the benchmark: kernels launched by this handle since creation, and
  * per-kernel device time when profiling is on (events around each launch). */
 typedef enum ellm_kernel_id {

@@ -38,6 +38,17 @@ def test_cpp_layer_through_operator_queue(tmp_path):
         assert "V rows off 0" in res.stdout
 
 
+def test_cpp_async_executor_eight_layers_graph_decode(tmp_path):
+    """8 layers x 32 decode steps through start_generation_async: one wait per step instead of a
+    barrier per operator, decode steps operator by operator and as a replayed CUDA graph - same
+    bits both ways, and within the stack's tolerance of the oracle."""
+    exe = _build(tmp_path, "async_layers_test")
+    for threads in ("1", "4"):
+        res = subprocess.run([exe, threads, "8", "32"], capture_output=True, text=True, timeout=600)
+        assert res.returncode == 0, res.stdout + res.stderr
+        assert "same bits" in res.stdout
+
+
 def test_cpp_executor_spmd_generation(tmp_path):
     exe = _build(tmp_path, "executor_test")
     for threads in ("1", "7"):
