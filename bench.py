@@ -435,10 +435,38 @@ def sharded_extra(rank, world, dev):
     return out
 
 
+def cpp_stack_decode():
+    """The same decode step driven from compiled host code: tests/cpp/stack_decode_bench.cpp (the C++
+    host mirror's asynchronous executor, one CUDA graph per step) built with g++ and run as a child
+    process.  Returns its JSON line, or {"unavailable": why}."""
+    import shutil
+    import tempfile
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    gxx = shutil.which("g++")
+    if not gxx:
+        return {"unavailable": "no g++ on this box"}
+    try:
+        with tempfile.TemporaryDirectory() as tmp:
+            exe = os.path.join(tmp, "stack_decode_bench")
+            subprocess.run([gxx, "-std=c++17", "-O2", "-pthread", os.path.join(ROOT, "tests", "cpp", "stack_decode_bench.cpp"),
+                            "-I", os.path.join(ROOT, "include"), "-I", os.path.join(cuda, "include"),
+                            "-L", os.path.join(ROOT, "ellm_b200"), "-lellm_attn", "-L", os.path.join(cuda, "lib64"), "-lcudart",
+                            "-Wl,-rpath," + os.path.join(ROOT, "ellm_b200"), "-Wl,-rpath," + os.path.join(cuda, "lib64"), "-o", exe],
+                           check=True, capture_output=True, text=True, timeout=300)
+            res = subprocess.run([exe, "48", "32768", "256", "1"], capture_output=True, text=True, timeout=300)
+            if res.returncode != 0:
+                return {"unavailable": "stack_decode_bench failed: " + (res.stderr or res.stdout)[-300:]}
+            return json.loads(res.stdout.strip().splitlines()[-1])
+    except (subprocess.SubprocessError, OSError, ValueError) as e:
+        return {"unavailable": f"{type(e).__name__}: {str(e)[-300:]}"}
+
+
 def stack_extra(dev):
     """BASELINE configs[3]: 48-layer attention-only stack, 32768-token prefill then 256 decode steps."""
     from ellm_b200 import stack
     res = stack.measure(device=f"cuda:{dev.index}")
+    torch.cuda.empty_cache()
+    res["cpp_executor_decode"] = cpp_stack_decode()
     burst, sustained, src = measured_tensor_peaks()
     hbm, hsrc = measured_peaks()
     res["prefill_frac_of_sustained_peak"] = res["prefill_tflops"] / sustained
@@ -493,7 +521,8 @@ def main():
     positions = lens.to(dev)
     op = Attention.new(q, cache.k[0], cache.v[0], out, BATCH, HQ, HKV, D, cache.strides, SCALE,
                        max_seq=MAX_SEQ, max_interval=1, lse=lse, k_new=k_new, v_new=v_new,
-                       device=local, stream=stream.cuda_stream, async_=True)
+                       device=local, stream=stream.cuda_stream, async_=True,
+                       early_stream=True)   # the steps run back to back on resident inputs: nothing writes the positions
     total_bytes, kernel_bytes = algorithmic_bytes(lens)
 
     def step():

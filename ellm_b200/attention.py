@@ -29,7 +29,7 @@ class Attention:
     def new(cls, q_ptr, k_ptr, v_ptr, output_ptr, batch_size, attention_head_num, kv_head_num,
             head_size, kv_strides, inverse_sqrt_head, *, max_seq, max_interval=1, lse=None,
             k_new=None, v_new=None, device=0, stream=None, async_=False,
-            prefill_kernel=L.PREFILL_AUTO):
+            prefill_kernel=L.PREFILL_AUTO, early_stream=False):
         self = object.__new__(cls)
         lib = L.load()
         d = L.AttnDesc()
@@ -46,6 +46,8 @@ class Attention:
         handle = C.c_void_p()
         L.check(lib.ellm_attn_create(C.byref(d), C.byref(handle)))
         self._lib, self._h, self.desc = lib, handle, d
+        if early_stream:   # see "decode_early_stream" in ellm_attn.h: the caller vouches for what precedes a decode step
+            L.check(lib.ellm_attn_set_option(handle, b"decode_early_stream", 1))
         # keep the buffers alive as long as the operator (the reference leaks them instead)
         self._keep = (q_ptr, k_ptr, v_ptr, output_ptr, lse, k_new, v_new)
         return self

@@ -61,6 +61,11 @@ struct DecodeParams {
     const __nv_bfloat16* v_new = nullptr;
     __nv_bfloat16* k_cache_w = nullptr;
     __nv_bfloat16* v_cache_w = nullptr;
+    // Early streaming (opt-in, see ellm_attn_set_option "decode_early_stream"): the tile table is
+    // built and the first K/V stages are requested BEFORE the wait for the stream's previous kernel.
+    // Only what that kernel cannot have written is touched early: the positions, and cache rows
+    // below each sequence's newest row; the queries and the stages that hold a newest row wait.
+    int early = 0;
 };
 
 // CTA index owning tile t under assign_range(total, n, .)
@@ -128,13 +133,20 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
     // wrote the positions, the queries and the newest cache row); a no-op for an ordinary launch.
     // Only then let the dependent grid (the merge) be set up: whatever it does before its own wait
     // - it rebuilds the tile table from the positions - then sees everything this grid sees.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // With early streaming the wait comes later, after the first stages have been requested.
+    bool waited = p.early == 0;
+    if (waited) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     dec_build_prefix(p, prefix, lens);
     const long long segs_per_seq = static_cast<long long>(p.kv_heads) * p.gtiles;
     const long long total = static_cast<long long>(prefix[p.batch]) * segs_per_seq;
     long long t_begin, t_end;
-    if (!assign_range(total, p.num_ctas, blockIdx.x, &t_begin, &t_end)) return;
+    if (!assign_range(total, p.num_ctas, blockIdx.x, &t_begin, &t_end)) {
+        if (!waited) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        return;
+    }
 
     const int r0 = lane >> 2;  // this thread's rows: r0 and r0 + 8
     long long t = t_begin;
@@ -206,10 +218,30 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
                 }
             }
         };
+        int s_first = 0;
+        if (!waited) {
+            // the CTA's first piece: request ahead of the wait whatever cannot hold a row the
+            // previous kernel writes (a sequence's newest row, at len - 1), stage by stage in order
+#pragma unroll
+            for (int s = 0; s < kDecStages - 1; ++s) {
+                const long long kfirst = key0 + static_cast<long long>(s) * kDecTileKeys;
+                const bool safe = s < ntiles && (len - 1 < kfirst || len - 1 >= kfirst + 16);
+                if (s == s_first && safe) {
+                    issue(s);
+                    cp_async_commit();
+                    ++s_first;
+                }
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+            waited = true;
+        }
 #pragma unroll
         for (int s = 0; s < kDecStages - 1; ++s) {
-            if (s < ntiles) issue(s);
-            cp_async_commit();
+            if (s >= s_first) {
+                if (s < ntiles) issue(s);
+                cp_async_commit();
+            }
         }
 
         // ---- Q fragments: rows = query heads kvh*group + gt*16 + r ----

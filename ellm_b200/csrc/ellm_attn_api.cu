@@ -149,8 +149,10 @@ struct ellm_attn {
     int group = 1, gtiles = 1;
     int dec_ctas = 0;
     size_t slots = 0;
-    float* part_o = nullptr;
-    float* part_lse = nullptr;
+    float* part_o = nullptr;           // two copies of the split-KV workspace, used in turn: a step's merge may
+    float* part_lse = nullptr;         // still read one while the next step's decode kernel fills the other
+    unsigned part_turn = 0;
+    int decode_early = 0;              // ellm_attn_set_option("decode_early_stream")
     int32_t* positions_dev = nullptr;  // staging for ellm_attn_run_host
     int* status_dev = nullptr;         // bounded-wait status word written by the tcgen05 kernel
     int* status_host = nullptr;        // pinned mirror
@@ -259,15 +261,17 @@ int launch_append(ellm_attn* h, cudaStream_t stream, void* k_cache, void* v_cach
 // partial output of the windowed form.
 int launch_decode(ellm_attn* h, const int32_t* positions, size_t position_index, size_t batch,
                   long long key_begin, long long key_end, float* out_f32, float* lse_out, bool append,
-                  void* out_override = nullptr) {
+                  void* out_override = nullptr, bool early = false) {
     if (batch > static_cast<size_t>(ellm::kDecMaxBatch))
         return fail(ELLM_ERR_UNSUPPORTED, "decode batch %zu exceeds %d", batch, ellm::kDecMaxBatch);
     ellm::DecodeParams p;
     p.q = static_cast<const __nv_bfloat16*>(h->d.q);
     p.k_cache = static_cast<const __nv_bfloat16*>(h->d.k_cache);
     p.v_cache = static_cast<const __nv_bfloat16*>(h->d.v_cache);
-    p.part_o = h->part_o;
-    p.part_lse = h->part_lse;
+    h->part_turn ^= 1u;
+    p.part_o = h->part_o + (h->part_turn ? h->slots * 16 * ellm::kHeadDim : 0);
+    p.part_lse = h->part_lse + (h->part_turn ? h->slots * 16 : 0);
+    p.early = early ? 1 : 0;
     p.positions = positions;
     long long len = static_cast<long long>(position_index) + 1;
     if (len > key_end) len = key_end;
@@ -419,8 +423,10 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
         if (rc) return rc;
     }
     if (interval == 1) {
+        // early streaming only where the caller vouched for it, and never for a step whose inputs the
+        // library itself stages right before (the host-buffer entry point passes a stream override)
         rc = launch_decode(h, positions, position_index, batch, key_begin, key_end, out_f32, lse_out, do_append,
-                           decode_out_override);
+                           decode_out_override, h->decode_early != 0 && stream_override == nullptr);
     } else {
         bool use_tc = false;
         if (h->d.prefill_kernel == ELLM_PREFILL_TCGEN05) use_tc = true;
@@ -493,8 +499,8 @@ int ellm_attn_create(const ellm_attn_desc* desc, ellm_attn** out) {
         ellm_attn_destroy(h);
         return status;
     };
-    if (cudaMalloc(&h->part_o, h->slots * 16 * ellm::kHeadDim * sizeof(float)) != cudaSuccess ||
-        cudaMalloc(&h->part_lse, h->slots * 16 * sizeof(float)) != cudaSuccess ||
+    if (cudaMalloc(&h->part_o, 2 * h->slots * 16 * ellm::kHeadDim * sizeof(float)) != cudaSuccess ||
+        cudaMalloc(&h->part_lse, 2 * h->slots * 16 * sizeof(float)) != cudaSuccess ||
         cudaMalloc(&h->positions_dev, desc->max_batch * sizeof(int32_t)) != cudaSuccess ||
         cudaMalloc(&h->status_dev, sizeof(int)) != cudaSuccess ||
         cudaMallocHost(&h->status_host, sizeof(int)) != cudaSuccess) {
@@ -976,8 +982,8 @@ int ellm_attn_merge_partials_list(const float* const* o_parts, const float* cons
 // ---- what a host without CUDA bindings needs to run a step asynchronously or as a graph ----
 namespace ellm {
 __global__ void positions_update_kernel(int32_t* positions, int count, int32_t value, int add) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < count) positions[i] = add ? positions[i] + value : value;
 }
@@ -1095,6 +1101,10 @@ int ellm_attn_set_option(ellm_attn* h, const char* name, long long value) {
     if (std::strcmp(name, "decode_ctas") == 0) {   // grid of the decode kernel: 1 .. 2 x SMs (the workspace is sized for that)
         if (value < 1 || value > 2 * h->sm_count) return fail(ELLM_ERR_INVALID_ARG, "decode_ctas must be in [1, %d]", 2 * h->sm_count);
         h->dec_ctas = static_cast<int>(value);
+        return ELLM_OK;
+    }
+    if (std::strcmp(name, "decode_early_stream") == 0) {
+        h->decode_early = value != 0;
         return ELLM_OK;
     }
     if (std::strcmp(name, "tc_persistent") == 0) {

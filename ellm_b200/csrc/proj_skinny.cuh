@@ -112,10 +112,12 @@ __global__ void __launch_bounds__(kSkThreads, 1) proj_skinny_kernel(const Skinny
     // fused head epilogue: a CTA's shared memory may be written by its cluster peers only once it runs;
     // every CTA says so here and checks the others just before the exchange
     if (p.heads != 0) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    // the next kernel of the stream may start its own prologue now
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // activations (and the residual) are the previous kernels' output: wait for them
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // only now may the next kernel of the stream start its own prologue: whatever it reads before
+    // its own wait (a decode kernel with early streaming: the positions, older cache rows) is then
+    // older than everything this kernel waited for
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (p.input_norm_eps >= 0.0f) {
         // the layer's input norm, y = x / (sqrt(mean x^2) + eps) rounded to bf16, on the few rows
         // of a decode step (src/kernel/generic/rms_norm.rs:6-26); the same code as rms_norm_kernel

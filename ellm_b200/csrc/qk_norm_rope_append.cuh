@@ -37,8 +37,8 @@ struct NormRopeParams {
 __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(const NormRopeParams p) {
     // programmatic dependent launches: the next kernel may be set up now; this one waits for the
     // kernel before it (the projection that wrote its input) - both no-ops for ordinary launches
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // after the wait: see proj_skinny.cuh
     const int lane = threadIdx.x & 31;
     const int heads = p.q_heads + 2 * p.kv_heads;
     const long long total = static_cast<long long>(p.interval) * p.batch * heads;

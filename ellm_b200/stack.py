@@ -74,7 +74,10 @@ class AttentionStack:
             ck, cv = self.cache.layer(i)
             self.ops.append(Attention.new(self.q, ck, cv, self.a, max_batch, q_heads, kv_heads, head_dim,
                                           self.cache.strides, self.scale, max_seq=max_seq, max_interval=max_interval,
-                                          device=dev_index, stream=raw_stream, async_=True))
+                                          device=dev_index, stream=raw_stream, async_=True,
+                                          # what precedes a decode step's attention here (the projection kernel, or the
+                                          # norm + rope + append kernel) writes only Q and each sequence's newest cache row
+                                          early_stream=True))
             if self.own_projections:
                 # the layer's input norm rides inside the projection operator
                 self.qkv_ops.append(MatMul3.new(self.x, self.wq[i], self.q, self.wk[i], ck, self.wv[i], cv, self.rope,

@@ -66,6 +66,8 @@ struct DeviceOptions {
     void* stream = nullptr;        // cudaStream_t
     bool async = false;            // false: run() returns after the stream drained (barrier semantics)
     int prefill_kernel = ELLM_PREFILL_AUTO;
+    bool early_stream = false;     // "decode_early_stream" of ellm_attn_set_option: the caller vouches that the
+                                   // kernel before a decode step writes only Q and each sequence's newest cache row
 };
 
 // T is the element type of the buffers; only 16-bit bf16 storage is implemented.
@@ -103,6 +105,7 @@ class Attention {
         d.prefill_kernel = opt.prefill_kernel;
         Attention a;
         check(ellm_attn_create(&d, &a.handle_));
+        if (opt.early_stream) check(ellm_attn_set_option(a.handle_, "decode_early_stream", 1));
         return a;
     }
 
@@ -430,6 +433,11 @@ struct AsyncOptions {
     void* stream = nullptr;
     int32_t* positions = nullptr;   // device int32[batch_size]; required for graph_decode
     bool graph_decode = true;       // decode steps: capture the operator queue once, replay it per step
+    size_t start_position = 0;      // tokens already in the cache: the first step starts here
+    size_t check_every = 64;        // decode steps between two status checks of all operators (each check
+                                    // reads a word back from the device per operator; a device-side wait
+                                    // that ran out took seconds, so it is reported soon enough); prompt
+                                    // chunks and the last step are always checked
 };
 
 // start_generation without a host barrier per operator.  The operators only enqueue on one stream
@@ -462,32 +470,35 @@ void start_generation_async(std::vector<Op>& operator_queue, size_t prompt_lengt
                     err = std::current_exception();
                 }
             };
-            auto finish = [&](size_t position, size_t interval) {   // one wait and one barrier per step
+            auto finish = [&](size_t position, size_t interval, bool check_status = true) {   // one wait and one barrier per step
                 if (tid == 0)
                     guarded([&] {
                         check(ellm_stream_synchronize(opt.device, opt.stream));
-                        for (auto& op : operator_queue) op.check_device();
+                        if (check_status)
+                            for (auto& op : operator_queue) op.check_device();
                         after_step(position, interval);
                     });
                 barrier.wait();
             };
-            auto eager_step = [&](size_t position, size_t interval, bool ragged) {
+            auto due = [&](size_t s) { return s + 1 == decode_steps || opt.check_every <= 1 || (s + 1) % opt.check_every == 0; };
+            auto eager_step = [&](size_t position, size_t interval, bool ragged, bool check_status = true) {
                 if (tid == 0) guarded([&] { before_step(position, interval); });
                 for (auto& op : operator_queue)
                     guarded([&] {
                         if (ragged) op.run_ragged(opt.positions, interval, batch_size, threads, tid);
                         else op.run(position, interval, batch_size, threads, tid);
                     });
-                finish(position, interval);
+                finish(position, interval, check_status);
             };
-            size_t position = 0;
-            while (position < prompt_length) {
-                const size_t interval = std::min(sequence_chunk_size, prompt_length - position);
+            size_t position = opt.start_position;
+            const size_t prompt_end = opt.start_position + prompt_length;
+            while (position < prompt_end) {
+                const size_t interval = std::min(sequence_chunk_size, prompt_end - position);
                 eager_step(position, interval, false);
                 position += interval;
             }
             if (!use_graph) {
-                for (size_t s = 0; s < decode_steps; ++s) eager_step(position++, 1, false);
+                for (size_t s = 0; s < decode_steps; ++s) eager_step(position++, 1, false, due(s));
                 return;
             }
             // first decode step: enqueued operator by operator, positions taken from the device array
@@ -517,7 +528,7 @@ void start_generation_async(std::vector<Op>& operator_queue, size_t prompt_lengt
                         before_step(position, 1);
                         check(ellm_step_graph_launch(graph, opt.stream));
                     });
-                finish(position, 1);
+                finish(position, 1, due(s));
             }
         });
     } catch (...) {

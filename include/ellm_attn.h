@@ -321,6 +321,17 @@ int ellm_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_c
  *   "tc_debug_skip_kv_item" test hook for that path: the kernel's loader never fetches ring item
  *                           N (0 = first K tile, 1 = first V tile, ...) so the wait on it runs
  *                           out; -1 (default) = off.  The context stays usable afterwards.
+ *   "decode_early_stream"   1: a decode step's kernel builds its tile table and requests its first K/V
+ *                           rows before it waits for the stream's previous kernel, so that its start
+ *                           overlaps that kernel's end.  The caller vouches that the previous kernel in
+ *                           the stream writes neither the positions nor cache rows below each sequence's
+ *                           newest row, and (if it is not one of this library's) that it was itself
+ *                           ordered after whatever does.  True for the decode steps of a layer stack -
+ *                           the projection before attention writes only Q and the newest row - and for
+ *                           back-to-back steps on resident inputs; default 0.  ellm_attn_run_host never
+ *                           uses it (its staging kernel writes the positions).
+ *   "tc_persistent"         prefill kernel: -1 (default) / 1 one CTA per SM walking the work-item list,
+ *                           0 one CTA per item; a tuning knob.
  *   "decode_ctas"           grid of the decode kernel, 1 .. 2 x SMs (default 2 x SMs, for which the
  *                           workspace is sized); a tuning knob.
  * Unknown names return ELLM_ERR_INVALID_ARG.  The reference has no counterpart (it aborts). */

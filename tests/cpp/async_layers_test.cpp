@@ -111,7 +111,7 @@ int main(int argc, char** argv) {
         ellm::ProjectionOptions popt;
         popt.max_batch = B; popt.stream = stream; popt.async = true;
         ellm::DeviceOptions aopt;
-        aopt.max_seq = max_seq; aopt.max_interval = chunk; aopt.stream = stream; aopt.async = true;
+        aopt.max_seq = max_seq; aopt.max_interval = chunk; aopt.stream = stream; aopt.async = true; aopt.early_stream = true;
         std::vector<ellm::Operator> queue;
         for (size_t l = 0; l < layers; ++l) {
             void *dk = nullptr, *dv = nullptr;

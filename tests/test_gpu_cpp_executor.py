@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _build(tmp_path, name):
+def _build(tmp_path, name, with_oracle=True):
     ellm_b200.load()
     oracle.load()
     cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
@@ -47,6 +47,18 @@ def test_cpp_async_executor_eight_layers_graph_decode(tmp_path):
         res = subprocess.run([exe, threads, "8", "32"], capture_output=True, text=True, timeout=600)
         assert res.returncode == 0, res.stdout + res.stderr
         assert "same bits" in res.stdout
+
+
+def test_cpp_stack_decode_bench_runs(tmp_path):
+    """The C++ timing program of the stack's decode step (the benchmark runs it at 48 layers and a
+    32768-token context) on a small geometry, both as a replayed graph and operator by operator."""
+    import json
+    exe = _build(tmp_path, "stack_decode_bench")
+    for graph in ("1", "0"):
+        res = subprocess.run([exe, "4", "2048", "12", graph], capture_output=True, text=True, timeout=300)
+        assert res.returncode == 0, res.stdout + res.stderr
+        line = json.loads(res.stdout.strip().splitlines()[-1])
+        assert line["finite"] and line["timed_steps"] == 10 and 0 < line["tpot_ms"] < 50
 
 
 def test_cpp_executor_spmd_generation(tmp_path):
