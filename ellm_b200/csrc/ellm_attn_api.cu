@@ -154,7 +154,8 @@ struct ellm_attn {
     unsigned part_turn = 0;
     int decode_early = 0;              // ellm_attn_set_option("decode_early_stream")
     int32_t* positions_dev = nullptr;  // staging for ellm_attn_run_host
-    int* status_dev = nullptr;         // bounded-wait status word written by the tcgen05 kernel
+    int* status_dev = nullptr;         // bounded-wait status word written by the tcgen05 kernel; two more words behind it
+                                       // are the prefill kernel's work-list counters
     int* status_host = nullptr;        // pinned mirror
     ellm::Tcgen05Plan tc;              // tensor maps etc. of the tcgen05 prefill kernel
     std::mutex mu;
@@ -374,7 +375,7 @@ int finish(ellm_attn* h, bool enqueue_only) {
     if (h->status_host && *h->status_host != 0) {
         const int code = *h->status_host;
         *h->status_host = 0;
-        cudaMemsetAsync(h->status_dev, 0, sizeof(int), h->stream);
+        cudaMemsetAsync(h->status_dev, 0, 4 * sizeof(int), h->stream);   // the status word and the work-list counters
         return fail(ELLM_ERR_DEVICE_TIMEOUT, "a bounded device-side wait ran out (code %d)", code);
     }
     return ELLM_OK;
@@ -502,17 +503,18 @@ int ellm_attn_create(const ellm_attn_desc* desc, ellm_attn** out) {
     if (cudaMalloc(&h->part_o, 2 * h->slots * 16 * ellm::kHeadDim * sizeof(float)) != cudaSuccess ||
         cudaMalloc(&h->part_lse, 2 * h->slots * 16 * sizeof(float)) != cudaSuccess ||
         cudaMalloc(&h->positions_dev, desc->max_batch * sizeof(int32_t)) != cudaSuccess ||
-        cudaMalloc(&h->status_dev, sizeof(int)) != cudaSuccess ||
+        cudaMalloc(&h->status_dev, 4 * sizeof(int)) != cudaSuccess ||
         cudaMallocHost(&h->status_host, sizeof(int)) != cudaSuccess) {
         cudaGetLastError();
         return cleanup(fail(ELLM_ERR_NO_MEMORY, "workspace allocation failed (%zu slots)", h->slots));
     }
     *h->status_host = 0;
-    if (cudaMemset(h->status_dev, 0, sizeof(int)) != cudaSuccess) return cleanup(fail(ELLM_ERR_CUDA, "memset failed"));
+    if (cudaMemset(h->status_dev, 0, 4 * sizeof(int)) != cudaSuccess) return cleanup(fail(ELLM_ERR_CUDA, "memset failed"));
     if (cudaFuncSetAttribute(ellm::decode_splitkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kDecSmemBytes) != cudaSuccess ||
         cudaFuncSetAttribute(ellm::prefill_warp_mma_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kPfSmemBytes) != cudaSuccess ||
         cudaFuncSetAttribute(ellm::prefill_warp_mma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kPfSmemBytes) != cudaSuccess)
         return cleanup(fail(ELLM_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(cudaGetLastError())));
+    h->tc.sched = h->status_dev + 2;
     ellm::tcgen05_plan_init(h->tc, h->d, h->sm_count);  // leaves tc.ready false (with a reason) when it cannot serve this handle
     if (desc->prefill_kernel == ELLM_PREFILL_TCGEN05 && !h->tc.ready) {
         fail(ELLM_ERR_UNSUPPORTED, "tcgen05 prefill requested but unavailable: %s", h->tc.why);
@@ -736,7 +738,7 @@ int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
     if (*h->status_host != 0) {
         const int code = *h->status_host;
         *h->status_host = 0;
-        cudaMemsetAsync(h->status_dev, 0, sizeof(int), h->stream);
+        cudaMemsetAsync(h->status_dev, 0, 4 * sizeof(int), h->stream);
         return fail(ELLM_ERR_DEVICE_TIMEOUT, "a bounded device-side wait ran out (code %d)", code);
     }
     return ELLM_OK;

@@ -66,6 +66,7 @@ struct Tcgen05Plan {
     unsigned long long wait_timeout_ns = 2000000000ull;   // ellm_attn_set_option("tc_wait_timeout_ns")
     int debug_skip_item = -1;                              // ellm_attn_set_option("tc_debug_skip_kv_item")
     int persistent = -1;                                   // ellm_attn_set_option("tc_persistent"): -1 auto, 0 one CTA per item, 1 one CTA per SM
+    int* sched = nullptr;                                  // the item counter and the exit counter of the one-CTA-per-SM form (the handle's)
 };
 
 struct TcParams {
@@ -78,6 +79,8 @@ struct TcParams {
     long long key_begin;    // rows attend keys [key_begin, min(position + 1, key_end)); key_end for a uniform chunk start only
     long long key_end;
     long long n_items;      // 256-row work items of the launch = pair_tiles * kv_heads * batch
+    int* sched;             // two device words, zero between launches: [0] items handed out beyond the first
+                            // one per CTA, [1] CTAs that have finished; nullptr = one item per CTA (grid = n_items)
     long long max_seq;      // rows per (sequence, kv head) in the cache
     int interval, batch, max_batch;
     int q_heads, kv_heads, group;
@@ -289,7 +292,7 @@ __device__ long long g_tc_trace[1024 * 64];
 
 // Status codes written by a wait that ran out (which wait gave up).
 enum { kTcWaitQ = 1, kTcWaitKvFull = 2, kTcWaitKvEmpty = 3, kTcWaitSFull = 4, kTcWaitPFull = 5, kTcWaitPvDone = 6,
-       kTcWaitQEmpty = 7 };
+       kTcWaitQEmpty = 7, kTcWaitSched = 8 };
 
 // One work item: 256 packed rows (two 128-row tiles) of one (sequence, KV head).
 struct TcItem {
@@ -305,14 +308,10 @@ struct TcItem {
 
 // The items are numbered heaviest first: later row tiles have more keys.  When all heads' K/V fit
 // in L2 together the order is heaviest-first over the whole launch, else head by head so that one
-// head's K/V stays resident while its row tiles are worked off.  A CTA takes item
-// round * gridDim.x + (its index, counted from the other end in odd rounds): with weights that fall
-// along the list the two directions even out, and a grid as large as the list gives every CTA one item.
-__device__ __forceinline__ bool tc_item(const TcParams& p, int round, TcItem& it) {
-    const long long grid = gridDim.x;
-    const long long idx = static_cast<long long>(round) * grid +
-                          ((round & 1) ? grid - 1 - static_cast<long long>(blockIdx.x) : static_cast<long long>(blockIdx.x));
-    if (idx >= p.n_items) return false;
+// head's K/V stays resident while its row tiles are worked off.  A CTA starts with item blockIdx.x
+// and then takes the next item nobody has taken yet (a device counter): long items first, short
+// ones fill the ends, whatever the items turn out to cost.
+__device__ __forceinline__ void tc_item(const TcParams& p, long long idx, TcItem& it) {
     const int heads = p.kv_heads * p.batch;
     int head;
     if (p.pair_major) {
@@ -349,7 +348,6 @@ __device__ __forceinline__ bool tc_item(const TcParams& p, int round, TcItem& it
     // sequence's end, so the last V tile may carry rows past key_end that hold anything; their P
     // is 0 but 0 * NaN is NaN, so the producer zeroes them before the MMA may read the tile.
     it.zero_tail = p.positions != nullptr && static_cast<long long>(it.j0 + it.nsteps) * kTcKeys > it.key_end;
-    return true;
 }
 
 // A wait of the teardown: bounded, sets no status.
@@ -389,10 +387,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     auto bar_q_empty = [&](int t) { return bar0 + 8u * (8 + 2 * kTcStages + t); };
     const uint32_t bar_tail = bar0 + 8u * (10 + 2 * kTcStages);
     const uint32_t bar_final = bar0 + 8u * (11 + 2 * kTcStages);
-    constexpr int kNumBars = 12 + 2 * kTcStages;
-    static_assert(8 * kNumBars + 16 <= 256, "the barrier block is 256 bytes");
+    auto bar_sched_full = [&](int s) { return bar0 + 8u * (12 + 2 * kTcStages + s); };    // the item list's two-slot mailbox
+    auto bar_sched_empty = [&](int s) { return bar0 + 8u * (14 + 2 * kTcStages + s); };
+    constexpr int kNumBars = 16 + 2 * kTcStages;
+    static_assert(8 * kNumBars + 24 <= 256, "the barrier block is 256 bytes");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kTcSmemBar + 8 * kNumBars);
     volatile int* abort_word = reinterpret_cast<volatile int*>(smem + kTcSmemBar + 8 * kNumBars + 8);
+    volatile int* sched_idx = reinterpret_cast<volatile int*>(smem + kTcSmemBar + 8 * kNumBars + 16);   // [2]
 
     if (threadIdx.x == 0) {
         for (int t = 0; t < kTcTiles; ++t) {
@@ -408,6 +409,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         mbar_init(bar_tail, 1);
         mbar_init(bar_final, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_sched_full(i), 1);
+            mbar_init(bar_sched_empty(i), 1 + kTcTiles * 4);   // the MMA thread and every softmax warp
+        }
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -426,7 +431,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) TC_TRACE(2);
     const int total_rows = p.interval * p.group;
-    const int rounds = static_cast<int>((p.n_items + gridDim.x - 1) / gridDim.x);
+    const int n_items = static_cast<int>(p.n_items);
+    // the k-th item of this CTA as the producer publishes it (n_items = no more)
+    auto take_item = [&](long long k, bool& ok, int code) -> int {
+        ok = mbar_wait(bar_sched_full(static_cast<int>(k & 1)), static_cast<uint32_t>((k >> 1) & 1), abort_word, p.status, code, p.wait_timeout_ns);
+        const int idx = ok ? sched_idx[k & 1] : n_items;
+        return idx;
+    };
 
     // Every role walks the same list of items.  What carries over from one item to the next are the
     // barriers' phases, so each role counts what it has pushed through them so far: ring items,
@@ -442,8 +453,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         bool ok = true;
         TcItem it;
         int n_traced = 0;
-        for (int round = 0; round < rounds && ok; ++round) {
-            if (!tc_item(p, round, it)) continue;
+        for (long long k = 0; ok; ++k) {
+            int idx = n_items;
+            if (lane == 0) idx = take_item(k, ok, kTcWaitSched);
+            idx = __shfl_sync(0xffffffffu, idx, 0);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            if (lane == 0) mbar_arrive(bar_sched_empty(static_cast<int>(k & 1)));
+            if (idx >= n_items) break;
+            tc_item(p, idx, it);
             const int tr = 8 + 8 * n_traced + 4 * t;   // trace slots of this item and tile
             ++n_traced;
             const int rho = (it.pair * kTcTiles + t) * kTcTileRows + row;
@@ -676,8 +694,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             int q_loads[kTcTiles] = {0, 0};
             int tails = 0;
             TcItem it;
-            for (int round = 0; round < rounds && ok; ++round) {
-                if (!tc_item(p, round, it)) continue;
+            for (long long k = 0; ok; ++k) {
+                // this CTA's k-th item: its own block index first, then whatever comes next on the list
+                long long idx = blockIdx.x;
+                if (k > 0) idx = p.sched ? static_cast<long long>(gridDim.x) + atomicAdd(p.sched, 1) : p.n_items;
+                if (idx > p.n_items) idx = p.n_items;
+                ok = mbar_wait(bar_sched_empty(static_cast<int>(k & 1)), static_cast<uint32_t>(((k >> 1) & 1) ^ 1), abort_word, p.status,
+                               kTcWaitSched, p.wait_timeout_ns);
+                if (!ok) break;
+                sched_idx[k & 1] = static_cast<int>(idx);
+                mbar_arrive(bar_sched_full(static_cast<int>(k & 1)));   // releases the word above to the waiters
+                if (idx >= p.n_items) break;
+                tc_item(p, idx, it);
                 for (int t = 0; t < kTcTiles && ok; ++t) {
                     if (it.steps[t] == 0) continue;
                     // the previous item's last Q.K^T of this row tile has finished with the Q tile
@@ -773,8 +801,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             int q_loads[kTcTiles] = {0, 0};
             int tails = 0;
             TcItem it;
-            for (int round = 0; round < rounds && ok; ++round) {
-                if (!tc_item(p, round, it)) continue;
+            for (long long k = 0; ok; ++k) {
+                const int idx = take_item(k, ok, kTcWaitSched);
+                if (!ok) break;
+                mbar_arrive(bar_sched_empty(static_cast<int>(k & 1)));
+                if (idx >= n_items) break;
+                tc_item(p, idx, it);
                 const int nsteps = it.nsteps;
                 // ring item i of this work item: K_(i/2) for even i, V_(i/2) for odd i
                 auto wait_item = [&](int item) {
@@ -850,6 +882,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0) { TC_TRACE(3); TC_TRACE_NS(4); }
+    if (threadIdx.x == 0 && p.sched) {
+        // the last CTA to leave puts the two words back to zero for the next launch
+        __threadfence();
+        if (atomicAdd(p.sched + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+            p.sched[0] = 0;
+            p.sched[1] = 0;
+            __threadfence();
+        }
+    }
     if (warp == kTcTiles * 4 + 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
@@ -974,8 +1015,9 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
     p.n_items = static_cast<long long>(items);
     // One CTA per SM walking the item list (no second wave that starts from nothing, the set-up paid
     // once), or one CTA per item taken by the hardware in block order.
-    const bool persistent = plan.persistent < 0 ? true : plan.persistent != 0;
+    const bool persistent = plan.sched != nullptr && (plan.persistent < 0 ? true : plan.persistent != 0);
     const unsigned long long ctas = persistent ? std::min<unsigned long long>(items, static_cast<unsigned long long>(plan.sm_count)) : items;
+    p.sched = persistent ? plan.sched : nullptr;
     // K and V rows this launch can touch, all heads and sequences together
     const unsigned long long kv_bytes = 2ull * static_cast<unsigned long long>(kv_rows) * 256ull * d.kv_heads * batch;
     p.pair_major = kv_bytes <= (96ull << 20) ? 1 : 0;
