@@ -418,7 +418,18 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
     const bool no_sync = enqueue_only < 0 ? h->d.async != 0 : enqueue_only != 0;
     int rc;
     const bool do_append = append && h->d.k_new;
-    if (do_append && interval > 1) {   // a decode step appends inside its own kernel
+    // which kernel takes a chunk of more than one row
+    bool use_tc = false;
+    if (interval > 1) {
+        if (h->d.prefill_kernel == ELLM_PREFILL_TCGEN05) use_tc = true;
+        else if (h->d.prefill_kernel == ELLM_PREFILL_AUTO) use_tc = ellm::tcgen05_prefers(h->tc, interval, h->group);
+    }
+    // the chunk's K/V rows go into the cache inside the attention kernel where that is possible (a decode
+    // step always does; the tensor-memory prefill kernel when the chunk starts on a key-tile boundary),
+    // else by the append kernel first
+    const bool fused = use_tc && do_append && !out_f32 &&
+                       ellm::tcgen05_can_fuse_append(h->tc, h->d, positions, position_index, batch, key_begin, key_end);
+    if (do_append && interval > 1 && !fused) {
         rc = launch_append(h, h->stream, h->d.k_cache, h->d.v_cache, h->d.k_new, h->d.v_new, h->d.kv_strides,
                            h->d.max_batch, h->d.kv_heads, h->d.max_seq, position_index, positions, interval, batch);
         if (rc) return rc;
@@ -429,16 +440,13 @@ int run_impl(ellm_attn* h, const int32_t* positions, size_t position_index, size
         rc = launch_decode(h, positions, position_index, batch, key_begin, key_end, out_f32, lse_out, do_append,
                            decode_out_override, h->decode_early != 0 && stream_override == nullptr);
     } else {
-        bool use_tc = false;
-        if (h->d.prefill_kernel == ELLM_PREFILL_TCGEN05) use_tc = true;
-        else if (h->d.prefill_kernel == ELLM_PREFILL_AUTO) use_tc = ellm::tcgen05_prefers(h->tc, interval, h->group);
         if (use_tc) {
             if (!h->tc.ready)
                 return fail(ELLM_ERR_UNSUPPORTED, "tcgen05 prefill unavailable for this handle: %s", h->tc.why);
             {
                 LaunchScope ls(h, ELLM_KERNEL_PREFILL_TCGEN05);
                 rc = ellm::launch_prefill_tcgen05(h->tc, h->d, positions, position_index, interval, batch, key_begin, key_end,
-                                                  out_f32, lse_out, h->status_dev, h->stream);
+                                                  out_f32, lse_out, h->status_dev, h->stream, fused);
             }
             if (rc == ELLM_ERR_UNSUPPORTED) return fail(rc, "tcgen05 prefill: %s", h->tc.why);
             if (rc) return fail(rc, "tcgen05 prefill launch failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -1107,6 +1115,10 @@ int ellm_attn_set_option(ellm_attn* h, const char* name, long long value) {
     }
     if (std::strcmp(name, "decode_early_stream") == 0) {
         h->decode_early = value != 0;
+        return ELLM_OK;
+    }
+    if (std::strcmp(name, "tc_fuse_append") == 0) {
+        h->tc.fuse_append = value != 0;
         return ELLM_OK;
     }
     if (std::strcmp(name, "tc_persistent") == 0) {

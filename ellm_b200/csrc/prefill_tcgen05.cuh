@@ -59,13 +59,15 @@ struct Tcgen05Plan {
     void* encode = nullptr;  // cuTensorMapEncodeTiled, fetched from the driver at run time
     int sm_count = 0;
     // the tensor maps of the last launch, reused when the next one has the same geometry
-    CUtensorMap map_q, map_k, map_v;
+    CUtensorMap map_q, map_k, map_v, map_kn, map_vn;
+    bool cached_fused = false;
     size_t cached_interval = 0, cached_batch = 0;
     long long cached_kv_rows = -1;
     const void* cached_q = nullptr;
     unsigned long long wait_timeout_ns = 2000000000ull;   // ellm_attn_set_option("tc_wait_timeout_ns")
     int debug_skip_item = -1;                              // ellm_attn_set_option("tc_debug_skip_kv_item")
     int persistent = -1;                                   // ellm_attn_set_option("tc_persistent"): -1 auto, 0 one CTA per item, 1 one CTA per SM
+    int fuse_append = 1;                                   // ellm_attn_set_option("tc_fuse_append"): 0 keeps the separate append kernel
     int* sched = nullptr;                                  // the item counter and the exit counter of the one-CTA-per-SM form (the handle's)
 };
 
@@ -155,6 +157,16 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
 }
+
+// shared -> global tile store of the same box shape (rows past the map's bound are dropped)
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -360,10 +372,13 @@ __device__ __noinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity, unsi
     }
 }
 
-template <typename OutT>
+// kFused: the chunk's own K/V rows come from k_new / v_new and are written into the cache here (a
+// separate instantiation, so that the plain kernel carries none of its state).
+template <typename OutT, bool kFused>
 __global__ void __launch_bounds__(kTcThreads, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_kn,
+                       const __grid_constant__ CUtensorMap map_vn, const TcParams p) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -374,6 +389,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+        if (kFused) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kn) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_vn) : "memory");
+        }
     }
 
     // barriers (8 bytes each) and two words behind them
@@ -693,6 +712,27 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             long long ring_n = 0;                   // ring items requested so far (K_0, V_0, K_1, ... of every item)
             int q_loads[kTcTiles] = {0, 0};
             int tails = 0;
+            // fused append: tiles waiting to be stored into the cache, per ring slot
+            bool store_pending[kTcStages] = {};
+            long long store_ring[kTcStages] = {};
+            int store_key0[kTcStages] = {};
+            int store_head[kTcStages] = {};
+            // waits until the slot's tile has landed, stores it to the cache rows it holds and waits until the
+            // store has read the slot (so that the slot can be refilled)
+            auto flush_store = [&](int slot) -> bool {
+                const long long r = store_ring[slot];
+                if (!mbar_wait(bar_kv_full(slot), static_cast<uint32_t>((r / kTcStages) & 1), abort_word, p.status, kTcWaitKvFull, p.wait_timeout_ns))
+                    return false;
+                const int hd = store_head[slot];
+                const CUtensorMap* map = (hd >> 30) ? &map_v : &map_k;
+                for (int h = 0; h < 2; ++h)
+                    tma_store_4d(map, smem_base + kTcSmemRing + slot * kTcTileBytes + h * kTcHalfBytes, h * 64, store_key0[slot],
+                                 hd & 0xffff, (hd >> 16) & 0x3fff);
+                bulk_commit();
+                bulk_wait_read_all();
+                store_pending[slot] = false;
+                return true;
+            };
             TcItem it;
             for (long long k = 0; ok; ++k) {
                 // this CTA's k-th item: its own block index first, then whatever comes next on the list
@@ -721,15 +761,40 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int item = 0; item < 2 * it.nsteps && ok; ++item, ++ring_n) {  // K_0, V_0, K_1, V_1, ...
                     const int slot = static_cast<int>(ring_n % kTcStages);
                     const uint32_t round_par = static_cast<uint32_t>((ring_n / kTcStages) & 1);
+                    if constexpr (kFused) {
+                        // a tile of the chunk's own rows that waits in this slot to be written into the cache
+                        // goes out first (it landed long ago: the slot has been consumed since)
+                        if (store_pending[slot]) ok = flush_store(slot);
+                        if (!ok) break;
+                    }
                     ok = mbar_wait(bar_kv_empty(slot), round_par ^ 1, abort_word, p.status, kTcWaitKvEmpty, p.wait_timeout_ns);
                     if (!ok) break;
                     if (ring_n == p.debug_skip_item) continue;   // test hook: this item's barrier is never signalled
-                    const CUtensorMap* map = (item & 1) ? &map_v : &map_k;
                     const int key0 = (it.j0 + (item >> 1)) * kTcKeys;
-                    mbar_arrive_expect_tx(bar_kv_full(slot), kTcTileBytes);
-                    for (int h = 0; h < 2; ++h)
-                        tma_load_4d(smem_base + kTcSmemRing + slot * kTcTileBytes + h * kTcHalfBytes, map, bar_kv_full(slot),
-                                    h * 64, key0, it.kvh, it.b);
+                    if constexpr (kFused) {
+                        // Key tiles at or past the chunk's start hold the chunk's own rows, which are not in the
+                        // cache yet - they come from k_new / v_new (row = key - chunk start).  Exactly one item
+                        // writes such a tile into the cache: the one whose rows include the tile's first token.
+                        const bool from_new = key0 >= p.base;
+                        const CUtensorMap* map = from_new ? ((item & 1) ? &map_vn : &map_kn) : ((item & 1) ? &map_v : &map_k);
+                        const int row0 = from_new ? key0 - static_cast<int>(p.base) : key0;
+                        mbar_arrive_expect_tx(bar_kv_full(slot), kTcTileBytes);
+                        for (int h = 0; h < 2; ++h)
+                            tma_load_4d(smem_base + kTcSmemRing + slot * kTcTileBytes + h * kTcHalfBytes, map, bar_kv_full(slot),
+                                        h * 64, row0, it.kvh, it.b);
+                        if (from_new && (static_cast<long long>(row0 / kTcKeys) * p.group) / 2 == it.pair) {
+                            store_pending[slot] = true;
+                            store_ring[slot] = ring_n;
+                            store_key0[slot] = key0;
+                            store_head[slot] = it.kvh | (it.b << 16) | ((item & 1) << 30);
+                        }
+                    } else {
+                        const CUtensorMap* map = (item & 1) ? &map_v : &map_k;
+                        mbar_arrive_expect_tx(bar_kv_full(slot), kTcTileBytes);
+                        for (int h = 0; h < 2; ++h)
+                            tma_load_4d(smem_base + kTcSmemRing + slot * kTcTileBytes + h * kTcHalfBytes, map, bar_kv_full(slot),
+                                        h * 64, key0, it.kvh, it.b);
+                    }
                 }
                 if (ok && it.zero_tail && it.nsteps > 0) {
                     const long long last = ring_n - 1;   // the last V tile
@@ -751,6 +816,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         ++tails;
                     }
                 }
+            }
+            if (kFused) {
+                for (int s = 0; s < kTcStages && ok; ++s)
+                    if (store_pending[s]) ok = flush_store(s);
+                bulk_wait_all();   // the cache rows are written before the kernel ends
             }
             if (*abort_word) {
                 // a wait ran out somewhere: copies this thread requested may still be on their way into
@@ -918,8 +988,9 @@ inline void tcgen05_plan_init(Tcgen05Plan& plan, const ellm_attn_desc& d, int sm
         snprintf(plan.why, sizeof(plan.why), "driver does not export cuTensorMapEncodeTiled");
         return;
     }
-    if (cudaFuncSetAttribute(prefill_tcgen05_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) != cudaSuccess ||
-        cudaFuncSetAttribute(prefill_tcgen05_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) != cudaSuccess) {
+    if (cudaFuncSetAttribute(prefill_tcgen05_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_tcgen05_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_tcgen05_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) != cudaSuccess) {
         snprintf(plan.why, sizeof(plan.why), "cannot reserve %d bytes of shared memory: %s", kTcSmemBytes,
                  cudaGetErrorString(cudaGetLastError()));
         return;
@@ -934,13 +1005,24 @@ inline bool tcgen05_prefers(const Tcgen05Plan& plan, size_t interval, int group)
     return plan.ready && interval * static_cast<size_t>(group) >= 16;
 }
 
+// The append can ride in the kernel when the chunk starts on a 128-key tile boundary with one start
+// for all sequences and the whole key range is attended: then every key tile holds either cache rows
+// only or new rows only.
+inline bool tcgen05_can_fuse_append(const Tcgen05Plan& plan, const ellm_attn_desc& d, const int32_t* positions,
+                                    size_t position_index, size_t batch, long long key_begin, long long key_end) {
+    return plan.ready && plan.fuse_append && d.k_new && d.v_new && !positions && position_index % kTcKeys == 0 && key_begin == 0 &&
+           key_end >= static_cast<long long>(d.max_seq) && batch < 16384 && d.kv_heads < 65536 &&
+           (d.max_batch * d.kv_heads * 256) % 16 == 0;
+}
+
 // With a uniform chunk start the K/V tensor maps are bounded at min(position_index + interval,
 // key_end) so that TMA zero-fills rows the chunk must not read; with per-sequence starts
 // (positions != nullptr) they are bounded by the cache and the kernel zeroes the tail itself.
 // out_f32 != nullptr writes an fp32 partial result there instead of bf16 to d.out.
 inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, const int32_t* positions,
                                   size_t position_index, size_t interval, size_t batch, long long key_begin,
-                                  long long key_end, float* out_f32, float* lse, int* status, cudaStream_t stream) {
+                                  long long key_end, float* out_f32, float* lse, int* status, cudaStream_t stream,
+                                  bool fused_append = false) {
     if (!plan.ready) return ELLM_ERR_UNSUPPORTED;
     const int group = static_cast<int>(d.q_heads / d.kv_heads);
     // per-sequence chunk starts: the maps can only be bounded by the cache itself
@@ -957,7 +1039,7 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
     CUtensorMap& map_v = plan.map_v;
     // the buffers, head counts and strides are fixed for the handle: the maps depend only on these
     const bool reuse = plan.cached_kv_rows == kv_rows && plan.cached_interval == interval && plan.cached_batch == batch &&
-                       plan.cached_q == d.q;
+                       plan.cached_q == d.q && plan.cached_fused == fused_append;
     plan.cached_kv_rows = -1;
     if (!reuse) {
         // q viewed as [head_dim, g, chunk row, kv head, sequence]; a box is 64 x G x (128/G) packed rows
@@ -984,6 +1066,24 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
             return ELLM_ERR_UNSUPPORTED;
         }
     }
+    if (fused_append && !reuse) {
+        // the chunk's new rows [chunk row, sequence, kv head, 128] seen as (128, chunk row, kv head, sequence):
+        // the same box as a cache tile, so a tile of new rows lands in shared memory exactly like a cache tile
+        for (int which = 0; which < 2; ++which) {
+            cuuint64_t dims[4] = {128, interval, d.kv_heads, batch};
+            cuuint64_t strides[3] = {d.max_batch * d.kv_heads * 256, 256, d.kv_heads * 256};
+            cuuint32_t box[4] = {64, 128, 1, 1};
+            cuuint32_t es[4] = {1, 1, 1, 1};
+            if (encode(which ? &plan.map_vn : &plan.map_kn, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                       const_cast<void*>(which ? d.v_new : d.k_new), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+                snprintf(plan.why, sizeof(plan.why), "cuTensorMapEncodeTiled(k_new / v_new) failed");
+                return ELLM_ERR_UNSUPPORTED;
+            }
+        }
+    }
+    plan.cached_fused = fused_append;
     plan.cached_kv_rows = kv_rows;
     plan.cached_interval = interval;
     plan.cached_batch = batch;
@@ -1032,8 +1132,17 @@ inline int launch_prefill_tcgen05(Tcgen05Plan& plan, const ellm_attn_desc& d, co
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = out_f32 ? cudaLaunchKernelEx(&cfg, prefill_tcgen05_kernel<float>, map_q, map_k, map_v, p)
-                                  : cudaLaunchKernelEx(&cfg, prefill_tcgen05_kernel<__nv_bfloat16>, map_q, map_k, map_v, p);
+    // without the fused append the two extra maps are never used; any valid map will do
+    const CUtensorMap& map_kn = fused_append ? plan.map_kn : map_k;
+    const CUtensorMap& map_vn = fused_append ? plan.map_vn : map_v;
+    if (fused_append && out_f32) {
+        snprintf(plan.why, sizeof(plan.why), "the fused append comes with bf16 output only");
+        return ELLM_ERR_UNSUPPORTED;
+    }
+    const cudaError_t e =
+        out_f32        ? cudaLaunchKernelEx(&cfg, prefill_tcgen05_kernel<float, false>, map_q, map_k, map_v, map_kn, map_vn, p)
+        : fused_append ? cudaLaunchKernelEx(&cfg, prefill_tcgen05_kernel<__nv_bfloat16, true>, map_q, map_k, map_v, map_kn, map_vn, p)
+                       : cudaLaunchKernelEx(&cfg, prefill_tcgen05_kernel<__nv_bfloat16, false>, map_q, map_k, map_v, map_kn, map_vn, p);
     return e == cudaSuccess ? ELLM_OK : ELLM_ERR_CUDA;
 }
 

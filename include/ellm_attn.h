@@ -330,6 +330,10 @@ int ellm_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_c
  *                           the projection before attention writes only Q and the newest row - and for
  *                           back-to-back steps on resident inputs; default 0.  ellm_attn_run_host never
  *                           uses it (its staging kernel writes the positions).
+ *   "tc_fuse_append"        prefill kernel: 1 (default) the chunk's K/V rows are read from k_new / v_new and
+ *                           written into the cache by the attention kernel itself when the chunk starts on a
+ *                           128-key boundary (one start for all sequences); 0 always runs the append kernel
+ *                           first.  Same cache bits either way.
  *   "tc_persistent"         prefill kernel: -1 (default) / 1 one CTA per SM walking the work-item list,
  *                           0 one CTA per item; a tuning knob.
  *   "decode_ctas"           grid of the decode kernel, 1 .. 2 x SMs (default 2 x SMs, for which the

@@ -204,3 +204,37 @@ def test_qk_norm_rope_append_matches_float64():
     assert np.array_equal(cv[1, 0, pos0 + 1], v[1, 1, 0])
     assert (ck[:, :, :pos0] == 0).all() and (ck[:, :, pos0 + S:] == 0).all()
     assert qo.shape == q.shape and (qo != 0).any()
+
+
+def test_f16_port_and_fp32_oracle_agree_on_non_uniform_inputs_within_the_measured_envelope(oracle_lib):
+    """Two restatements written independently from two reference files - the AVX-512-FP16 kernel
+    (src/kernel/x86_64/f16_512/flash_attention.rs:30-92, all arithmetic in half precision) and the
+    generic recurrence (src/kernel/generic/flash_attention.rs:60-89, here in fp32) - on the same
+    seeded N(0,1) rows of BASELINE configs[0] (one head, 2048 keys, scale 1/sqrt(128)).  The
+    reference's own tests only use uniform inputs, which pin neither the scale nor the causal limit;
+    here both restatements must see the same keys with the same scale to stay this close.  The half-
+    precision kernel drifts from the fp32 one as keys accumulate: about 1e-3 on short rows, up to
+    6e-3 at 2048 keys."""
+    if not oracle_lib.oracle_f16_available():
+        pytest.skip("CPU without avx512fp16 (the reference skips the same way)")
+    import torch
+    from oracle.binding import aligned_empty
+    S, scale = 2048, 1.0 / np.sqrt(128.0)
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(S, 128, generator=g).to(torch.float16) for _ in range(3))
+    kb = aligned_empty((S, 128), np.uint16); kb[:] = k.view(torch.int16).numpy().view(np.uint16)
+    vb = aligned_empty((S, 128), np.uint16); vb[:] = v.view(torch.int16).numpy().view(np.uint16)
+    kf, vf = k.float().numpy(), v.float().numpy()
+    worst_short = worst_long = 0.0
+    for pos in (0, 1, 7, 63, 64, 127, 255, 256, 1023, 1024, 1500, 2000, 2047):
+        qb = aligned_empty((128,), np.uint16); qb[:] = q[pos].view(torch.int16).numpy().view(np.uint16)
+        ob = aligned_empty((128,), np.uint16); ob[:] = 0
+        oracle_lib.oracle_f16_flash_attention(qb.ctypes.data, kb.ctypes.data, vb.ctypes.data, ob.ctypes.data, scale, 128, 128, pos)
+        o = np.zeros(128, np.float32)
+        oracle.flash_attention_f32(q[pos].float().numpy(), kf, vf, o, scale, pos)
+        d = float(np.abs(ob.view(np.float16).astype(np.float32) - o).max())
+        if pos < 128:
+            worst_short = max(worst_short, d)
+        worst_long = max(worst_long, d)
+    assert worst_short <= 2.5e-3, worst_short
+    assert 1e-4 < worst_long <= 6e-3, worst_long     # different arithmetic (not the same code twice), same function
