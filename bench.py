@@ -665,10 +665,10 @@ def main():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_splitkv_kernel launch on this workload
-# (609.89 MB read + 4.09 MB written), from an `ncu --set full --clock-control none -k
-# regex:decode_splitkv -c 2` capture of `python bench.py --steps 2 --warmup 3 --no-cpu-baseline
-# --no-extra` on a B200.  A constant of that capture, not measured by this run.
-TRAFFIC_BYTES_PER_LAUNCH = 613.95e6
+# (609.91 MB read + 3.76 / 4.55 MB written, two launches), from an `ncu --set full --clock-control none
+# -k regex:decode_splitkv -s 6 -c 2` capture of `python bench.py --steps 2 --warmup 3 --min-seconds 0.001
+# --no-extra --no-cpu-baseline` on a B200.  A constant of that capture, not measured by this run.
+TRAFFIC_BYTES_PER_LAUNCH = 614.07e6
 TRAFFIC_SOURCE = "ncu capture of this workload (dram__bytes_read.sum + dram__bytes_write.sum, one launch); a recorded constant"
 
 if __name__ == "__main__":
