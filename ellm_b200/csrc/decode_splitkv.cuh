@@ -222,6 +222,8 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
         if (!waited) {
             // the CTA's first piece: request ahead of the wait whatever cannot hold a row the
             // previous kernel writes (a sequence's newest row, at len - 1), stage by stage in order
+            // (the stages the prologue below would request; filling the third ring slot as well was
+            // measured 1 us slower per step, early or not: the loop's extra test changes its code)
 #pragma unroll
             for (int s = 0; s < kDecStages - 1; ++s) {
                 const long long kfirst = key0 + static_cast<long long>(s) * kDecTileKeys;
@@ -236,6 +238,8 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
             asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             waited = true;
         }
+        // every stage is its own group and the groups are committed in stage order, so "all but the
+        // last kDecStages - 1 groups have landed" below always covers the stage an iteration needs
 #pragma unroll
         for (int s = 0; s < kDecStages - 1; ++s) {
             if (s >= s_first) {

@@ -258,6 +258,32 @@ int launch_append(ellm_attn* h, cudaStream_t stream, void* k_cache, void* v_cach
     return ELLM_OK;
 }
 
+// The merge of a decode step in the shape that fits the step: many rows with few pieces each get
+// the light shape (2 warps per row, tables in dynamic shared memory), few rows with many pieces the
+// wide one.  A row's pieces are at most the decode grid's CTAs.
+cudaError_t launch_merge(const ellm::DecodeParams& p, size_t batch, unsigned blocks, float* out_f32, void* out_bf16,
+                         float* lse_out, cudaStream_t stream, bool dependent) {
+    const int pieces_cap = std::min(p.num_ctas, ellm::kMergeMaxPieces);
+    const size_t smem = ellm::merge_smem_bytes(static_cast<int>(batch), pieces_cap);
+    const bool light = blocks >= 128;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(light ? ellm::kMergeLightThreads : ellm::kMergeThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent ? 1 : 0;
+    __nv_bfloat16* ob = static_cast<__nv_bfloat16*>(out_bf16);
+    if (out_f32)
+        return light ? cudaLaunchKernelEx(&cfg, ellm::decode_merge_kernel<float, 2, 4>, p, out_f32, lse_out, pieces_cap)
+                     : cudaLaunchKernelEx(&cfg, ellm::decode_merge_kernel<float, 8, 10>, p, out_f32, lse_out, pieces_cap);
+    return light ? cudaLaunchKernelEx(&cfg, ellm::decode_merge_kernel<__nv_bfloat16, 2, 4>, p, ob, lse_out, pieces_cap)
+                 : cudaLaunchKernelEx(&cfg, ellm::decode_merge_kernel<__nv_bfloat16, 8, 10>, p, ob, lse_out, pieces_cap);
+}
+
 // Decode (interval == 1): K2 then K3.  out_f32 != nullptr selects the fp32
 // partial output of the windowed form.
 int launch_decode(ellm_attn* h, const int32_t* positions, size_t position_index, size_t batch,
@@ -303,22 +329,8 @@ int launch_decode(ellm_attn* h, const int32_t* positions, size_t position_index,
         // programmatic dependent launch: the merge grid is set up while the decode grid drains;
         // its first instruction waits for the decode grid's memory to be visible
         LaunchScope ls(h, ELLM_KERNEL_MERGE);
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(blocks);
-        cfg.blockDim = dim3(ellm::kMergeThreads);
-        cfg.dynamicSmemBytes = 0;
-        cfg.stream = h->stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        cudaError_t e;
-        if (out_f32)
-            e = cudaLaunchKernelEx(&cfg, ellm::decode_merge_kernel<float>, p, out_f32, lse_out);
-        else
-            e = cudaLaunchKernelEx(&cfg, ellm::decode_merge_kernel<__nv_bfloat16>, p,
-                                   static_cast<__nv_bfloat16*>(out_override ? out_override : h->d.out), lse_out);
+        const cudaError_t e = launch_merge(p, batch, blocks, out_f32, out_f32 ? nullptr : (out_override ? out_override : h->d.out),
+                                           lse_out, h->stream, true);
         if (e != cudaSuccess) return fail(ELLM_ERR_CUDA, "merge launch failed: %s", cudaGetErrorString(e));
     }
     ELLM_CUDA(cudaGetLastError());
@@ -1287,7 +1299,7 @@ extern "C" int ellm_attn_decode_noalloc(const void* q, const void* k_cache, cons
     ellm::decode_splitkv_kernel<<<num_ctas, ellm::kDecThreads, ellm::kDecSmemBytes, s>>>(p);
     ELLM_CUDA(cudaGetLastError());
     const unsigned blocks = static_cast<unsigned>(batch_size * q_heads);
-    ellm::decode_merge_kernel<__nv_bfloat16><<<blocks, ellm::kMergeThreads, 0, s>>>(p, static_cast<__nv_bfloat16*>(out), lse);
+    ELLM_CUDA(launch_merge(p, batch_size, blocks, nullptr, out, lse, s, false));
     ELLM_CUDA(cudaGetLastError());
     return ELLM_OK;
 }

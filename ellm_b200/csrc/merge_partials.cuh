@@ -25,27 +25,41 @@ __device__ __forceinline__ void store_row4<__nv_bfloat16>(__nv_bfloat16* dst, fl
     *reinterpret_cast<uint2*>(dst) = u;
 }
 
-// Combines the pieces the decode kernel left in its workspace.  Grid: one CTA of 8 warps per
-// (sequence, query head).  A segment spread over many CTAs has many pieces (a single long sequence:
-// one per CTA of the decode grid), so the combine is laid out for latency: first every thread
-// fetches the log-sum-exp of one piece and the CTA agrees on their maximum, which fixes every
-// piece's weight; then the warps take the pieces round-robin, four loads in flight each, with no
-// dependence between pieces - and the rows are requested before the weights are known; last the
-// eight partial rows are added through shared memory.
+// Combines the pieces the decode kernel left in its workspace.  Grid: one CTA per (sequence, query
+// head).  A segment spread over many CTAs has many pieces (a single long sequence: one per CTA of
+// the decode grid), so the combine is laid out for latency: first every thread fetches the
+// log-sum-exp of one piece and the CTA agrees on their maximum, which fixes every piece's weight;
+// then the warps take the pieces round-robin, kAhead loads in flight each, with no dependence
+// between pieces - and the rows are requested before the weights are known; last the warps'
+// partial rows are added through shared memory.
+//
+// Two shapes.  kWarps = 8, kAhead = 10: few rows with many pieces each (one sequence: 74 pieces per
+// row).  kWarps = 2, kAhead = 4 with all tables in a few hundred bytes of dynamic shared memory: many
+// rows with few pieces each (a batch) - small enough in registers and shared memory to sit on an
+// SM beside two CTAs of the decode kernel, so that the whole grid is resident (and has let its own
+// dependents go) long before the decode grid ends, and the next step's decode CTAs can move in as
+// this step's leave instead of queueing behind this grid.
 // out: [max_batch, q_heads, 128], lse: [max_batch, q_heads].
-constexpr int kMergeThreads = 256;
+constexpr int kMergeThreads = 256;      // the wide shape
+constexpr int kMergeLightThreads = 64;  // the light shape
 constexpr int kMergeMaxPieces = 1024;   // weights kept in shared memory; more pieces are handled in rounds
 
-template <typename OutT>
-__global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const DecodeParams p, OutT* out, float* lse) {
+// dynamic shared memory of the merge: tile prefix table, lengths, piece weights
+__host__ __device__ inline size_t merge_smem_bytes(int batch, int pieces_cap) {
+    return (static_cast<size_t>(2 * batch + 1) + static_cast<size_t>(pieces_cap)) * 4;
+}
+
+template <typename OutT, int kWarps, int kAhead>
+__global__ void __launch_bounds__(kWarps * 32) decode_merge_kernel(const DecodeParams p, OutT* out, float* lse, int pieces_cap) {
     // a following kernel launched as a programmatic dependent may start its own prologue now
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    __shared__ float s_l[kMergeMaxPieces];
-    __shared__ float s_red[kMergeThreads / 32];
-    __shared__ float4 s_acc[kMergeThreads / 32][32];
-    __shared__ int s_prefix[kDecMaxBatch + 1];
-    __shared__ int s_lens[kDecMaxBatch];
-    constexpr int kWarps = kMergeThreads / 32;
+    extern __shared__ __align__(16) unsigned char merge_smem[];
+    int* s_prefix = reinterpret_cast<int*>(merge_smem);                // [batch + 1]
+    int* s_lens = s_prefix + p.batch + 1;                              // [batch]
+    float* s_l = reinterpret_cast<float*>(s_lens + p.batch);           // [pieces_cap]
+    __shared__ float s_red[kWarps];
+    __shared__ float4 s_acc[kWarps][32];
+    constexpr int kThreads = kWarps * 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // Where this row's pieces are follows from the positions alone, which are older than the decode
     // grid (it lets this grid start only after its own wait): the tile table is rebuilt here, before
@@ -81,21 +95,20 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Decod
     }
 
     // The pieces' rows do not depend on their weights, so a warp requests the rows of its first
-    // kMergeAhead pieces before anything else: they travel while the log-sum-exps are fetched and
+    // kAhead pieces before anything else: they travel while the log-sum-exps are fetched and
     // their maximum is agreed on - two dependent round trips to L2 in all instead of four or five.
-    constexpr int kMergeAhead = 10;
-    float4 x[kMergeAhead];
+    float4 x[kAhead];
 #pragma unroll
-    for (int u = 0; u < kMergeAhead; ++u) {
+    for (int u = 0; u < kAhead; ++u) {
         const int i = warp + u * kWarps;
         x[u] = i < pieces ? *reinterpret_cast<const float4*>(o_base + static_cast<long long>(i) * 16 * kHeadDim)
                           : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     // 1. the maximum of the pieces' log-sum-exps (every piece has seen at least one key: finite)
     float mx = -INFINITY;
-    for (int i = threadIdx.x; i < pieces; i += kMergeThreads) {
+    for (int i = threadIdx.x; i < pieces; i += kThreads) {
         const float l = lse_base[static_cast<long long>(i) * 16];
-        if (i < kMergeMaxPieces) s_l[i] = l;
+        if (i < pieces_cap) s_l[i] = l;
         mx = fmaxf(mx, l);
     }
 #pragma unroll
@@ -109,9 +122,9 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Decod
     // 2. weighted sums, pieces round-robin over the warps
     float wsum = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    auto piece_lse = [&](int i) { return i < kMergeMaxPieces ? s_l[i] : lse_base[static_cast<long long>(i) * 16]; };
+    auto piece_lse = [&](int i) { return i < pieces_cap ? s_l[i] : lse_base[static_cast<long long>(i) * 16]; };
 #pragma unroll
-    for (int u = 0; u < kMergeAhead; ++u) {
+    for (int u = 0; u < kAhead; ++u) {
         const int i = warp + u * kWarps;
         if (i < pieces) {
             const float w = __expf(piece_lse(i) - mm);
@@ -119,7 +132,7 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Decod
             acc.x += w * x[u].x; acc.y += w * x[u].y; acc.z += w * x[u].z; acc.w += w * x[u].w;
         }
     }
-    for (int i = warp + kMergeAhead * kWarps; i < pieces; i += kWarps) {   // a segment cut into more than 80 pieces
+    for (int i = warp + kAhead * kWarps; i < pieces; i += kWarps) {   // more pieces than the warps hold ahead
         const float4 y = *reinterpret_cast<const float4*>(o_base + static_cast<long long>(i) * 16 * kHeadDim);
         const float w = __expf(piece_lse(i) - mm);
         wsum += w;
@@ -130,15 +143,15 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Decod
     if (lane == 0) s_red[warp] = wsum;
     __syncthreads();
 
-    // 3. the eight partial rows
+    // 3. the warps' partial rows
     if (warp == 0) {
         float tot = 0.0f;
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int w8 = 0; w8 < kWarps; ++w8) {
-            const float4 x = s_acc[w8][lane];
+            const float4 xw = s_acc[w8][lane];
             tot += s_red[w8];
-            o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w;
+            o.x += xw.x; o.y += xw.y; o.z += xw.z; o.w += xw.w;
         }
         const float inv = 1.0f / tot;
         o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
