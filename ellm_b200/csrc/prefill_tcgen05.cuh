@@ -16,8 +16,9 @@
 //   warp  8    TMA producer (one lane): Q tiles once, then K_j, V_j through a ring
 //   warp  9    MMA issuer (one lane) and owner of the tensor-memory allocation
 // Per 128-key tile j and row tile t:  S_t = Q_t K_j^T (tensor memory) -> softmax
-// threads read S_t, write P_t (bf16) back into the first 64 columns of S_t and,
-// when the running max moved by more than 2^8, rescale O_t in tensor memory ->
+// threads read S_t half a row at a time, write P_t (bf16) back into the first 64
+// columns of S_t (the first half's P before the second half's scores are fetched)
+// and, when the running max moved by more than 2^8, rescale O_t in tensor memory ->
 // O_t += P_t V_j with P_t read from tensor memory as the A operand.
 // The two row tiles alternate on the tensor core, so one tile's softmax overlaps
 // the other's MMAs.
@@ -372,6 +373,83 @@ __device__ __noinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity, unsi
     }
 }
 
+// Rare tail of the one-pass step: a score among the row's second 64 keys leapt far above the maximum in
+// use after the first 64 keys' P had gone to tensor memory.  Finds the second half's true maximum,
+// rescales O_t and the stored first half of P_t to it, and recomputes the second half.  Out of line:
+// its registers must not be charged to the plain step.
+struct TcFixed {
+    float m_used, l;
+};
+__device__ __noinline__ TcFixed tc_fix_second_half(uint32_t tS, uint32_t tO, float scale_log2, float m_used, float l,
+                                                   float first_half_sum, uint32_t* pk) {
+    float mx = -INFINITY;
+#pragma unroll 1
+    for (int c = 0; c < 2; ++c) {
+        float v[32];
+        tmem_ld32(tS + 64 + c * 32, v);
+        tmem_wait_ld();
+        float m0 = max3(v[0], v[1], v[2]), m1 = max3(v[3], v[4], v[5]);
+#pragma unroll
+        for (int i = 6; i < 30; i += 6) {
+            m0 = max3(m0, v[i], v[i + 1]);
+            m1 = max3(m1, v[i + 2], v[i + 3]);
+            m0 = fmaxf(m0, v[i + 4]);
+            m1 = fmaxf(m1, v[i + 5]);
+        }
+        mx = max3(mx, max3(m0, v[30], v[31]), m1);
+    }
+    const float m_new = fmaxf(m_used, mx * scale_log2);
+    // rows whose maximum did not move far keep it (their corr is 1): as in the two-pass step
+    const bool moved = m_new - m_used > kTcRescaleThreshold;
+    const float corr = moved ? fast_exp2(m_used - m_new) : 1.0f;
+    if (moved) m_used = m_new;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {   // O_t: every P.V of earlier steps has completed (this step's S_t exists)
+        float o[32];
+        tmem_ld32(tO + c * 32, o);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] *= corr;
+        tmem_st32(tO + c * 32, o);
+    }
+    {   // the first half of P_t, bf16 pairs in columns [0, 32)
+        uint32_t q[32];
+        tmem_ld32(tS, *reinterpret_cast<float(*)[32]>(&q[0]));
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&q[i]);
+            q[i] = pack_bf16(__low2float(h) * corr, __high2float(h) * corr);
+        }
+        tmem_st32u(tS, q);
+    }
+    const uint64_t scale2 = pack2(scale_log2, scale_log2), negm2 = pack2(-m_used, -m_used);
+    uint64_t sum_a = pack2(0.0f, 0.0f), sum_b = sum_a;
+#pragma unroll 1
+    for (int c = 0; c < 2; ++c) {
+        float v[32];
+        tmem_ld32(tS + 64 + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int cc = 0; cc < 16; ++cc) {
+            const uint64_t x2 = fma2(pack2(v[2 * cc], v[2 * cc + 1]), scale2, negm2);
+            float x0, x1;
+            unpack2(x2, x0, x1);
+            const uint64_t p2 = pack2(fast_exp2(x0), fast_exp2(x1));
+            if (cc & 1) sum_b = add2(sum_b, p2); else sum_a = add2(sum_a, p2);
+            float p0, p1;
+            unpack2(p2, p0, p1);
+            pk[c * 16 + cc] = pack_bf16(p0, p1);
+        }
+    }
+    float sa, sb;
+    unpack2(add2(sum_a, sum_b), sa, sb);
+    TcFixed r;
+    r.m_used = m_used;
+    r.l = (l + first_half_sum) * corr + (sa + sb);
+    return r;
+}
+
 // kFused: the chunk's own K/V rows come from k_new / v_new and are written into the cache here (a
 // separate instantiation, so that the plain kernel carries none of its state).
 template <typename OutT, bool kFused>
@@ -510,49 +588,64 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 // the two-pass slow path below redoes the step with a rescale of O_t.
                 bool slow = (j == 0) || edge;
                 if (!slow) {
+                    // Half a row at a time: the first 64 keys' P goes to tensor memory (over columns of S_t
+                    // that have been read) before the second 64 scores are fetched, so that a thread holds 64
+                    // scores and 32 packed P values at most.
                     const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_used, -m_used);
-                    uint64_t sum_a = pack2(0.0f, 0.0f), sum_b = sum_a;
-                    uint32_t pk[64];
+                    uint32_t pk[32];
+                    float half_sum[2];
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
                         float s[64];
                         tmem_ld32(tS + half * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
                         tmem_ld32(tS + half * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
                         tmem_wait_ld();
+                        uint64_t sum_a = pack2(0.0f, 0.0f), sum_b = sum_a;
 #pragma unroll
                         for (int cc = 0; cc < 32; ++cc) {
-                            const int c = half * 32 + cc;
                             const uint64_t x2 = fma2(pack2(s[2 * cc], s[2 * cc + 1]), scale2, negm2);
                             uint64_t p2;
-                            if (kTcPolyEvery > 0 && (c % kTcPolyDiv) == kTcPolyDiv - 1) {
+                            if (kTcPolyEvery > 0 && (cc % kTcPolyDiv) == kTcPolyDiv - 1) {
                                 p2 = exp2_poly2(x2);
                             } else {
                                 float x0, x1;
                                 unpack2(x2, x0, x1);
                                 p2 = pack2(fast_exp2(x0), fast_exp2(x1));
                             }
-                            if (c & 1) sum_b = add2(sum_b, p2); else sum_a = add2(sum_a, p2);
+                            if (cc & 1) sum_b = add2(sum_b, p2); else sum_a = add2(sum_a, p2);
                             float p0, p1;
                             unpack2(p2, p0, p1);
-                            pk[c] = pack_bf16(p0, p1);
+                            pk[cc] = pack_bf16(p0, p1);
                         }
-                    }
-                    // No row maximum is tracked here.  A score far above the maximum in use shows up as a huge
-                    // term of this step's sum (2^16 and more: one key 16 octaves above, or infinity); then the
-                    // step is redone the slow way, which finds the true maximum and rescales.  Below that, P
-                    // (bf16) and the fp32 accumulators take the larger terms as they are.
-                    float sa, sb;
-                    unpack2(add2(sum_a, sum_b), sa, sb);
-                    const float step_sum = sa + sb;
-                    slow = __any_sync(0xffffffffu, !(step_sum < kTcSumTrigger));
-                    if (!slow) {
-                        l += step_sum;
-                        tmem_st32u(tS, pk);
-                        tmem_st32u(tS + 32, pk + 32);
-                        tmem_wait_st();
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bar_p_full(t));
+                        float sa, sb;
+                        unpack2(add2(sum_a, sum_b), sa, sb);
+                        half_sum[half] = sa + sb;
+                        // No row maximum is tracked here.  A score far above the maximum in use shows up as a huge
+                        // term of the sum (2^16 and more: one key 16 octaves above, or infinity).
+                        const bool leapt = __any_sync(0xffffffffu, !(half_sum[half] < kTcSumTrigger));
+                        if (half == 0) {
+                            if (leapt) {   // S_t is still intact: the whole step the slow way
+                                slow = true;
+                                break;
+                            }
+                            tmem_st32u(tS, pk);
+                        } else {
+                            if (leapt) {   // the first half's P is already in place: bring it and O_t to the new maximum
+                                uint32_t redone[32];   // (addressable only here: pk itself stays in registers)
+                                const TcFixed f = tc_fix_second_half(tS, tO, p.scale_log2, m_used, l, half_sum[0], redone);
+                                m_used = f.m_used;
+                                l = f.l;
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) pk[i] = redone[i];
+                            } else {
+                                l += half_sum[0] + half_sum[1];
+                            }
+                            tmem_st32u(tS + 32, pk);
+                            tmem_wait_st();
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar_p_full(t));
+                        }
                     }
                 }
                 if (slow) {

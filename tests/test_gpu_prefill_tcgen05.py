@@ -171,6 +171,22 @@ def test_key_windows_that_start_past_key_zero(interval, pos):
     assert_attention_close(case, bits(out), lse.view(interval, 2, 8).cpu().numpy(), want_o, want_l)
 
 
+def test_more_items_than_sms_with_ragged_starts_and_with_the_fused_append():
+    """The work list with several items per CTA in its two stateful corners: per-sequence chunk starts
+    (the producer clears the tail of the last V tile of every item: a barrier whose phase carries from
+    item to item) and the fused append (tiles waiting in ring slots to be stored into the cache while
+    the next item's loads queue up).  5 sequences x 8 KV heads x 4 row-tile pairs = 160 items."""
+    ragged = Case(seed=4321, interval=1024, batch=5, q_heads=8, kv_heads=8, max_seq=1700,
+                  positions=[0, 300, 37, 512, 640], max_batch=6)
+    _check(ragged)
+    aligned = Case(seed=4322, interval=1024, batch=5, q_heads=8, kv_heads=8, max_seq=1300, position_index=256, max_batch=6)
+    _check(aligned)          # starts on a key-tile boundary: the chunk's rows never pass through the append kernel
+    assert aligned.last_stats["kv_append"][0] == 0
+    shifted = Case(seed=4323, interval=1024, batch=5, q_heads=8, kv_heads=8, max_seq=1300, position_index=200, max_batch=6)
+    _check(shifted)          # starts inside a key tile: the append kernel runs first
+    assert shifted.last_stats["kv_append"][0] == 1
+
+
 def test_one_cta_per_sm_and_one_cta_per_item_give_the_same_bits():
     """The work-item list walked by one CTA per SM (several items per CTA, barrier phases carried
     from item to item) against one CTA per item: 2 sequences x 4 KV heads x 24 row-tile pairs = 192
@@ -253,7 +269,9 @@ def test_scores_that_leap_above_the_running_maximum(boost):
     the exponentials overflow before the rescale) - deep inside the sequence, in the middle of a key tile
     and at tile starts, so that steps after the first one meet them."""
     case = Case(seed=61, interval=1536, batch=1, q_heads=4, kv_heads=1, max_seq=1536, position_index=0)
-    for key in (300, 301, 640, 1024, 1400):
+    # columns 44, 45, 0, 0 of their key tiles (first half of a row: the step is redone from intact scores) and
+    # columns 120, 64, 127 (second half: the first half's P has already gone to tensor memory and is rescaled there)
+    for key in (300, 301, 640, 1024, 1400, 832, 1151):
         case.k_new[key] = (case.k_new[key].float() * boost).to(torch.bfloat16)
     want_k, want_v, want_o, want_l = case.oracle()
     got_k, got_v, got_o, got_l = case.gpu(prefill_kernel=L.PREFILL_TCGEN05)
