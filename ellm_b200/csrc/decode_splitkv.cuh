@@ -75,28 +75,28 @@ __device__ __forceinline__ long long cta_of_tile(long long total, long long n, l
     return r + (t - (q + 1) * r) / q;
 }
 
-// Keys sequence b attends: its new token sits at positions[b], so positions[b] + 1.
-__device__ __forceinline__ long long dec_seq_len(const DecodeParams& p, int b) {
-    long long len = p.positions ? static_cast<long long>(p.positions[b]) + 1 : p.uniform_len;
-    return len < p.len_cap ? len : p.len_cap;
+// Keys sequence b would attend without the cap: its new token sits at positions[b], so positions[b] + 1.
+__device__ __forceinline__ long long dec_seq_len_raw(const DecodeParams& p, int b) {
+    return p.positions ? static_cast<long long>(p.positions[b]) + 1 : p.uniform_len;
 }
 
-// Tiles of sequence b (all of its segments have the same count).
-__device__ __forceinline__ int dec_seq_tiles(const DecodeParams& p, int b) {
-    long long n = dec_seq_len(p, b) - p.key_begin;
+// Tiles of a sequence of `len` keys (all of its segments have the same count).
+__device__ __forceinline__ int dec_tiles_of(const DecodeParams& p, long long len) {
+    const long long n = len - p.key_begin;
     if (n <= 0) return 0;
     return static_cast<int>((n + kDecTileKeys - 1) / kDecTileKeys);
 }
 
-// prefix[b] = sum of tiles of sequences < b, for b in [0, batch]; lens[b] = keys sequence b
-// attends.  All threads call.  The positions are fetched by as many threads as there are
+// prefix[b] = sum of tiles of sequences < b, for b in [0, batch]; lens[b] = keys sequence b would
+// attend without the cap (the positions are read here once, by one thread per sequence, and never
+// again: they may live in page-locked host memory).  All threads call.  The positions are fetched by as many threads as there are
 // sequences (one global-memory latency, not one per sequence); the running sum over the
 // per-sequence tile counts is then a short loop over shared memory.
 __device__ inline void dec_build_prefix(const DecodeParams& p, int* prefix, int* lens) {
     for (int b = threadIdx.x; b < p.batch; b += blockDim.x) {
-        const long long len = dec_seq_len(p, b);
-        lens[b] = static_cast<int>(len < 0 ? 0 : len);
-        prefix[b + 1] = dec_seq_tiles(p, b);
+        const long long raw = dec_seq_len_raw(p, b);
+        lens[b] = static_cast<int>(raw < 0 ? 0 : raw);
+        prefix[b + 1] = dec_tiles_of(p, raw < p.len_cap ? raw : p.len_cap);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -162,7 +162,8 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
         const int ntiles = static_cast<int>(piece_end - t);
         const int kvh = seg_in_seq / p.gtiles, gt = seg_in_seq % p.gtiles;
         const long long segment = static_cast<long long>(b) * segs_per_seq + seg_in_seq;
-        const long long len = lens[b];
+        const long long len_raw = lens[b];
+        const long long len = len_raw < p.len_cap ? len_raw : p.len_cap;
         const int rows_valid = min(16, p.group - gt * 16);
         const long long key0 = p.key_begin + static_cast<long long>(tile0) * kDecTileKeys + warp * 16;
         const __nv_bfloat16* kbase = p.k_cache + b * p.s0 + kvh * p.s1;
@@ -171,10 +172,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
         // the row being appended is the sequence's last key, unless its position lies past the
         // cache (then len was capped and nothing is read or written there)
         long long new_pos = -1;
-        if (p.k_new) {
-            const long long uncapped = p.positions ? static_cast<long long>(p.positions[b]) + 1 : p.uniform_len;
-            if (uncapped == len) new_pos = len - 1;
-        }
+        if (p.k_new && len_raw == len) new_pos = len - 1;
         const __nv_bfloat16* knew = p.k_new ? p.k_new + (static_cast<long long>(b) * p.kv_heads + kvh) * kHeadDim : nullptr;
         const __nv_bfloat16* vnew = p.k_new ? p.v_new + (static_cast<long long>(b) * p.kv_heads + kvh) * kHeadDim : nullptr;
 

@@ -648,6 +648,9 @@ int ellm_attn_run_host(ellm_attn* h, const void* q_host, const void* k_new_host,
         };
         add(h->d.q, dq, q_width);
         if (k_new_host) { add(h->d.k_new, dk, kv_width); add(h->d.v_new, dv, kv_width); }
+        // (the positions are staged like the rest: letting the decode and merge kernels read them straight
+        // from the page-locked buffer, to start streaming K/V while Q is still on its way, was measured -
+        // every CTA's read is its own PCIe transaction, and 800 CTAs of them made the step 27 us longer)
         add(h->positions_dev, dp, batch_size * sizeof(int32_t));
         unsigned long long stage_chunks = 0;
         for (int i = 0; i < si.n; ++i) stage_chunks += si.bytes[i] / 16;
