@@ -84,7 +84,7 @@ inline int skinny_smem_bytes(int k_chunks, int cols, int pass_chunks, int m_rows
     return skinny_x_bytes(k_chunks, m_rows) + slice + 128;
 }
 
-__global__ void __launch_bounds__(kSkThreads, 1) proj_skinny_kernel(const SkinnyParams p) {
+__global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const SkinnyParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int x_bytes = skinny_x_bytes(p.k_chunks, p.m_rows);
@@ -118,6 +118,23 @@ __global__ void __launch_bounds__(kSkThreads, 1) proj_skinny_kernel(const Skinny
     // its own wait (a decode kernel with early streaming: the positions, older cache rows) is then
     // older than everything this kernel waited for
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // fused head epilogue: what its last step needs from global memory - the token's position, its
+    // rotation row, the norm weights - is requested now, two dependent round trips ahead of its use
+    long long ep_pos = -1;
+    float4 ep_wv = make_float4(1.f, 1.f, 1.f, 1.f), ep_cs = make_float4(1.f, 0.f, 1.f, 0.f);
+    if (p.heads != 0 && threadIdx.x < 4 * p.m_rows) {
+        const int m = threadIdx.x >> 2, quad = threadIdx.x & 3, b = m % p.max_batch;
+        if (b < p.batch) {
+            ep_pos = (p.positions ? static_cast<long long>(p.positions[b]) : p.position_index) + m / p.max_batch;
+            const int head = n0 >> 7, ch = (n0 & 127) + quad * 4;
+            const int kind = head >= p.mat_q_heads + p.mat_k_heads ? 2 : (head >= p.mat_q_heads ? 1 : 0);
+            if (kind != 2 && ep_pos >= 0 && ep_pos < p.rope_rows) {
+                const float* wgt = kind == 0 ? p.q_norm_weight : p.k_norm_weight;
+                if (wgt) ep_wv = *reinterpret_cast<const float4*>(wgt + ch);
+                ep_cs = *reinterpret_cast<const float4*>(p.rope + ep_pos * kHeadDim + ch);  // cos0 sin0 cos1 sin1
+            }
+        }
+    }
     if (p.input_norm_eps >= 0.0f) {
         // the layer's input norm, y = x / (sqrt(mean x^2) + eps) rounded to bf16, on the few rows
         // of a decode step (src/kernel/generic/rms_norm.rs:6-26); the same code as rms_norm_kernel
@@ -238,7 +255,7 @@ __global__ void __launch_bounds__(kSkThreads, 1) proj_skinny_kernel(const Skinny
         cluster_sync_all();   // every CTA of the head has every partial sum
         if (live) {
             const int b = m % p.max_batch;
-            const long long pos = (p.positions ? static_cast<long long>(p.positions[b]) : p.position_index) + m / p.max_batch;
+            const long long pos = ep_pos;
             const int ch = (n0 & 127) + quad * 4;   // channel of x[0] inside the head
             if (kind == 2) {
                 if (pos >= 0 && pos < p.max_seq && pos < p.rope_rows) {   // as K: no rotation row, no cache write
@@ -261,11 +278,8 @@ __global__ void __launch_bounds__(kSkThreads, 1) proj_skinny_kernel(const Skinny
                     for (int i = 0; i < 32; ++i) tsum[i] = nxt[i];
                 }
                 const float rrms = 1.0f / (sqrtf(tsum[0] / static_cast<float>(kHeadDim)) + p.eps);
-                float4 wv = make_float4(1.f, 1.f, 1.f, 1.f);
-                const float* wgt = kind == 0 ? p.q_norm_weight : p.k_norm_weight;
-                if (wgt) wv = *reinterpret_cast<const float4*>(wgt + ch);
+                const float4 wv = ep_wv, cs = ep_cs;
                 const float y0 = x[0] * rrms * wv.x, y1 = x[1] * rrms * wv.y, y2 = x[2] * rrms * wv.z, y3 = x[3] * rrms * wv.w;
-                const float4 cs = *reinterpret_cast<const float4*>(p.rope + pos * kHeadDim + ch);  // cos0 sin0 cos1 sin1
                 uint2 outv;
                 outv.x = pack_bf16(y0 * cs.x - y1 * cs.y, y0 * cs.y + y1 * cs.x);
                 outv.y = pack_bf16(y2 * cs.z - y3 * cs.w, y2 * cs.w + y3 * cs.z);
