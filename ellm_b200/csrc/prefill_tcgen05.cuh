@@ -7,10 +7,11 @@
 // it calls (src/kernel/generic/flash_attention.rs:60-89): chunk row r of sequence
 // b is the token at position base + r and attends keys 0..=base + r.
 //
-// One CTA owns 256 packed rows of one (sequence, KV head): packed row rho = r*G + g
+// A work item is 256 packed rows of one (sequence, KV head): packed row rho = r*G + g
 // (g = query head inside its group, fastest), split in two tiles of 128 rows, so
 // the G query heads of a group share every K/V tile - the reference's "one KV
-// head at a time" locality.  Warp roles:
+// head at a time" locality.  One CTA per SM walks the list of items (heaviest
+// first, the next untaken one from a device counter).  Warp roles:
 //   warps 0-3  softmax / correction / epilogue of tile 0 (thread = one row)
 //   warps 4-7  the same for tile 1
 //   warp  8    TMA producer (one lane): Q tiles once, then K_j, V_j through a ring

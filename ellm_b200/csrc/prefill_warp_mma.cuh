@@ -1,8 +1,10 @@
 // K1 (general form): causal grouped-query flash-attention over a chunk of query
 // rows on the warp-level tensor-core MMA.  It takes every shape the operator
 // accepts - any chunk length, any start position, ragged per-sequence positions,
-// a restricted key window, fp32 partial output - and is what small chunks run on;
-// large aligned chunks go to the tcgen05 kernel (prefill_tcgen05.cuh).
+// a restricted key window, fp32 partial output.  The operator picks it by itself
+// only for chunks of fewer than 16 packed rows; everything else goes to the
+// tcgen05 kernel (prefill_tcgen05.cuh), against which this independent second
+// implementation is the tests' cross-check.
 //
 // Replaces the item walk of the reference's Attention::run
 // (src/compiler/mul/attention.rs:85-153) together with the per-row key loop it

@@ -32,7 +32,8 @@ typedef enum ellm_dtype { ELLM_DTYPE_BF16 = 0 } ellm_dtype;
 
 /* Which kernel ellm_attn_run picks for a chunk of more than one row. */
 typedef enum ellm_prefill_kernel {
-    ELLM_PREFILL_AUTO = 0,     /* tcgen05 kernel when the chunk is large enough, else the warp-MMA kernel */
+    ELLM_PREFILL_AUTO = 0,     /* tcgen05 kernel from 16 packed rows (chunk rows x query heads per KV head) up,
+                                  else the warp-MMA kernel */
     ELLM_PREFILL_TCGEN05 = 1,
     ELLM_PREFILL_WARP_MMA = 2
 } ellm_prefill_kernel;
