@@ -408,6 +408,17 @@ def sharded_extra(rank, world, dev):
     pos = [0, 1, 127, 128, 129, 255, 256, 4095, 4096, 65535, 65536, S - 129, S - 128, S - 2, S - 1]
     pos += [int(x) for x in rng.integers(0, S, n_rows - len(pos))]
     res, sample = multi_gpu.heads_prefill(S, Hq, Hkv, rank, world, dev, steps=2, warmup=1, seed=2, sample_positions=pos)
+    if world > 1:
+        # the same problem on rank 0's GPU alone, in the same run on the same box: what the N-rank time is compared with
+        single = None
+        if rank == 0:
+            single, _ = multi_gpu.heads_prefill(S, Hq, Hkv, 0, 1, dev, steps=2, warmup=1, seed=2)
+        torch.distributed.barrier()
+        if rank == 0:
+            res["single_gpu_ms_same_run"] = single["ms"]
+            res["speedup_over_single_gpu"] = single["ms"] / res["ms"]
+            res["strong_scaling_efficiency"] = single["ms"] / res["ms"] / min(world, Hkv)
+        torch.cuda.empty_cache()
     if rank == 0:
         res["workload"] = ("BASELINE configs[2]: causal prefill, seq 131072, 64 q / 8 kv heads, KV-head groups sharded over the "
                            "ranks, no collective; strong scaling (fixed problem)")
@@ -421,6 +432,16 @@ def sharded_extra(rank, world, dev):
     pos = multi_gpu.owned_sample_positions(S, world, 64)
     res, sample = multi_gpu.seq_prefill(S, Hq, Hkv, rank, world, dev, steps=1, warmup=1 if world > 1 else 0, seed=4,
                                         sample_positions=pos)
+    if world > 1:
+        single = None
+        if rank == 0:   # one GPU, the same code path (two chunks on one rank, no exchange), one step without warm-up
+            single, _ = multi_gpu.seq_prefill(S, Hq, Hkv, 0, 1, dev, steps=1, warmup=0, seed=4)
+        torch.distributed.barrier()
+        if rank == 0:
+            res["single_gpu_ms_same_run"] = single["ms"]
+            res["speedup_over_single_gpu"] = single["ms"] / res["ms"]
+            res["strong_scaling_efficiency"] = single["ms"] / res["ms"] / world
+        torch.cuda.empty_cache()
     if rank == 0:
         res["workload"] = ("BASELINE configs[4]: causal prefill, seq 1048576, 32 q / 4 kv heads, 2N zig-zag sequence chunks; "
                            "Q all-gather + fp32 (O, LSE) partials over NCCL, merged by the owner; strong scaling"
