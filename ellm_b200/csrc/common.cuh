@@ -78,6 +78,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Transposes an 8x8 matrix of 16-bit values held across the warp (thread = row lane/4, columns
+// (lane%4)*2 and +1 in one register).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
+
 // Byte offset of 16-byte chunk `chunk` (0..15) of row `row` in a tile of 256-byte
 // rows, XOR-swizzled so that the 8 rows one ldmatrix phase touches fall in 8
 // different bank groups.
@@ -177,6 +185,81 @@ __device__ __forceinline__ void qk_step(const uint32_t (&qf)[8][4], uint32_t k_b
             ldmatrix_x4(k_base + swz_off(krow, ks * 2 + (mat & 1)), b0, b1, b2, b3);
             mma_bf16_16816(s[2 * jp], qf[ks], b0, b1);
             mma_bf16_16816(s[2 * jp + 1], qf[ks], b2, b3);
+        }
+    }
+}
+
+// ---- the decode kernel's stage, keys as the M dimension ----------------------------------
+// One warp, 16 keys against up to 8 * NB query heads of one group.  With a handful of query heads
+// per KV head the heads make a poor M for a 16-row MMA (half of the rows empty at 8 heads), so the
+// products are taken transposed:  S^T[16 keys x 8 heads] = K . Q^T  (A = the K rows as they lie in
+// shared memory, B = the query heads, register-resident) and  O^T[128 dims x 8 heads] += V^T . P^T
+// (A = V read with a transposing ldmatrix, B = P^T, which is the S^T fragment turned by movmatrix).
+// Per 16 keys: 8 + 8 MMAs per block of 8 heads instead of 16 + 16, half the exponentials, and O
+// takes 32 registers per block of 8 heads.
+// Thread layout: of every S^T / O^T fragment a thread owns heads (lane%4)*2, +1 of the block and
+// keys (or dims) lane/4 and lane/4 + 8 - so the running maximum m and the sum l of a head live in
+// the 8 lanes that share lane%4; l holds this thread's keys only until the piece is finalised.
+template <int NB>
+__device__ __forceinline__ void decode_stage_t(const uint32_t (&qb)[NB][8][2], uint32_t k_base, uint32_t v_base,
+                                               long long kfirst, long long len, float scale_log2, float (&m)[NB][2],
+                                               float (&l)[NB][2], float (&oT)[NB][8][4], int lane) {
+    const int mat = lane >> 3, mrow = lane & 7;
+    float s[NB][4];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
+    {
+        // ldmatrix.x4: (keys 0-7, d 0-7), (keys 8-15, d 0-7), (keys 0-7, d 8-15), (keys 8-15, d 8-15) of this k16 step over head_dim
+        const int krow = (mat & 1) * 8 + mrow;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            uint32_t a[4];
+            ldmatrix_x4(k_base + swz_off(krow, ks * 2 + (mat >> 1)), a[0], a[1], a[2], a[3]);
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) mma_bf16_16816(s[nb], a, qb[nb][ks][0], qb[nb][ks][1]);
+        }
+    }
+    const bool in_lo = kfirst + (lane >> 2) < len, in_hi = kfirst + (lane >> 2) + 8 < len;
+    uint32_t pb[NB][2];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float s_lo = in_lo ? s[nb][h] * scale_log2 : -INFINITY;
+            const float s_hi = in_hi ? s[nb][h + 2] * scale_log2 : -INFINITY;
+            float mx = fmaxf(s_lo, s_hi);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            mx = fmaxf(mx, m[nb][h]);
+            // a head that has seen no key yet keeps m = -inf; subtract 0 there so that
+            // exp2(-inf - 0) = 0 instead of exp2(-inf + inf) = NaN
+            const float msub = (mx == -INFINITY) ? 0.0f : mx;
+            const float corr = fast_exp2(m[nb][h] - msub);
+            m[nb][h] = mx;
+            const float p_lo = fast_exp2(s_lo - msub), p_hi = fast_exp2(s_hi - msub);
+            l[nb][h] = l[nb][h] * corr + (p_lo + p_hi);
+            s[nb][h] = p_lo;
+            s[nb][h + 2] = p_hi;
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) {
+                oT[nb][mt][h] *= corr;
+                oT[nb][mt][h + 2] *= corr;
+            }
+        }
+        // P^T as the B operand: the two 8 x 8 blocks (keys 0-7 / 8-15 by heads) turned over
+        pb[nb][0] = movmatrix_trans(pack_bf16(s[nb][0], s[nb][1]));
+        pb[nb][1] = movmatrix_trans(pack_bf16(s[nb][2], s[nb][3]));
+    }
+    {
+        // ldmatrix.x4.trans: (d 0-7, keys 0-7), (d 8-15, keys 0-7), (d 0-7, keys 8-15), (d 8-15, keys 8-15) of a 16-dim block
+        const int vrow = (mat >> 1) * 8 + mrow;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            uint32_t a[4];
+            ldmatrix_x4_trans(v_base + swz_off(vrow, mt * 2 + (mat & 1)), a[0], a[1], a[2], a[3]);
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) mma_bf16_16816(oT[nb][mt], a, pb[nb][0], pb[nb][1]);
         }
     }
 }

@@ -22,9 +22,12 @@
 // Inside a CTA the 4 warps are independent streams: warp w owns keys
 // [16w, 16w+16) of every tile, copies them global->shared itself (cp.async, 16 B
 // per lane, 512 B contiguous per instruction, XOR-swizzled rows), and keeps its
-// own online-softmax state; the warps only meet at the end of a piece.  Q.K^T and
-// P.V run on the warp-level tensor-core MMA with the <=16 query heads of the
-// group as the M dimension, so one K/V read serves the whole group.
+// own online-softmax state; the warps only meet at the end of a piece.  The
+// products run on the warp-level tensor-core MMA with the warp's 16 KEYS as the M
+// dimension and the group's query heads, 8 to a block, as N (decode_stage_t in
+// common.cuh), so one K/V read serves the whole group and a group of 8 heads
+// fills the MMA exactly.  NB = blocks of 8 heads per segment (1 for groups of up
+// to 8 heads, else 2).
 #pragma once
 #include "common.cuh"
 
@@ -122,6 +125,7 @@ __device__ __forceinline__ int dec_find_seq(const int* prefix, int batch, long l
     return lo;
 }
 
+template <int NB>
 __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     int* prefix = reinterpret_cast<int*>(smem + kDecWarps * kDecStages * kDecWarpStageBytes);   // [kDecMaxBatch + 1]
@@ -148,7 +152,6 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
         return;
     }
 
-    const int r0 = lane >> 2;  // this thread's rows: r0 and r0 + 8
     long long t = t_begin;
     while (t < t_end) {
         // ---- locate the piece: segment of tile t and how far it runs ----
@@ -246,29 +249,29 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
             }
         }
 
-        // ---- Q fragments: rows = query heads kvh*group + gt*16 + r ----
-        uint32_t qf[8][4];
-        {
-            const int c0 = (lane & 3) * 2;
-            const __nv_bfloat16* qrow0 =
-                p.q + (static_cast<long long>(b) * p.q_heads + kvh * p.group + gt * 16 + r0) * kHeadDim;
-            const __nv_bfloat16* qrow1 = qrow0 + 8 * kHeadDim;
-            const bool v0 = r0 < rows_valid, v1 = r0 + 8 < rows_valid;
+        // ---- Q as B fragments: head nb*8 + lane/4 of the segment, dims ks*16 + (lane%4)*2 (+1), +8 ----
+        uint32_t qb[NB][8][2];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            const int head = nb * 8 + (lane >> 2);
+            const bool hv = head < rows_valid;
+            const __nv_bfloat16* qrow =
+                p.q + (static_cast<long long>(b) * p.q_heads + kvh * p.group + gt * 16 + (hv ? head : 0)) * kHeadDim + (lane & 3) * 2;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
-                qf[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(qrow0 + ks * 16 + c0) : 0u;
-                qf[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(qrow1 + ks * 16 + c0) : 0u;
-                qf[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(qrow0 + ks * 16 + c0 + 8) : 0u;
-                qf[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(qrow1 + ks * 16 + c0 + 8) : 0u;
+                qb[nb][ks][0] = hv ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16) : 0u;
+                qb[nb][ks][1] = hv ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8) : 0u;
             }
         }
 
-        RowState st;
-        st.m[0] = st.m[1] = -INFINITY;
-        st.l[0] = st.l[1] = 0.0f;
-        float o[16][4];
+        float hm[NB][2], hl[NB][2], oT[NB][8][4];
 #pragma unroll
-        for (int nb = 0; nb < 16; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.0f;
+        for (int nb = 0; nb < NB; ++nb) {
+            hm[nb][0] = hm[nb][1] = -INFINITY;
+            hl[nb][0] = hl[nb][1] = 0.0f;
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) oT[nb][mt][0] = oT[nb][mt][1] = oT[nb][mt][2] = oT[nb][mt][3] = 0.0f;
+        }
 
         for (int it = 0; it < ntiles; ++it) {
             if (it + kDecStages - 1 < ntiles) issue(it + kDecStages - 1);
@@ -278,46 +281,45 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
             const long long kfirst = key0 + static_cast<long long>(it) * kDecTileKeys;
             if (kfirst < len) {  // warp-uniform: this warp's 16 keys are not all past the end
                 const uint32_t sK = warp_smem + (it % kDecStages) * kDecWarpStageBytes;
-                float s[2][4];
-                qk_step<2>(qf, sK, s, lane);
-                const long long kc = kfirst + (lane & 3) * 2;
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const bool in0 = kc + 8 * j < len, in1 = kc + 8 * j + 1 < len;
-                    s[j][0] = in0 ? s[j][0] * p.scale_log2 : -INFINITY;
-                    s[j][1] = in1 ? s[j][1] * p.scale_log2 : -INFINITY;
-                    s[j][2] = in0 ? s[j][2] * p.scale_log2 : -INFINITY;
-                    s[j][3] = in1 ? s[j][3] * p.scale_log2 : -INFINITY;
-                }
-                softmax_pv_step<2>(s, st, o, sK + 16 * kRowBytes, lane);
+                decode_stage_t<NB>(qb, sK, sK + 16 * kRowBytes, kfirst, len, p.scale_log2, hm, hl, oT, lane);
             }
             __syncwarp();  // all lanes done with this stage before it is refilled
         }
         cp_async_wait<0>();
 
         // ---- end of piece: combine the 4 warps through shared memory ----
+        // a head's sum is spread over the 8 lanes that share lane%4 (their keys differ)
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
-            st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
-        }
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                hl[nb][h] += __shfl_xor_sync(0xffffffffu, hl[nb][h], 4);
+                hl[nb][h] += __shfl_xor_sync(0xffffffffu, hl[nb][h], 8);
+                hl[nb][h] += __shfl_xor_sync(0xffffffffu, hl[nb][h], 16);
+            }
         __syncthreads();  // every warp has drained its ring; smem is free
-        float* so = reinterpret_cast<float*>(smem);             // [warps][16][128]
+        float* so = reinterpret_cast<float*>(smem);             // [warps][16 heads][128]
         float* sm = so + kDecWarps * 16 * kHeadDim;             // [warps][16]
         float* sl = sm + kDecWarps * 16;                        // [warps][16]
         {
             float* wo = so + warp * 16 * kHeadDim;
-            const int c0 = (lane & 3) * 2;
+            const int d0 = lane >> 2, h0 = (lane & 3) * 2;
 #pragma unroll
-            for (int nb = 0; nb < 16; ++nb) {
-                *reinterpret_cast<float2*>(wo + r0 * kHeadDim + nb * 8 + c0) = make_float2(o[nb][0], o[nb][1]);
-                *reinterpret_cast<float2*>(wo + (r0 + 8) * kHeadDim + nb * 8 + c0) = make_float2(o[nb][2], o[nb][3]);
-            }
-            if ((lane & 3) == 0) {
-                sm[warp * 16 + r0] = st.m[0];
-                sm[warp * 16 + r0 + 8] = st.m[1];
-                sl[warp * 16 + r0] = st.l[0];
-                sl[warp * 16 + r0 + 8] = st.l[1];
+            for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+                for (int mt = 0; mt < 8; ++mt) {
+                    float* col = wo + (nb * 8 + h0) * kHeadDim + mt * 16 + d0;
+                    col[0] = oT[nb][mt][0];
+                    col[kHeadDim] = oT[nb][mt][1];
+                    col[8] = oT[nb][mt][2];
+                    col[kHeadDim + 8] = oT[nb][mt][3];
+                }
+                if ((lane >> 2) == 0) {
+                    sm[warp * 16 + nb * 8 + h0] = hm[nb][0];
+                    sm[warp * 16 + nb * 8 + h0 + 1] = hm[nb][1];
+                    sl[warp * 16 + nb * 8 + h0] = hl[nb][0];
+                    sl[warp * 16 + nb * 8 + h0 + 1] = hl[nb][1];
+                }
             }
         }
         __syncthreads();

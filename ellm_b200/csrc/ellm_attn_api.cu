@@ -321,7 +321,10 @@ int launch_decode(ellm_attn* h, const int32_t* positions, size_t position_index,
     }
     {
         LaunchScope ls(h, ELLM_KERNEL_DECODE_SPLITKV);
-        launch_dependent(ellm::decode_splitkv_kernel, h->dec_ctas, ellm::kDecThreads, ellm::kDecSmemBytes, h->stream, p);
+        if (h->group <= 8)   // blocks of 8 query heads per segment: one for groups of up to 8 heads, else two
+            launch_dependent(ellm::decode_splitkv_kernel<1>, h->dec_ctas, ellm::kDecThreads, ellm::kDecSmemBytes, h->stream, p);
+        else
+            launch_dependent(ellm::decode_splitkv_kernel<2>, h->dec_ctas, ellm::kDecThreads, ellm::kDecSmemBytes, h->stream, p);
     }
     ELLM_CUDA(cudaGetLastError());
     const unsigned blocks = static_cast<unsigned>(batch * h->d.q_heads);
@@ -530,7 +533,8 @@ int ellm_attn_create(const ellm_attn_desc* desc, ellm_attn** out) {
     }
     *h->status_host = 0;
     if (cudaMemset(h->status_dev, 0, 4 * sizeof(int)) != cudaSuccess) return cleanup(fail(ELLM_ERR_CUDA, "memset failed"));
-    if (cudaFuncSetAttribute(ellm::decode_splitkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kDecSmemBytes) != cudaSuccess ||
+    if (cudaFuncSetAttribute(ellm::decode_splitkv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kDecSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(ellm::decode_splitkv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kDecSmemBytes) != cudaSuccess ||
         cudaFuncSetAttribute(ellm::prefill_warp_mma_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kPfSmemBytes) != cudaSuccess ||
         cudaFuncSetAttribute(ellm::prefill_warp_mma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kPfSmemBytes) != cudaSuccess)
         return cleanup(fail(ELLM_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(cudaGetLastError())));
@@ -1231,7 +1235,8 @@ int noalloc_setup(int device, NoAllocDevice** out) {
         int major = 0;
         ELLM_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
         if (major != 10) return fail(ELLM_ERR_UNSUPPORTED, "device %d is not sm_100", device);
-        ELLM_CUDA(cudaFuncSetAttribute(ellm::decode_splitkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kDecSmemBytes));
+        ELLM_CUDA(cudaFuncSetAttribute(ellm::decode_splitkv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kDecSmemBytes));
+        ELLM_CUDA(cudaFuncSetAttribute(ellm::decode_splitkv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kDecSmemBytes));
         nd.scratch = static_cast<unsigned char*>(ptr);
         nd.ready = true;
     }
@@ -1299,7 +1304,8 @@ extern "C" int ellm_attn_decode_noalloc(const void* q, const void* k_cache, cons
     p.scale_log2 = scale * ellm::kLog2e;
     p.num_ctas = num_ctas;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    ellm::decode_splitkv_kernel<<<num_ctas, ellm::kDecThreads, ellm::kDecSmemBytes, s>>>(p);
+    if (group <= 8) ellm::decode_splitkv_kernel<1><<<num_ctas, ellm::kDecThreads, ellm::kDecSmemBytes, s>>>(p);
+    else ellm::decode_splitkv_kernel<2><<<num_ctas, ellm::kDecThreads, ellm::kDecSmemBytes, s>>>(p);
     ELLM_CUDA(cudaGetLastError());
     const unsigned blocks = static_cast<unsigned>(batch_size * q_heads);
     ELLM_CUDA(launch_merge(p, batch_size, blocks, nullptr, out, lse, s, false));
