@@ -697,10 +697,10 @@ def main():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_splitkv_kernel launch on this workload
-# (609.91 MB read + 3.76 / 4.55 MB written, two launches), from an `ncu --set full --clock-control none
+# (609.96 / 609.91 MB read + 4.51 / 4.61 MB written, two launches of decode_splitkv_kernel<1>), from an `ncu --set full --clock-control none
 # -k regex:decode_splitkv -s 6 -c 2` capture of `python bench.py --steps 2 --warmup 3 --min-seconds 0.001
 # --no-extra --no-cpu-baseline` on a B200.  A constant of that capture, not measured by this run.
-TRAFFIC_BYTES_PER_LAUNCH = 614.07e6
+TRAFFIC_BYTES_PER_LAUNCH = 614.49e6
 TRAFFIC_SOURCE = "ncu capture of this workload (dram__bytes_read.sum + dram__bytes_write.sum, one launch); a recorded constant"
 
 if __name__ == "__main__":
