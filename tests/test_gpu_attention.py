@@ -61,6 +61,16 @@ def test_decode_wide_group_uses_two_head_tiles():
     _check(case)
 
 
+@pytest.mark.parametrize("group", [1, 2, 3, 5, 7, 8, 9, 12, 15, 16, 17, 33])
+def test_decode_every_group_size(group):
+    """The decode kernel puts a segment's query heads in blocks of 8 on the N side of its products (one
+    block for groups up to 8, two for 9-16, several segments above 16): every fill of the blocks, with
+    two KV heads so that a segment's heads are not the tensor's first, against the oracle."""
+    case = Case(seed=400 + group, interval=1, batch=3, q_heads=2 * group, kv_heads=2, max_seq=700,
+                positions=[699, 64, 200], poison=True)
+    _check(case)
+
+
 def test_decode_long_contexts_many_pieces():
     # enough tiles that every CTA gets a piece and sequences span several CTAs
     case = Case(seed=9, interval=1, batch=4, q_heads=32, kv_heads=4, max_seq=8192,
