@@ -84,6 +84,9 @@ inline int skinny_smem_bytes(int k_chunks, int cols, int pass_chunks, int m_rows
     return skinny_x_bytes(k_chunks, m_rows) + slice + 128;
 }
 
+// kNB16: blocks of 16 columns a CTA may own (its accumulators): 1 for the 16-column slices of the
+// decode-step shapes, kSkMaxCols / 16 for anything up to kSkMaxCols columns.
+template <int kNB16>
 __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const SkinnyParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -170,9 +173,9 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
         }
     }
 
-    float acc[kSkMaxCols / 8][4];
+    float acc[kNB16 * 2][4];
 #pragma unroll
-    for (int i = 0; i < kSkMaxCols / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+    for (int i = 0; i < kNB16 * 2; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
     const int nblocks16 = p.cols >> 4;
     const int a_row = lane & 15;
     const bool a_live = a_row < p.m_rows;
@@ -185,6 +188,34 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
         __syncthreads();
         const int c_begin = pass * p.pass_chunks;
         const int steps = min(p.pass_chunks, p.k_chunks - c_begin) >> 1;   // 16-wide k steps of this pass
+        if (kNB16 == 1) {
+            // one block of 16 columns: the fragments of four of the warp's k-steps are requested before
+            // the first of their products is issued (the steps are a dependent chain through the
+            // accumulators; fetched one at a time, every step also waits for its own two loads).  The
+            // products run in the same order as in the general loop below, so the sums are the same bits.
+            for (int step = warp; step < steps; step += 4 * kSkWarps) {
+                uint32_t af[4][4], bf[4][4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int st = step + u * kSkWarps;
+                    if (st < steps) {
+                        const int piece = c_begin + st * 2 + (lane >> 4);
+                        const uint32_t addr = a_live ? x_base + (a_row * p.k_chunks + (piece ^ (a_row & 7))) * 16 : zero_addr;
+                        ldmatrix_x4(addr, af[u][0], af[u][1], af[u][2], af[u][3]);
+                        const int n = ((lane >> 4) << 3) + (lane & 7), wpiece = st * 2 + ((lane >> 3) & 1);
+                        ldmatrix_x4(w_base + (n * p.pass_chunks + (wpiece ^ (n & 7))) * 16, bf[u][0], bf[u][1], bf[u][2], bf[u][3]);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (step + u * kSkWarps < steps) {
+                        mma_bf16_16816(acc[0], af[u], bf[u][0], bf[u][1]);
+                        mma_bf16_16816(acc[1], af[u], bf[u][2], bf[u][3]);
+                    }
+                }
+            }
+            continue;
+        }
         for (int step = warp; step < steps; step += kSkWarps) {
             uint32_t af[4];
             {
@@ -193,7 +224,7 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
                 ldmatrix_x4(addr, af[0], af[1], af[2], af[3]);
             }
 #pragma unroll
-            for (int nb = 0; nb < kSkMaxCols / 16; ++nb) {
+            for (int nb = 0; nb < kNB16; ++nb) {
                 if (nb < nblocks16) {
                     // matrices: (cols 0-7, k 0-7), (cols 0-7, k 8-15), (cols 8-15, k 0-7), (cols 8-15, k 8-15)
                     const int n = nb * 16 + ((lane >> 4) << 3) + (lane & 7), piece = step * 2 + ((lane >> 3) & 1);
@@ -211,7 +242,7 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
     {
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
 #pragma unroll
-        for (int i = 0; i < kSkMaxCols / 8; ++i) {
+        for (int i = 0; i < kNB16 * 2; ++i) {
             if (i * 8 < p.cols) {
                 float* dst = part + (warp * kSkRows) * p.cols + i * 8 + c0;
                 dst[r0 * p.cols] = acc[i][0];
