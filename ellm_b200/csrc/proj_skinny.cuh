@@ -94,6 +94,10 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
     const uint32_t x_base = smem_u32(smem), zero_addr = x_base + p.m_rows * p.k_chunks * 16, w_base = x_base + x_bytes;
     const int n0 = blockIdx.x * p.cols;
     const int passes = (p.k_chunks + p.pass_chunks - 1) / p.pass_chunks;
+    // 16-column slices with at most 8 activation rows (the decode-step shapes) read their fragments with
+    // plain 16-byte shared-memory loads instead of ldmatrix (see the product loop); both tiles are then
+    // laid out for that: the 16-byte piece p of row r sits at p ^ ((r & 1) << 2)
+    const bool few_rows = kNB16 == 1 && p.m_rows <= 8 && (p.k_chunks & 3) == 0 && (p.pass_chunks & 3) == 0;
 
     // pieces [pass * pass_chunks, ...) of every row of the slice; rows past N arrive as zeros
     auto request_pass = [&](int pass) {
@@ -105,7 +109,7 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
             const bool real = n0 + n < p.n_cols;
             const __nv_bfloat16* src = p.w + (real ? (static_cast<long long>(n0 + n) * p.k_chunks + c_begin) * 8 : 0);
             const uint32_t dst = w_base + n * p.pass_chunks * 16;
-            const int sw = n & 7;
+            const int sw = few_rows ? (n & 1) << 2 : n & 7;
             for (int cc = threadIdx.x; cc < pc; cc += kSkThreads)
                 cp_async_16(dst + ((cc ^ sw) << 4), src + (real ? cc * 8 : 0), real ? 16 : 0);
         }
@@ -148,7 +152,7 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
             const uint4* src = reinterpret_cast<const uint4*>(p.a + (live ? m * p.lda : 0));
             const float rrms = live ? block_row_rrms(src, p.k_chunks, p.k_chunks * 8, p.input_norm_eps, warp_sums, &s_rrms) : 0.0f;
             for (int c = threadIdx.x; c < p.k_chunks; c += kSkThreads)
-                *reinterpret_cast<uint4*>(smem + (m * p.k_chunks + (c ^ (m & 7))) * 16) =
+                *reinterpret_cast<uint4*>(smem + (m * p.k_chunks + (c ^ (few_rows ? (m & 1) << 2 : m & 7))) * 16) =
                     live ? scale_piece(src[c], rrms) : make_uint4(0u, 0u, 0u, 0u);
         }
     } else {
@@ -156,10 +160,10 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
             const bool live = (m % p.max_batch) < p.batch;
             const __nv_bfloat16* src = p.a + (live ? m * p.lda : 0);
             for (int c = threadIdx.x; c < p.k_chunks; c += kSkThreads)
-                cp_async_16(x_base + (m * p.k_chunks + (c ^ (m & 7))) * 16, src + c * 8, live ? 16 : 0);
+                cp_async_16(x_base + (m * p.k_chunks + (c ^ (few_rows ? (m & 1) << 2 : m & 7))) * 16, src + c * 8, live ? 16 : 0);
         }
     }
-    if (threadIdx.x < 8) cp_async_16(zero_addr + threadIdx.x * 16, p.a, 0);   // the row every missing row reads
+    if (threadIdx.x < 8) cp_async_16(zero_addr + threadIdx.x * 16, p.a, 0);   // 128 zero bytes: what every missing row reads
     cp_async_commit();
     // the residual values of this thread's outputs, requested now, used at the very end
     const int outs = p.m_rows * p.cols;
@@ -173,6 +177,10 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
         }
     }
 
+    // (16-column slices, at most 8 rows: four accumulators of the transposed products, see below)
+    float tacc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) tacc[i][0] = tacc[i][1] = tacc[i][2] = tacc[i][3] = 0.0f;
     float acc[kNB16 * 2][4];
 #pragma unroll
     for (int i = 0; i < kNB16 * 2; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
@@ -188,29 +196,39 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
         __syncthreads();
         const int c_begin = pass * p.pass_chunks;
         const int steps = min(p.pass_chunks, p.k_chunks - c_begin) >> 1;   // 16-wide k steps of this pass
-        if (kNB16 == 1) {
-            // one block of 16 columns: the fragments of four of the warp's k-steps are requested before
-            // the first of their products is issued (the steps are a dependent chain through the
-            // accumulators; fetched one at a time, every step also waits for its own two loads).  The
-            // products run in the same order as in the general loop below, so the sums are the same bits.
-            for (int step = warp; step < steps; step += 4 * kSkWarps) {
-                uint32_t af[4][4], bf[4][4];
+        if (few_rows) {
+            // 16 columns, at most 8 activation rows: the products are taken transposed - the slice's 16
+            // columns are the M side of m16n8k16, the rows the N side, one product per 16 k instead of
+            // two - and the fragments come from plain 16-byte shared-memory loads: ldmatrix delivers
+            // one 8x8 matrix per ~3 clocks per SM here (measured: the slice's 128 KB took 2.4 us through
+            // it, whatever the products did), a 16-byte load per lane four times that.  A lane's 16 bytes
+            // of a row are 4 k-pairs; which k a fragment register stands for is free as long as the
+            // slice and the rows agree, so lane (g, t) reads piece 4 * kb + t of slice rows g and g + 8
+            // and of activation row g, and feeds register pairs 0,1 to one product and 2,3 to the next.
+            // A quarter-warp then touches 8 different pieces (rows g, g + 1 sit in opposite halves of
+            // a 128-byte bank line): no conflicts.  Four independent accumulators, added at the end.
+            const int g = lane >> 2, t = lane & 3, sw = (g & 1) << 2;
+            const int kblocks = steps >> 1;   // 32-k blocks of this pass
+            const uint32_t w_lo = w_base + g * p.pass_chunks * 16, w_hi = w_lo + 8 * p.pass_chunks * 16;
+            const bool x_live = g < p.m_rows;
+            const uint32_t x_row = x_base + g * p.k_chunks * 16;
+            for (int kb = warp; kb < kblocks; kb += 2 * kSkWarps) {
+                uint4 lo[2], hi[2], xr[2];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int st = step + u * kSkWarps;
-                    if (st < steps) {
-                        const int piece = c_begin + st * 2 + (lane >> 4);
-                        const uint32_t addr = a_live ? x_base + (a_row * p.k_chunks + (piece ^ (a_row & 7))) * 16 : zero_addr;
-                        ldmatrix_x4(addr, af[u][0], af[u][1], af[u][2], af[u][3]);
-                        const int n = ((lane >> 4) << 3) + (lane & 7), wpiece = st * 2 + ((lane >> 3) & 1);
-                        ldmatrix_x4(w_base + (n * p.pass_chunks + (wpiece ^ (n & 7))) * 16, bf[u][0], bf[u][1], bf[u][2], bf[u][3]);
+                for (int u = 0; u < 2; ++u) {
+                    const int c = (kb + u * kSkWarps) * 4 + t;
+                    if (kb + u * kSkWarps < kblocks) {
+                        lo[u] = lds128(w_lo + ((c ^ sw) << 4));
+                        hi[u] = lds128(w_hi + ((c ^ sw) << 4));
+                        xr[u] = lds128(x_live ? x_row + (((c_begin + c) ^ sw) << 4) : zero_addr + ((((c_begin + c) ^ sw) & 7) << 4));
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (step + u * kSkWarps < steps) {
-                        mma_bf16_16816(acc[0], af[u], bf[u][0], bf[u][1]);
-                        mma_bf16_16816(acc[1], af[u], bf[u][2], bf[u][3]);
+                for (int u = 0; u < 2; ++u) {
+                    if (kb + u * kSkWarps < kblocks) {
+                        const uint32_t a0[4] = {lo[u].x, hi[u].x, lo[u].y, hi[u].y}, a1[4] = {lo[u].z, hi[u].z, lo[u].w, hi[u].w};
+                        mma_bf16_16816(tacc[2 * u], a0, xr[u].x, xr[u].y);
+                        mma_bf16_16816(tacc[2 * u + 1], a1, xr[u].z, xr[u].w);
                     }
                 }
             }
@@ -239,7 +257,15 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
     // every warp is done with the slice: the partial sums go over it
     __syncthreads();
     float* part = reinterpret_cast<float*>(smem + x_bytes);   // [warp][row][col]
-    {
+    if (few_rows) {
+        // transposed accumulators: this lane holds columns lane/4 and lane/4 + 8 of rows (lane%4)*2, +1
+        const int col = lane >> 2, m0 = (lane & 3) * 2;
+        float* dst = part + (warp * kSkRows + m0) * p.cols + col;
+        dst[0] = (tacc[0][0] + tacc[1][0]) + (tacc[2][0] + tacc[3][0]);
+        dst[p.cols] = (tacc[0][1] + tacc[1][1]) + (tacc[2][1] + tacc[3][1]);
+        dst[8] = (tacc[0][2] + tacc[1][2]) + (tacc[2][2] + tacc[3][2]);
+        dst[p.cols + 8] = (tacc[0][3] + tacc[1][3]) + (tacc[2][3] + tacc[3][3]);
+    } else {
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
 #pragma unroll
         for (int i = 0; i < kNB16 * 2; ++i) {
