@@ -90,6 +90,18 @@ def test_matmul_decode_dead_slots_no_residual():
     _matmul_add(6, interval=1, max_batch=5, batch=3, n=1024, k=512, residual=False)
 
 
+@pytest.mark.parametrize("rows", [2, 8, 9])
+def test_matmul_decode_row_counts_around_the_fragment_paths(rows):
+    # up to 8 rows of a 16-column slice take the transposed products fed by 16-byte shared-memory loads,
+    # 9 and more the ldmatrix loop
+    _matmul_add(40 + rows, interval=1, max_batch=rows, batch=rows, n=1024, k=1024, residual=True)
+
+
+def test_matmul_decode_long_rows_take_the_slice_in_two_passes():
+    # 16 columns x 12288 do not fit shared memory at once: the slice comes in two passes over K
+    _matmul_add(50, interval=1, max_batch=3, batch=3, n=256, k=12288, residual=True)
+
+
 def _matmul3(seed, interval, max_batch, batch, q_heads, kv_heads, hidden, max_seq, position_index=0, positions=None,
              weights=True, one_matrix=False, pairing=None):
     g = torch.Generator().manual_seed(seed)
