@@ -125,6 +125,57 @@ __device__ __forceinline__ int dec_find_seq(const int* prefix, int batch, long l
     return lo;
 }
 
+// Segment-aligned split.  The flat rule (assign_range over all tiles) gives every CTA the same
+// number of tiles, but a CTA whose range crosses a segment boundary has two pieces: it drains its
+// ring, combines and writes a partial, then starts again with an empty ring - about 3 us more than
+// its neighbours, and the grid ends with its last CTA.  With many segments that is what the even
+// split costs everywhere; with few (a step of one or a few sequences: every segment has many CTAs
+// and the kernel is a few microseconds long) those few CTAs decide the step.  There the CTA
+// boundaries are snapped to the segment boundaries instead: segment [P, P + T) of the flat tile
+// list gets CTAs [snap(P), snap(P + T)), snap(x) = round(x * ctas / total), and splits its T tiles
+// evenly over them, so every CTA has one piece.  The decision depends on the positions only and is
+// taken identically by every CTA of the decode grid and of the merge grid.
+// (only called where total <= 32 * ctas and ctas is a few hundred: 32-bit arithmetic, no 64-bit division)
+__device__ __forceinline__ long long dec_snap(long long tile, long long total, long long ctas) {
+    return static_cast<long long>((static_cast<unsigned>(tile) * static_cast<unsigned>(ctas) + static_cast<unsigned>(total) / 2u) /
+                                  static_cast<unsigned>(total));
+}
+__device__ inline bool dec_split_is_aligned(const DecodeParams& p, const int* prefix, long long segs_per_seq, long long total) {
+    // few segments, at least a tile per CTA, and short enough that a rounding of one CTA per segment
+    // (at most 1/8 of a segment's share) costs less than the second pieces would
+    if (static_cast<long long>(p.batch) * segs_per_seq * 8 > p.num_ctas || total < p.num_ctas || total > 32LL * p.num_ctas || p.num_ctas > 4096) return false;
+    for (int b = 0; b < p.batch; ++b) {
+        const long long tiles_b = prefix[b + 1] - prefix[b];
+        if (tiles_b == 0) continue;
+        const long long base = static_cast<long long>(prefix[b]) * segs_per_seq;
+        for (long long j = 0; j < segs_per_seq; ++j)   // every segment needs a CTA of its own
+            if (dec_snap(base + (j + 1) * tiles_b, total, p.num_ctas) == dec_snap(base + j * tiles_b, total, p.num_ctas)) return false;
+    }
+    return true;
+}
+// The tile range of CTA `cta` under the segment-aligned split; false when it has none.
+__device__ inline bool dec_aligned_range(const DecodeParams& p, const int* prefix, long long segs_per_seq, long long total,
+                                         long long cta, long long* t_begin, long long* t_end) {
+    for (int b = 0; b < p.batch; ++b) {
+        const long long tiles_b = prefix[b + 1] - prefix[b];
+        if (tiles_b == 0) continue;
+        const long long base = static_cast<long long>(prefix[b]) * segs_per_seq;
+        if (cta >= dec_snap(base + segs_per_seq * tiles_b, total, p.num_ctas)) continue;   // a later sequence
+        for (long long j = 0; j < segs_per_seq; ++j) {
+            const long long first = base + j * tiles_b;
+            const long long c0 = dec_snap(first, total, p.num_ctas), c1 = dec_snap(first + tiles_b, total, p.num_ctas);
+            if (cta >= c0 && cta < c1) {
+                long long lb, le;
+                if (!assign_range(tiles_b, c1 - c0, cta - c0, &lb, &le)) return false;
+                *t_begin = first + lb;
+                *t_end = first + le;
+                return true;
+            }
+        }
+    }
+    return false;
+}
+
 template <int NB>
 __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -146,8 +197,11 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
     dec_build_prefix(p, prefix, lens);
     const long long segs_per_seq = static_cast<long long>(p.kv_heads) * p.gtiles;
     const long long total = static_cast<long long>(prefix[p.batch]) * segs_per_seq;
-    long long t_begin, t_end;
-    if (!assign_range(total, p.num_ctas, blockIdx.x, &t_begin, &t_end)) {
+    long long t_begin = 0, t_end = 0;
+    const bool has_tiles = dec_split_is_aligned(p, prefix, segs_per_seq, total)
+                               ? dec_aligned_range(p, prefix, segs_per_seq, total, blockIdx.x, &t_begin, &t_end)
+                               : assign_range(total, p.num_ctas, blockIdx.x, &t_begin, &t_end);
+    if (!has_tiles) {
         if (!waited) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         return;
     }

@@ -77,8 +77,16 @@ __global__ void __launch_bounds__(kWarps * 32) decode_merge_kernel(const DecodeP
     long long c_first = 0, c_last = -1;
     if (tiles_b > 0) {
         const long long t0 = static_cast<long long>(s_prefix[b]) * segs_per_seq + static_cast<long long>(seg_in_seq) * tiles_b;
-        c_first = cta_of_tile(total, p.num_ctas, t0);
-        c_last = cta_of_tile(total, p.num_ctas, t0 + tiles_b - 1);
+        if (dec_split_is_aligned(p, s_prefix, segs_per_seq, total)) {
+            // the decode grid snapped its CTA boundaries to the segments: this segment's CTAs, of which
+            // the first min(CTAs, tiles) have a piece
+            c_first = dec_snap(t0, total, p.num_ctas);
+            const long long n = dec_snap(t0 + tiles_b, total, p.num_ctas) - c_first;
+            c_last = c_first + (n < tiles_b ? n : tiles_b) - 1;
+        } else {
+            c_first = cta_of_tile(total, p.num_ctas, t0);
+            c_last = cta_of_tile(total, p.num_ctas, t0 + tiles_b - 1);
+        }
     }
     const int pieces = static_cast<int>(c_last - c_first + 1);
     const float* lse_base = p.part_lse + (c_first + segment) * 16 + r;            // piece i at + i * 16
