@@ -71,6 +71,17 @@ def test_decode_every_group_size(group):
     _check(case)
 
 
+@pytest.mark.parametrize("positions", [[20000, 3000], [30000, 10], [9000], [700, 650, 600, 580]])
+def test_decode_few_segments_split_by_segment(positions):
+    """Steps with few segments snap the decode grid's CTA boundaries to the segment boundaries (one piece
+    per CTA) and the merge kernel derives the same ranges: two ragged sequences (every segment gets CTAs of
+    its own), a long and a one-tile sequence (the short one's segments would get no CTA: back to the even
+    split), one sequence, and four short ones (fewer tiles than CTAs: even split)."""
+    case = Case(seed=500 + len(positions), interval=1, batch=len(positions), q_heads=32, kv_heads=4,
+                max_seq=max(positions) + 2, positions=positions)
+    _check(case)
+
+
 def test_decode_long_contexts_many_pieces():
     # enough tiles that every CTA gets a piece and sequences span several CTAs
     case = Case(seed=9, interval=1, batch=4, q_heads=32, kv_heads=4, max_seq=8192,
