@@ -85,6 +85,23 @@ class Attention:
                                              _ptr(positions_host), position_index,
                                              position_interval, batch_size))
 
+    def bind_host(self, q_host, out_host, position_index, position_interval, batch_size, *,
+                  k_new_host=None, v_new_host=None, lse_host=None, positions_host=None):
+        """run_host for a loop that reuses the same host buffers: the arguments are converted once and the
+        returned callable makes the one C call per step (a decode loop rewrites the buffers' contents, not
+        the buffers).  The buffers are kept alive by the callable."""
+        fn, h = self._lib.ellm_attn_run_host, self._h
+        args = (C.c_void_p(_ptr(q_host)), C.c_void_p(_ptr(k_new_host)), C.c_void_p(_ptr(v_new_host)),
+                C.c_void_p(_ptr(out_host)), C.c_void_p(_ptr(lse_host)), C.c_void_p(_ptr(positions_host)),
+                C.c_size_t(position_index), C.c_size_t(position_interval), C.c_size_t(batch_size))
+        keep = (q_host, k_new_host, v_new_host, out_host, lse_host, positions_host)
+
+        def step(_keep=keep):
+            status = fn(h, *args)
+            if status:
+                L.check(status)
+        return step
+
     def set_option(self, name, value):
         L.check(self._lib.ellm_attn_set_option(self._h, name.encode(), int(value)))
 

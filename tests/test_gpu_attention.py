@@ -135,6 +135,30 @@ def test_run_host_copies_in_and_out():
     _check(case, use_run_host=True, prefill_kernel=L.PREFILL_WARP_MMA)
 
 
+def test_bound_host_step_equals_run_host():
+    """Attention.bind_host converts the host-buffer arguments once; the callable it returns is run_host."""
+    dev = torch.device("cuda:0")
+    case = Case(seed=61, interval=1, batch=3, q_heads=8, kv_heads=2, max_seq=600, positions=[599, 10, 300])
+    want_k, want_v, want_o, want_l = case.oracle()
+    q, ck, cv = case.q.to(dev), case.cache_k.to(dev), case.cache_v.to(dev)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(1, case.max_batch, case.q_heads, dtype=torch.float32, device=dev)
+    op = ellm_b200.Attention.new(q, ck, cv, out, case.max_batch, case.q_heads, case.kv_heads, 128, case.strides, case.scale,
+                                 max_seq=case.max_seq, lse=lse, k_new=torch.zeros_like(case.k_new).to(dev),
+                                 v_new=torch.zeros_like(case.v_new).to(dev))
+    qh, kh, vh = case.q.clone().pin_memory(), case.k_new.clone().pin_memory(), case.v_new.clone().pin_memory()
+    oh = torch.zeros_like(qh).pin_memory()
+    lh = torch.zeros(1, case.max_batch, case.q_heads, dtype=torch.float32).pin_memory()
+    ph = torch.from_numpy(case.positions).clone().pin_memory()
+    step = op.bind_host(qh, oh, 0, 1, case.batch, k_new_host=kh, v_new_host=vh, lse_host=lh, positions_host=ph)
+    for _ in range(3):
+        oh.zero_()
+        step()
+    assert_attention_close(case, bits(oh), lh.numpy(), want_o, want_l)
+    assert np.array_equal(bits(ck), want_k) and np.array_equal(bits(cv), want_v)
+    op.close()
+
+
 def test_kv_append_standalone_bit_exact_with_canaries():
     dev = torch.device("cuda:0")
     case = Case(seed=50, interval=3, batch=2, max_batch=4, q_heads=2, kv_heads=2, max_seq=16, positions=[0, 13], poison=False)
