@@ -38,6 +38,49 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int s
                  "r"(src_bytes)
                  : "memory");
 }
+// The GPU's nanosecond clock: what the bounded device-side waits measure against.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Per-CTA time stamps of the decode-step kernels, for tuning the chain of programmatic dependents
+// (compiled in only with -DELLM_CHAIN_TRACE; `python -m ellm_b200.chain_trace` builds that variant
+// of the library beside the product one and prints the timeline).  A kernel makes one ChainTrace at
+// its start; thread 0 stamps waited() after griddepcontrol.wait, mid() / mid2() at two points of the
+// kernel's choosing, and the destructor stores the record {kernel id, SM, CTA, five times}.
+#ifdef ELLM_CHAIN_TRACE
+constexpr unsigned kChainTraceCap = 65536;
+__device__ unsigned long long g_chain_trace[kChainTraceCap * 6];
+__device__ unsigned g_chain_trace_n;
+struct ChainTrace {
+    unsigned long long t0, t1, t2, t3;
+    int kid;
+    __device__ __forceinline__ explicit ChainTrace(int k) : t1(0), t2(0), t3(0), kid(k) { t0 = global_timer_ns(); }
+    __device__ __forceinline__ void waited() { if (threadIdx.x == 0 && t1 == 0) t1 = global_timer_ns(); }
+    __device__ __forceinline__ void mid() { if (threadIdx.x == 0 && t2 == 0) t2 = global_timer_ns(); }
+    __device__ __forceinline__ void mid2() { if (threadIdx.x == 0 && t3 == 0) t3 = global_timer_ns(); }
+    __device__ __forceinline__ ~ChainTrace() {
+        if (threadIdx.x != 0) return;
+        const unsigned long long t4 = global_timer_ns();
+        const unsigned slot = atomicAdd(&g_chain_trace_n, 1u);
+        if (slot >= kChainTraceCap) return;
+        unsigned sm;
+        asm("mov.u32 %0, %%smid;" : "=r"(sm));
+        unsigned long long* r = g_chain_trace + static_cast<size_t>(slot) * 6;
+        r[0] = (static_cast<unsigned long long>(kid) << 48) | (static_cast<unsigned long long>(sm) << 32) | blockIdx.x;
+        r[1] = t0; r[2] = t1; r[3] = t2; r[4] = t3; r[5] = t4;
+    }
+};
+#else
+struct ChainTrace {
+    __device__ __forceinline__ explicit ChainTrace(int) {}
+    __device__ __forceinline__ void waited() {}
+    __device__ __forceinline__ void mid() {}
+    __device__ __forceinline__ void mid2() {}
+};
+#endif
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

@@ -183,6 +183,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
     int* lens = prefix + kDecMaxBatch + 1;                                                        // [kDecMaxBatch]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t warp_smem = smem_u32(smem) + warp * kDecStages * kDecWarpStageBytes;
+    ChainTrace ct(2);
 
     // Under a programmatic dependent launch of this grid, wait here for the kernel before it (it
     // wrote the positions, the queries and the newest cache row); a no-op for an ordinary launch.
@@ -193,6 +194,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
     if (waited) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        ct.waited();
     }
     dec_build_prefix(p, prefix, lens);
     const long long segs_per_seq = static_cast<long long>(p.kv_heads) * p.gtiles;
@@ -292,6 +294,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
             asm volatile("griddepcontrol.wait;" ::: "memory");
             asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             waited = true;
+            ct.waited();
         }
         // every stage is its own group and the groups are committed in stage order, so "all but the
         // last kDecStages - 1 groups have landed" below always covers the stage an iteration needs
@@ -340,6 +343,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_splitkv_kernel(const De
             __syncwarp();  // all lanes done with this stage before it is refilled
         }
         cp_async_wait<0>();
+        ct.mid();   // (trace) the CTA's first piece has been streamed
 
         // ---- end of piece: combine the 4 warps through shared memory ----
         // a head's sum is spread over the 8 lanes that share lane%4 (their keys differ)

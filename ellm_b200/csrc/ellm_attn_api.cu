@@ -1320,4 +1320,17 @@ extern "C" int ellm_debug_read_tc_trace(long long* host, size_t count) {
 }
 #endif
 
+#ifdef ELLM_CHAIN_TRACE
+// reset != 0: forget the records; else copy the record count and (host != NULL) the records, 6 words each
+extern "C" int ellm_debug_chain_trace(unsigned long long* host, unsigned* count, int reset) {
+    if (reset) {
+        const unsigned zero = 0;
+        return cudaMemcpyToSymbol(ellm::g_chain_trace_n, &zero, sizeof(zero)) == cudaSuccess ? 0 : 2;
+    }
+    if (count && cudaMemcpyFromSymbol(count, ellm::g_chain_trace_n, sizeof(unsigned)) != cudaSuccess) return 2;
+    if (host && cudaMemcpyFromSymbol(host, ellm::g_chain_trace, sizeof(unsigned long long) * ellm::kChainTraceCap * 6) != cudaSuccess) return 2;
+    return 0;
+}
+#endif
+
 #include "ellm_proj_api.cuh"

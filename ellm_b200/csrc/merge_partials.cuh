@@ -50,8 +50,12 @@ __host__ __device__ inline size_t merge_smem_bytes(int batch, int pieces_cap) {
 }
 
 template <typename OutT, int kWarps, int kAhead>
-__global__ void __launch_bounds__(kWarps * 32) decode_merge_kernel(const DecodeParams p, OutT* out, float* lse, int pieces_cap) {
+// (both shapes are held to 64 registers: they have to fit beside two decode CTAs of ~184 registers x 128 threads -
+// one wide CTA, or the light shape's three or four per SM - or they cannot move in, and release their own
+// dependents, before the decode grid has drained)
+__global__ void __launch_bounds__(kWarps * 32, kWarps >= 8 ? 4 : 20) decode_merge_kernel(const DecodeParams p, OutT* out, float* lse, int pieces_cap) {
     // a following kernel launched as a programmatic dependent may start its own prologue now
+    ChainTrace ct(3);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ __align__(16) unsigned char merge_smem[];
     int* s_prefix = reinterpret_cast<int*>(merge_smem);                // [batch + 1]
@@ -94,6 +98,7 @@ __global__ void __launch_bounds__(kWarps * 32) decode_merge_kernel(const DecodeP
     // under a programmatic dependent launch: wait until the decode grid's writes are visible
     // (a no-op for an ordinary launch)
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    ct.waited();
     if (tiles_b == 0) {  // no key in range for this sequence
         if (warp == 0) {
             store_row4<OutT>(orow, make_float4(0.f, 0.f, 0.f, 0.f));
@@ -146,6 +151,7 @@ __global__ void __launch_bounds__(kWarps * 32) decode_merge_kernel(const DecodeP
         wsum += w;
         acc.x += w * y.x; acc.y += w * y.y; acc.z += w * y.z; acc.w += w * y.w;
     }
+    ct.mid();   // (trace) the weighted sums are done
     s_acc[warp][lane] = acc;
     __syncthreads();   // also: every read of s_red above is done
     if (lane == 0) s_red[warp] = wsum;

@@ -116,11 +116,6 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return done;
 }
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 
 // Bounded wait.  Returns false when the CTA has been told to give up (abort word set by
 // any thread) or when this wait itself ran out, in which case it sets both words.

@@ -94,6 +94,7 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
     const uint32_t x_base = smem_u32(smem), zero_addr = x_base + p.m_rows * p.k_chunks * 16, w_base = x_base + x_bytes;
     const int n0 = blockIdx.x * p.cols;
     const int passes = (p.k_chunks + p.pass_chunks - 1) / p.pass_chunks;
+    ChainTrace ct(p.heads != 0 ? 7 : 8);
     // 16-column slices with at most 8 activation rows (the decode-step shapes) read their fragments with
     // plain 16-byte shared-memory loads instead of ldmatrix (see the product loop); both tiles are then
     // laid out for that: the 16-byte piece p of row r sits at p ^ ((r & 1) << 2)
@@ -121,6 +122,7 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
     if (p.heads != 0) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     // activations (and the residual) are the previous kernels' output: wait for them
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    ct.waited();
     // only now may the next kernel of the stream start its own prologue: whatever it reads before
     // its own wait (a decode kernel with early streaming: the positions, older cache rows) is then
     // older than everything this kernel waited for
@@ -194,6 +196,7 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
         }
         cp_async_wait<0>();
         __syncthreads();
+        ct.mid();   // (trace) slice and rows are in shared memory
         const int c_begin = pass * p.pass_chunks;
         const int steps = min(p.pass_chunks, p.k_chunks - c_begin) >> 1;   // 16-wide k steps of this pass
         if (few_rows) {
@@ -256,6 +259,7 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
     }
     // every warp is done with the slice: the partial sums go over it
     __syncthreads();
+    ct.mid2();  // (trace) the product loop is done
     float* part = reinterpret_cast<float*>(smem + x_bytes);   // [warp][row][col]
     if (few_rows) {
         // transposed accumulators: this lane holds columns lane/4 and lane/4 + 8 of rows (lane%4)*2, +1
