@@ -17,7 +17,10 @@
 //   * then legacy warp-level MMA (m16n8k16) with the activation rows as M - the tensor core is
 //     only the cheapest way to multiply up to 16 rows by a tile - the 16-wide k steps going round
 //     the 8 warps; the eight partial sums of an output are added in warp order, the residual is
-//     added, the sum is rounded to bf16 once.
+//     added, the sum is rounded to bf16 once;
+//   * 16-column slices with at most 8 rows (a decode step of a few sequences) take the products
+//     transposed - the slice's columns as M - and read their fragments with 16-byte shared-memory
+//     loads instead of ldmatrix, which was the limit of the loop (see the product loop).
 // When the activation rows leave too little shared memory for the whole slice (many rows, long K)
 // the slice is taken in several passes over K.
 #pragma once
