@@ -16,6 +16,16 @@ def test_library_exports_every_declared_symbol():
     assert lib.ellm_attn_abi_version() == 1
 
 
+def test_product_library_carries_no_tuning_hooks():
+    """The per-CTA time stamps of the decode chain and of the prefill kernel exist only in libraries built
+    with -DELLM_CHAIN_TRACE / -DELLM_TC_TRACE (ellm_b200/chain_trace.py builds one beside the product)."""
+    lib = ellm_b200.load()
+    for name in ("ellm_debug_chain_trace", "ellm_debug_read_tc_trace"):
+        assert not hasattr(lib, name)
+    from ellm_b200 import chain_trace
+    assert chain_trace.TRACE_LIB != ellm_b200.build.LIB and callable(chain_trace.build_trace_lib)
+
+
 def test_status_strings():
     lib = ellm_b200.load()
     assert lib.ellm_status_string(0) == b"ok"
