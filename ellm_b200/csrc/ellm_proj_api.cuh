@@ -59,6 +59,7 @@ int proj_common_create(ProjHandle* h, int device, void* stream, int async) {
     ELLM_CUDA(cudaMemset(h->status_dev, 0, sizeof(int)));
     static_assert(ellm::kSkSmemMax + 256 + 3072 <= 232448, "shared memory budget: dynamic + static");
     if (cudaFuncSetAttribute(ellm::proj_skinny_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kSkSmemMax + 256) != cudaSuccess ||
+        cudaFuncSetAttribute(ellm::proj_skinny_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kSkSmemMax + 256) != cudaSuccess ||
         cudaFuncSetAttribute(ellm::proj_skinny_kernel<ellm::kSkMaxCols / 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, ellm::kSkSmemMax + 256) != cudaSuccess)
         return fail(ELLM_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(cudaGetLastError()));
     return ELLM_OK;
@@ -133,7 +134,8 @@ int skinny_launch(ProjHandle* h, const ProjHandle::Skinny& sk, const void* a, si
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = fused ? 2 : 1;
-    const cudaError_t e = cols == 16 ? cudaLaunchKernelEx(&cfg, ellm::proj_skinny_kernel<1>, p)
+    const cudaError_t e = cols == 16 && rows > 8 ? cudaLaunchKernelEx(&cfg, ellm::proj_skinny_kernel<1, true>, p)
+                          : cols == 16 ? cudaLaunchKernelEx(&cfg, ellm::proj_skinny_kernel<1>, p)
                                      : cudaLaunchKernelEx(&cfg, ellm::proj_skinny_kernel<ellm::kSkMaxCols / 16>, p);
     if (e != cudaSuccess) return fail(ELLM_ERR_CUDA, "projection launch failed: %s", cudaGetErrorString(e));
     ++h->skinny_launches;

@@ -18,9 +18,9 @@
 //     only the cheapest way to multiply up to 16 rows by a tile - the 16-wide k steps going round
 //     the 8 warps; the eight partial sums of an output are added in warp order, the residual is
 //     added, the sum is rounded to bf16 once;
-//   * 16-column slices with at most 8 rows (a decode step of a few sequences) take the products
-//     transposed - the slice's columns as M - and read their fragments with 16-byte shared-memory
-//     loads instead of ldmatrix, which was the limit of the loop (see the product loop).
+//   * 16-column slices (the decode-step shapes) take the products transposed - the slice's columns
+//     as M, the rows as one or two N blocks of 8 - and read their fragments with 16-byte
+//     shared-memory loads instead of ldmatrix, which was the limit of the loop (see the product loop).
 // When the activation rows leave too little shared memory for the whole slice (many rows, long K)
 // the slice is taken in several passes over K.
 #pragma once
@@ -89,7 +89,9 @@ inline int skinny_smem_bytes(int k_chunks, int cols, int pass_chunks, int m_rows
 
 // kNB16: blocks of 16 columns a CTA may own (its accumulators): 1 for the 16-column slices of the
 // decode-step shapes, kSkMaxCols / 16 for anything up to kSkMaxCols columns.
-template <int kNB16>
+// kTwo (16-column instantiation only): 9 to 16 activation rows, two N blocks of the transposed products; an
+// instantiation of its own so that the code for up to 8 rows - the one-sequence decode step - stays as it is.
+template <int kNB16, bool kTwo = false>
 __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const SkinnyParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -98,10 +100,12 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
     const int n0 = blockIdx.x * p.cols;
     const int passes = (p.k_chunks + p.pass_chunks - 1) / p.pass_chunks;
     ChainTrace ct(p.heads != 0 ? 7 : 8);
-    // 16-column slices with at most 8 activation rows (the decode-step shapes) read their fragments with
-    // plain 16-byte shared-memory loads instead of ldmatrix (see the product loop); both tiles are then
-    // laid out for that: the 16-byte piece p of row r sits at p ^ ((r & 1) << 2)
-    const bool few_rows = kNB16 == 1 && p.m_rows <= 8 && (p.k_chunks & 3) == 0 && (p.pass_chunks & 3) == 0;
+    // 16-column slices (the decode-step shapes) read their fragments with plain 16-byte shared-memory loads
+    // instead of ldmatrix (see the product loop); both tiles are then laid out for that: the 16-byte piece
+    // p of row r sits at p ^ ((r & 1) << 2).  Up to 8 activation rows are one N block of the transposed
+    // products, 9 to 16 two.
+    const bool few_rows = kNB16 == 1 && (kTwo || p.m_rows <= 8) && (p.k_chunks & 3) == 0 && (p.pass_chunks & 3) == 0;
+    constexpr bool two_blocks = kTwo;
 
     // pieces [pass * pass_chunks, ...) of every row of the slice; rows past N arrive as zeros
     auto request_pass = [&](int pass) {
@@ -203,7 +207,7 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
         const int c_begin = pass * p.pass_chunks;
         const int steps = min(p.pass_chunks, p.k_chunks - c_begin) >> 1;   // 16-wide k steps of this pass
         if (few_rows) {
-            // 16 columns, at most 8 activation rows: the products are taken transposed - the slice's 16
+            // 16 columns: the products are taken transposed - the slice's 16
             // columns are the M side of m16n8k16, the rows the N side, one product per 16 k instead of
             // two - and the fragments come from plain 16-byte shared-memory loads: ldmatrix delivers
             // one 8x8 matrix per ~3 clocks per SM here (measured: the slice's 128 KB took 2.4 us through
@@ -218,6 +222,25 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
             const uint32_t w_lo = w_base + g * p.pass_chunks * 16, w_hi = w_lo + 8 * p.pass_chunks * 16;
             const bool x_live = g < p.m_rows;
             const uint32_t x_row = x_base + g * p.k_chunks * 16;
+            if (two_blocks) {
+                // 9 to 16 rows: rows g and g + 8 are two N blocks against the same slice fragments; accumulators
+                // 0, 1 belong to rows 0-7 and 2, 3 to rows 8-15
+                const bool x_live_hi = g + 8 < p.m_rows;
+                const uint32_t x_row_hi = x_row + 8 * p.k_chunks * 16;
+                for (int kb = warp; kb < kblocks; kb += kSkWarps) {
+                    const int c = kb * 4 + t;
+                    const uint4 lo = lds128(w_lo + ((c ^ sw) << 4)), hi = lds128(w_hi + ((c ^ sw) << 4));
+                    const uint32_t x_off = ((c_begin + c) ^ sw) << 4, z_off = (((c_begin + c) ^ sw) & 7) << 4;
+                    const uint4 x0 = lds128(x_live ? x_row + x_off : zero_addr + z_off);
+                    const uint4 x1 = lds128(x_live_hi ? x_row_hi + x_off : zero_addr + z_off);
+                    const uint32_t a0[4] = {lo.x, hi.x, lo.y, hi.y}, a1[4] = {lo.z, hi.z, lo.w, hi.w};
+                    mma_bf16_16816(tacc[0], a0, x0.x, x0.y);
+                    mma_bf16_16816(tacc[1], a1, x0.z, x0.w);
+                    mma_bf16_16816(tacc[2], a0, x1.x, x1.y);
+                    mma_bf16_16816(tacc[3], a1, x1.z, x1.w);
+                }
+                continue;
+            }
             for (int kb = warp; kb < kblocks; kb += 2 * kSkWarps) {
                 uint4 lo[2], hi[2], xr[2];
 #pragma unroll
@@ -268,10 +291,22 @@ __global__ void __launch_bounds__(kSkThreads, 3) proj_skinny_kernel(const Skinny
         // transposed accumulators: this lane holds columns lane/4 and lane/4 + 8 of rows (lane%4)*2, +1
         const int col = lane >> 2, m0 = (lane & 3) * 2;
         float* dst = part + (warp * kSkRows + m0) * p.cols + col;
-        dst[0] = (tacc[0][0] + tacc[1][0]) + (tacc[2][0] + tacc[3][0]);
-        dst[p.cols] = (tacc[0][1] + tacc[1][1]) + (tacc[2][1] + tacc[3][1]);
-        dst[8] = (tacc[0][2] + tacc[1][2]) + (tacc[2][2] + tacc[3][2]);
-        dst[p.cols + 8] = (tacc[0][3] + tacc[1][3]) + (tacc[2][3] + tacc[3][3]);
+        if (two_blocks) {
+            float* dst_hi = dst + 8 * p.cols;   // rows 8-15
+            dst[0] = tacc[0][0] + tacc[1][0];
+            dst[p.cols] = tacc[0][1] + tacc[1][1];
+            dst[8] = tacc[0][2] + tacc[1][2];
+            dst[p.cols + 8] = tacc[0][3] + tacc[1][3];
+            dst_hi[0] = tacc[2][0] + tacc[3][0];
+            dst_hi[p.cols] = tacc[2][1] + tacc[3][1];
+            dst_hi[8] = tacc[2][2] + tacc[3][2];
+            dst_hi[p.cols + 8] = tacc[2][3] + tacc[3][3];
+        } else {
+            dst[0] = (tacc[0][0] + tacc[1][0]) + (tacc[2][0] + tacc[3][0]);
+            dst[p.cols] = (tacc[0][1] + tacc[1][1]) + (tacc[2][1] + tacc[3][1]);
+            dst[8] = (tacc[0][2] + tacc[1][2]) + (tacc[2][2] + tacc[3][2]);
+            dst[p.cols + 8] = (tacc[0][3] + tacc[1][3]) + (tacc[2][3] + tacc[3][3]);
+        }
     } else {
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
 #pragma unroll
